@@ -1,0 +1,150 @@
+/*
+ * scanscam_b200 -- C-ABI launch layer of the B200 (sm_100a) gated linear scan.
+ *
+ *   forward :  h_t  = a_t * h_{t-1} + b_t           (a = gate, b = value, h = output)
+ *   backward:  gb_t = g_t + a_{t+1} * gb_{t+1}      (g = upstream gradient)
+ *              ga_t = gb_t * h_{t-1}
+ *
+ * Every entry point takes raw DEVICE pointers, 64-bit sizes and a CUDA stream
+ * (a `cudaStream_t` passed as `void*`; NULL = the legacy default stream), enqueues
+ * its kernels on that stream without synchronising, and returns an `ssb_status_t`.
+ * Outputs are caller-allocated, as in the reference extension, whose functions all
+ * have the shape `void f(Tensor inputs..., Tensor outputs...)`
+ * (reference: src/scanscam_cuda.cu:725-737).  No entry point allocates device
+ * memory; the ones that need scratch take it from the caller (see
+ * ssb_scan_workspace_bytes).  No torch types appear here: the PyTorch extension
+ * `scanscam_ext` and any other FFI binding (ctypes, cgo, JNI ...) are equal clients.
+ *
+ * "rows" layout   : dense [rows, T], scan axis innermost and contiguous.
+ * "cl" layout     : dense [N, T, C] (channels-last), scan over the middle axis.
+ *
+ * Thread safety: entry points may be called concurrently from several host threads
+ * and on several streams.  The only process-wide state is a per-device status word
+ * that device code sets when one of its bounded waits gives up (ssb_device_status).
+ */
+#ifndef SCANSCAM_B200_H
+#define SCANSCAM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ssb_status {
+    SSB_OK = 0,
+    SSB_ERR_BAD_ARG = 1,     /* NULL where data is required, negative size, size overflow */
+    SSB_ERR_ALIGNMENT = 2,   /* pointer not aligned to its element size */
+    SSB_ERR_LAUNCH = 3,      /* the CUDA runtime or driver rejected a call; see ssb_last_error */
+    SSB_ERR_DEVICE_WAIT = 4, /* a bounded device-side wait ran out (reported by ssb_device_status) */
+    SSB_ERR_WORKSPACE = 5,   /* workspace missing or smaller than ssb_scan_workspace_bytes says */
+    SSB_ERR_UNSUPPORTED = 6  /* the requested kernel variant cannot run this shape */
+} ssb_status_t;
+
+/* Kernel families, for callers that want to pin one (tests, tuning sweeps).
+ * SSB_VARIANT_AUTO picks from (rows, T, alignment). */
+typedef enum ssb_variant {
+    SSB_VARIANT_AUTO = 0,
+    SSB_VARIANT_WARP = 1,    /* one warp per row, register-resident, any T / any alignment */
+    SSB_VARIANT_TMA = 2,     /* TMA-staged shared-memory tiles; needs T % 32 == 0, 16-B aligned base */
+    SSB_VARIANT_LOOKBACK = 3 /* T split across CTAs with decoupled look-back; needs a workspace */
+} ssb_variant_t;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int ssb_version(void);
+/* Human-readable name of a status code (static storage). */
+const char *ssb_status_string(int status);
+/* Message of the last failure on the calling host thread (thread-local, never NULL). */
+const char *ssb_last_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * Forward scan, rows layout.
+ * Replaces `blocked_linear_scan(gate, value, output)` (src/scanscam_cuda.cu:260-307,
+ * kernels :144-258) and, behind the same math, `simple_linear_scan` (:38-59) and
+ * `coalesced_linear_scan` (:121-142).
+ *   gate, value, out : [rows, T]
+ *   h_in             : optional [rows]; h just before step 0 (NULL = 0, the reference's case).
+ *                      Used when this call is one shard of a longer sequence.
+ * ---------------------------------------------------------------------------------- */
+int ssb_scan_fwd_f32(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                     const float *h_in, void *stream);
+int ssb_scan_fwd_f64(const double *gate, const double *value, double *out, int64_t rows,
+                     int64_t T, const double *h_in, void *stream);
+/* Same, with the kernel family pinned and an optional workspace (only
+ * SSB_VARIANT_LOOKBACK needs one). */
+int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t rows,
+                        int64_t T, const float *h_in, int variant, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fused backward, rows layout: one pass reads gate, h, gout and writes both gradients.
+ * Replaces `blocked_linear_scan_backward(gate, output, outGrad, gateGradOut, valueGradOut)`
+ * (src/scanscam_cuda.cu:427-469, kernel :366-425) and `simple_linear_scan_backward`
+ * (:334-364).
+ *   gate, h, gout, ggate, gvalue : [rows, T]   (h = the forward output)
+ *   c_in   : optional [rows]; a_T * gb_T flowing in from the step after the last one (NULL = 0)
+ *   h_prev : optional [rows]; h just before step 0, multiplies gb_0 into ga_0 (NULL = 0)
+ * ---------------------------------------------------------------------------------- */
+int ssb_scan_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate,
+                     float *gvalue, int64_t rows, int64_t T, const float *c_in,
+                     const float *h_prev, void *stream);
+int ssb_scan_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate,
+                     double *gvalue, int64_t rows, int64_t T, const double *c_in,
+                     const double *h_prev, void *stream);
+int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate,
+                        float *gvalue, int64_t rows, int64_t T, const float *c_in,
+                        const float *h_prev, int variant, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
+/* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
+ * The workspace must be 256-byte aligned; its contents need not be initialised. */
+size_t ssb_scan_workspace_bytes(int64_t rows, int64_t T, int variant);
+
+/* ------------------------------------------------------------------------------------
+ * Channels-last layout, [N, T, C] scanned over T.
+ * Replace `transposed_linear_scan(gate, value, output, channelsPerBlock)`
+ * (src/scanscam_cuda.cu:556-582, kernel :471-554) and
+ * `transposed_linear_scan_backward(...)` (:687-723, kernel :584-685).  The reference's
+ * `channelsPerBlock` is a tuning hint with no effect on results; it has no counterpart here.
+ * ---------------------------------------------------------------------------------- */
+int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T,
+                        int64_t C, void *stream);
+int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, int64_t N,
+                        int64_t T, int64_t C, void *stream);
+int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate,
+                        float *gvalue, int64_t N, int64_t T, int64_t C, void *stream);
+int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate,
+                        double *gvalue, int64_t N, int64_t T, int64_t C, void *stream);
+
+/* ------------------------------------------------------------------------------------
+ * Sequence (T) sharding.  The reference never splits a sequence; these three entry
+ * points are the pieces a caller needs to do it: each shard is the affine map
+ * h_end = A*h_in + B per row, maps compose associatively, and the composition of the
+ * shards to the left (forward) or right (backward) is the carry a shard starts from.
+ *
+ * ssb_shard_reduce_fwd_f32: agg[r] = (A, B) with A = prod_t a_t and B = the scan's last
+ *   value when started from 0.  Reads gate and value once, writes 8 bytes per row.
+ * ssb_shard_reduce_bwd_f32: agg[r] = (A, D) of the reverse recurrence
+ *   c_t = a_t * (g_t + c_{t+1}):  c_first = A * c_in + D.
+ * ssb_shard_carry_f32: aggs is [n_shards, rows, 2] (every shard's pair, e.g. after an
+ *   all-gather).  reverse == 0: carry[r] = h entering shard `shard` (fold of shards
+ *   0..shard-1 from zero).  reverse != 0: carry[r] = c entering shard `shard` from the
+ *   right (fold of shards n_shards-1 .. shard+1 from zero).
+ * ---------------------------------------------------------------------------------- */
+int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows,
+                             int64_t T, void *stream);
+int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows,
+                             int64_t T, void *stream);
+int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse, int64_t rows,
+                        float *carry, void *stream);
+
+/* Synchronises the current device, returns and clears its device-side status word:
+ * SSB_OK, or SSB_ERR_DEVICE_WAIT if a kernel's bounded wait (mbarrier, look-back flag)
+ * gave up since the last call.  *detail (optional) receives the kernel-specific code. */
+int ssb_device_status(int *detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCANSCAM_B200_H */

@@ -1,0 +1,78 @@
+"""ctypes binding of the C-ABI library (``include/scanscam_b200.h``).
+
+This is the same boundary any other FFI client would bind; the test-suite and the benchmark
+call the kernels through it with raw device pointers taken from torch tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libscanscam_b200.so")
+
+OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED = range(7)
+VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK = range(4)
+
+_p, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+
+# name -> (restype, argtypes); one entry per declaration in include/scanscam_b200.h
+SIGNATURES = {
+    "ssb_version": (_int, []),
+    "ssb_status_string": (ctypes.c_char_p, [_int]),
+    "ssb_last_error": (ctypes.c_char_p, []),
+    "ssb_scan_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
+    "ssb_scan_fwd_f64": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
+    "ssb_scan_fwd_f32_ex": (_int, [_p, _p, _p, _i64, _i64, _p, _int, _p, _sz, _p]),
+    "ssb_scan_bwd_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_bwd_f64": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_bwd_f32_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _int, _p, _sz, _p]),
+    "ssb_scan_workspace_bytes": (_sz, [_i64, _i64, _int]),
+    "ssb_scan_cl_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _i64, _p]),
+    "ssb_scan_cl_fwd_f64": (_int, [_p, _p, _p, _i64, _i64, _i64, _p]),
+    "ssb_scan_cl_bwd_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "ssb_scan_cl_bwd_f64": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "ssb_shard_reduce_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p]),
+    "ssb_shard_reduce_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p]),
+    "ssb_shard_carry_f32": (_int, [_p, _int, _int, _int, _i64, _p, _p]),
+    "ssb_device_status": (_int, [ctypes.POINTER(_int)]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library (raises ``OSError`` when it has not been built) and types every symbol."""
+    global _lib
+    if _lib is None:
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class NativeError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"scanscam_b200 status {status}: {message}")
+        self.status = status
+
+
+def check(status: int) -> None:
+    """Raises :class:`NativeError` for a non-zero status, with the library's message."""
+    if status != OK:
+        lib = load()
+        raise NativeError(status, f"{lib.ssb_status_string(status).decode()}: {lib.ssb_last_error().decode()}")
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a torch tensor (None passes through as NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t) -> int:
+    """The raw handle of torch's current stream on the tensor's device."""
+    import torch
+
+    return torch.cuda.current_stream(t.device).cuda_stream

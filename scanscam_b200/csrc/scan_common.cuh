@@ -1,0 +1,98 @@
+// Shared device helpers for the gated-linear-scan kernels (sm_100a).
+//
+// The scan h_t = a_t*h_{t-1} + b_t is a fold of affine maps x -> a*x + b.  Maps compose
+// associatively: applying (a1,b1) and then (a2,b2) is (a2*a1, a2*b1 + b2).  Every kernel
+// here composes such pairs and never divides by a gate or goes through logarithms, so
+// exact-zero gates ("resets") and gates with |a| > 1 are handled like any other value.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ssb {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// Device-side status word: [0] = ssb_status_t code (0 = ok), [1] = kernel-specific detail.
+// Written by a kernel whose bounded wait gives up; read and cleared by ssb_device_status().
+__device__ int g_status_word[2];
+
+__device__ __forceinline__ void report_device_wait(int detail) {
+    if (atomicCAS(&g_status_word[0], 0, 4 /* SSB_ERR_DEVICE_WAIT */) == 0) {
+        g_status_word[1] = detail;
+    }
+}
+
+// A naturally aligned pack of VEC scalars; loads/stores of a 16-byte pack compile to one
+// 128-bit memory instruction.
+template <typename real, int VEC>
+struct alignas(sizeof(real) * VEC) Pack {
+    real v[VEC];
+};
+
+// Streaming (evict-first) global loads and stores: every byte is touched exactly once.
+template <typename real, int VEC>
+__device__ __forceinline__ Pack<real, VEC> load_stream(const real *p) {
+    Pack<real, VEC> r;
+    if constexpr (sizeof(real) * VEC == 16 && sizeof(real) == 4) {
+        float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else if constexpr (sizeof(real) * VEC == 16 && sizeof(real) == 8) {
+        double2 t = __ldcs(reinterpret_cast<const double2 *>(p));
+        r.v[0] = t.x; r.v[1] = t.y;
+    } else {
+        static_assert(VEC == 1, "unsupported pack width");
+        r.v[0] = __ldcs(p);
+    }
+    return r;
+}
+
+template <typename real, int VEC>
+__device__ __forceinline__ void store_stream(real *p, const Pack<real, VEC> &r) {
+    if constexpr (sizeof(real) * VEC == 16 && sizeof(real) == 4) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(r.v[0], r.v[1], r.v[2], r.v[3]));
+    } else if constexpr (sizeof(real) * VEC == 16 && sizeof(real) == 8) {
+        __stcs(reinterpret_cast<double2 *>(p), make_double2(r.v[0], r.v[1]));
+    } else {
+        static_assert(VEC == 1, "unsupported pack width");
+        __stcs(p, r.v[0]);
+    }
+}
+
+template <typename real>
+__device__ __forceinline__ real fma_(real a, real b, real c);
+template <>
+__device__ __forceinline__ float fma_<float>(float a, float b, float c) { return fmaf(a, b, c); }
+template <>
+__device__ __forceinline__ double fma_<double>(double a, double b, double c) { return fma(a, b, c); }
+
+// Inclusive scan of affine maps across the lanes of a warp, left to right: afterwards lane l
+// holds the composition of the maps of lanes 0..l (lane 0's applied first).
+template <typename real>
+__device__ __forceinline__ void warp_scan_forward(real &A, real &B, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        real Ap = __shfl_up_sync(kFullMask, A, d);
+        real Bp = __shfl_up_sync(kFullMask, B, d);
+        if (lane >= d) {
+            B = fma_<real>(A, Bp, B);
+            A *= Ap;
+        }
+    }
+}
+
+// Same, right to left: lane l ends with the composition of lanes 31..l (lane 31's first).
+template <typename real>
+__device__ __forceinline__ void warp_scan_reverse(real &A, real &B, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        real Ap = __shfl_down_sync(kFullMask, A, d);
+        real Bp = __shfl_down_sync(kFullMask, B, d);
+        if (lane + d < 32) {
+            B = fma_<real>(A, Bp, B);
+            A *= Ap;
+        }
+    }
+}
+
+}  // namespace ssb

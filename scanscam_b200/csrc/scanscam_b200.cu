@@ -1,0 +1,465 @@
+// C-ABI launch layer (see include/scanscam_b200.h).  One translation unit: the kernels are
+// header templates instantiated here.  No torch, no allocation, no synchronisation except in
+// ssb_device_status().
+#include "../../include/scanscam_b200.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+
+#include "scan_cl.cuh"
+#include "scan_common.cuh"
+#include "scan_tma.cuh"
+#include "scan_warp.cuh"
+
+namespace {
+
+thread_local char t_last_error[512] = "";
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int check_launch(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return fail(SSB_ERR_LAUNCH, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    }
+    return SSB_OK;
+}
+
+bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Validates a [rows, T] problem; *n receives rows*T.
+int check_shape(int64_t rows, int64_t T, int64_t *n) {
+    if (rows < 0 || T < 0) return fail(SSB_ERR_BAD_ARG, "negative size: rows=%lld T=%lld", (long long)rows, (long long)T);
+    if (T > 0 && rows > std::numeric_limits<int64_t>::max() / 8 / T)
+        return fail(SSB_ERR_BAD_ARG, "rows*T overflows: rows=%lld T=%lld", (long long)rows, (long long)T);
+    *n = rows * T;
+    return SSB_OK;
+}
+
+int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int v = cached[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+// ------------------------------------------------------------------------------------
+// Warp-per-row family
+// ------------------------------------------------------------------------------------
+template <typename real>
+constexpr int vec_width() { return 16 / (int)sizeof(real); }
+
+int warp_grid(int64_t rows) {
+    const int64_t want = (rows + ssb::kWarpKernelWarps - 1) / ssb::kWarpKernelWarps;
+    const int64_t cap = (int64_t)sm_count() * 8;  // 8 CTAs of 8 warps fill an SM
+    return (int)(want < cap ? want : cap);
+}
+
+template <typename real, bool REDUCE>
+int launch_warp_fwd(const real *gate, const real *value, real *out, int64_t rows, int64_t T,
+                    const real *h_in, real *agg, cudaStream_t st) {
+    constexpr int V = vec_width<real>();
+    const bool vec = (T % V == 0) && aligned_to(gate, 16) && aligned_to(value, 16) &&
+                     (REDUCE || aligned_to(out, 16));
+    const int grid = warp_grid(rows);
+    const int block = ssb::kWarpKernelWarps * 32;
+    if (vec) {
+        ssb::warp_rows_fwd_kernel<real, V, 4, REDUCE><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, agg);
+    } else {
+        ssb::warp_rows_fwd_kernel<real, 1, 4, REDUCE><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, agg);
+    }
+    return check_launch("warp_rows_fwd_kernel");
+}
+
+template <typename real, bool REDUCE>
+int launch_warp_bwd(const real *gate, const real *h, const real *gout, real *ggate, real *gvalue,
+                    int64_t rows, int64_t T, const real *c_in, const real *h_prev, real *agg,
+                    cudaStream_t st) {
+    constexpr int V = vec_width<real>();
+    const bool vec = (T % V == 0) && aligned_to(gate, 16) && aligned_to(gout, 16) &&
+                     (REDUCE || (aligned_to(h, 16) && aligned_to(ggate, 16) && aligned_to(gvalue, 16)));
+    const int grid = warp_grid(rows);
+    const int block = ssb::kWarpKernelWarps * 32;
+    if (vec) {
+        ssb::warp_rows_bwd_kernel<real, V, 4, REDUCE><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, agg);
+    } else {
+        ssb::warp_rows_bwd_kernel<real, 1, 4, REDUCE><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, agg);
+    }
+    return check_launch("warp_rows_bwd_kernel");
+}
+
+// ------------------------------------------------------------------------------------
+// TMA family
+// ------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static std::atomic<void *> cached{nullptr};
+    void *p = cached.load(std::memory_order_acquire);
+    if (p == nullptr) {
+        cudaDriverEntryPointQueryResult q;
+        void *fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cached.store(fn, std::memory_order_release);
+        p = fn;
+    }
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+}
+
+bool tma_eligible(int64_t rows, int64_t T) {
+    return T % 32 == 0 && T >= 32 && rows <= 0x7fffffffLL && T / 32 <= 0x7fffffffLL;
+}
+
+// Describes a dense fp32 [rows, T] matrix as [rows][T/32][32] with boxes of `lines` 128-byte
+// lines of one row, 128-byte swizzle, zero fill outside.
+int make_rows_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, int lines) {
+    PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
+    if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {32, (cuuint64_t)(T / 32), (cuuint64_t)rows};
+    cuuint64_t strides[2] = {128, (cuuint64_t)T * 4};
+    cuuint32_t box[3] = {32, (cuuint32_t)lines, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SSB_OK;
+}
+
+template <int EPL, int STAGES, int WARPS>
+int launch_tma_fwd(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                   const float *h_in, cudaStream_t st) {
+    CUtensorMap mg, mv, mo;
+    int rc;
+    if ((rc = make_rows_map(&mg, gate, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mv, value, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mo, out, rows, T, EPL)) != SSB_OK) return rc;
+    auto kern = ssb::tma::tma_rows_fwd_kernel<EPL, STAGES, WARPS>;
+    const int smem = WARPS * ssb::tma::warp_smem_bytes<EPL, STAGES, 2, 1>() + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(tma_rows_fwd_kernel)");
+    const int64_t want = (rows + WARPS - 1) / WARPS;
+    const int grid = (int)(want < sm_count() ? want : sm_count());
+    kern<<<grid, WARPS * 32, smem, st>>>(mg, mv, mo, rows, T, h_in);
+    return check_launch("tma_rows_fwd_kernel");
+}
+
+template <int EPL, int STAGES, int WARPS>
+int launch_tma_bwd(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
+                   int64_t rows, int64_t T, const float *c_in, const float *h_prev, cudaStream_t st) {
+    CUtensorMap ma, mh, mg, mga, mgb;
+    int rc;
+    if ((rc = make_rows_map(&ma, gate, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mh, h, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mg, gout, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mga, ggate, rows, T, EPL)) != SSB_OK) return rc;
+    if ((rc = make_rows_map(&mgb, gvalue, rows, T, EPL)) != SSB_OK) return rc;
+    auto kern = ssb::tma::tma_rows_bwd_kernel<EPL, STAGES, WARPS>;
+    const int smem = WARPS * ssb::tma::warp_smem_bytes<EPL, STAGES, 3, 2>() + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(tma_rows_bwd_kernel)");
+    const int64_t want = (rows + WARPS - 1) / WARPS;
+    const int grid = (int)(want < sm_count() ? want : sm_count());
+    kern<<<grid, WARPS * 32, smem, st>>>(ma, mh, mg, mga, mgb, rows, T, c_in, h_prev);
+    return check_launch("tma_rows_bwd_kernel");
+}
+
+// `variant` carries the family in its low byte and a tuning id in bits 8..15 (0 = default).
+int family_of(int variant) { return variant & 0xff; }
+int tuning_of(int variant) { return (variant >> 8) & 0xff; }
+
+int dispatch_tma_fwd(int tuning, const float *gate, const float *value, float *out, int64_t rows,
+                     int64_t T, const float *h_in, cudaStream_t st) {
+    switch (tuning) {
+        case 0: return launch_tma_fwd<16, 4, 8>(gate, value, out, rows, T, h_in, st);
+        case 1: return launch_tma_fwd<16, 2, 8>(gate, value, out, rows, T, h_in, st);
+        case 2: return launch_tma_fwd<16, 3, 8>(gate, value, out, rows, T, h_in, st);
+        case 3: return launch_tma_fwd<16, 6, 8>(gate, value, out, rows, T, h_in, st);
+        case 4: return launch_tma_fwd<16, 4, 10>(gate, value, out, rows, T, h_in, st);
+        case 5: return launch_tma_fwd<16, 8, 4>(gate, value, out, rows, T, h_in, st);
+        case 6: return launch_tma_fwd<32, 2, 8>(gate, value, out, rows, T, h_in, st);
+        case 7: return launch_tma_fwd<32, 4, 4>(gate, value, out, rows, T, h_in, st);
+        case 8: return launch_tma_fwd<32, 2, 6>(gate, value, out, rows, T, h_in, st);
+        case 9: return launch_tma_fwd<16, 4, 6>(gate, value, out, rows, T, h_in, st);
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown forward TMA tuning id %d", tuning);
+    }
+}
+
+int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float *gout, float *ggate,
+                     float *gvalue, int64_t rows, int64_t T, const float *c_in, const float *h_prev,
+                     cudaStream_t st) {
+    switch (tuning) {
+        case 0: return launch_tma_bwd<16, 3, 8>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 1: return launch_tma_bwd<16, 2, 8>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 2: return launch_tma_bwd<16, 2, 10>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 3: return launch_tma_bwd<16, 4, 6>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 4: return launch_tma_bwd<16, 5, 5>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 5: return launch_tma_bwd<16, 8, 4>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 6: return launch_tma_bwd<32, 2, 5>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 7: return launch_tma_bwd<32, 3, 4>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 8: return launch_tma_bwd<16, 3, 6>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown backward TMA tuning id %d", tuning);
+    }
+}
+
+int pick_family(int64_t rows, int64_t T, bool all_aligned16) {
+    (void)rows;
+    if (all_aligned16 && tma_eligible(rows, T) && T >= 256) return SSB_VARIANT_TMA;
+    return SSB_VARIANT_WARP;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ssb_version(void) { return 100; }
+
+const char *ssb_status_string(int status) {
+    switch (status) {
+        case SSB_OK: return "ok";
+        case SSB_ERR_BAD_ARG: return "bad argument";
+        case SSB_ERR_ALIGNMENT: return "misaligned pointer";
+        case SSB_ERR_LAUNCH: return "CUDA launch or driver error";
+        case SSB_ERR_DEVICE_WAIT: return "device-side wait ran out";
+        case SSB_ERR_WORKSPACE: return "workspace missing or too small";
+        case SSB_ERR_UNSUPPORTED: return "variant does not support this shape";
+        default: return "unknown status";
+    }
+}
+
+const char *ssb_last_error(void) { return t_last_error; }
+
+size_t ssb_scan_workspace_bytes(int64_t rows, int64_t T, int variant) {
+    (void)rows; (void)T; (void)variant;
+    return 0;
+}
+
+int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                        const float *h_in, int variant, void *workspace, size_t workspace_bytes,
+                        void *stream) {
+    (void)workspace; (void)workspace_bytes;
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_fwd_f32: NULL tensor pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(out, 4) || !aligned_to(h_in, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_fwd_f32: pointers must be 4-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
+    int family = family_of(variant);
+    if (family == SSB_VARIANT_AUTO) family = pick_family(rows, T, al16);
+    switch (family) {
+        case SSB_VARIANT_WARP:
+            return launch_warp_fwd<float, false>(gate, value, out, rows, T, h_in, nullptr, st);
+        case SSB_VARIANT_TMA:
+            if (!al16 || !tma_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "TMA forward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            return dispatch_tma_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
+        default:
+            return fail(SSB_ERR_UNSUPPORTED, "forward variant %d is not available", variant);
+    }
+}
+
+int ssb_scan_fwd_f32(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                     const float *h_in, void *stream) {
+    return ssb_scan_fwd_f32_ex(gate, value, out, rows, T, h_in, SSB_VARIANT_AUTO, nullptr, 0, stream);
+}
+
+int ssb_scan_fwd_f64(const double *gate, const double *value, double *out, int64_t rows, int64_t T,
+                     const double *h_in, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_fwd_f64: NULL tensor pointer");
+    if (!aligned_to(gate, 8) || !aligned_to(value, 8) || !aligned_to(out, 8) || !aligned_to(h_in, 8))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_fwd_f64: pointers must be 8-byte aligned");
+    return launch_warp_fwd<double, false>(gate, value, out, rows, T, h_in, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
+                        int64_t rows, int64_t T, const float *c_in, const float *h_prev, int variant,
+                        void *workspace, size_t workspace_bytes, void *stream) {
+    (void)workspace; (void)workspace_bytes;
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !h || !gout || !ggate || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_bwd_f32: NULL tensor pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(h, 4) || !aligned_to(gout, 4) || !aligned_to(ggate, 4) ||
+        !aligned_to(gvalue, 4) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_f32: pointers must be 4-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
+                      aligned_to(ggate, 16) && aligned_to(gvalue, 16);
+    int family = family_of(variant);
+    if (family == SSB_VARIANT_AUTO) family = pick_family(rows, T, al16);
+    switch (family) {
+        case SSB_VARIANT_WARP:
+            return launch_warp_bwd<float, false>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr, st);
+        case SSB_VARIANT_TMA:
+            if (!al16 || !tma_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "TMA backward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            return dispatch_tma_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        default:
+            return fail(SSB_ERR_UNSUPPORTED, "backward variant %d is not available", variant);
+    }
+}
+
+int ssb_scan_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
+                     int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream) {
+    return ssb_scan_bwd_f32_ex(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, SSB_VARIANT_AUTO, nullptr, 0, stream);
+}
+
+int ssb_scan_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate, double *gvalue,
+                     int64_t rows, int64_t T, const double *c_in, const double *h_prev, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !h || !gout || !ggate || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_bwd_f64: NULL tensor pointer");
+    if (!aligned_to(gate, 8) || !aligned_to(h, 8) || !aligned_to(gout, 8) || !aligned_to(ggate, 8) ||
+        !aligned_to(gvalue, 8) || !aligned_to(c_in, 8) || !aligned_to(h_prev, 8))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_f64: pointers must be 8-byte aligned");
+    return launch_warp_bwd<double, false>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr,
+                                          static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ---- channels-last ---------------------------------------------------------------------
+namespace {
+constexpr int kClWarps = 16;
+constexpr int kClSteps = 8;
+
+int check_cl(int64_t N, int64_t T, int64_t C, int64_t *n) {
+    if (N < 0 || T < 0 || C < 0) return fail(SSB_ERR_BAD_ARG, "negative size: N=%lld T=%lld C=%lld", (long long)N, (long long)T, (long long)C);
+    if (C > 0 && T > std::numeric_limits<int64_t>::max() / 8 / C) return fail(SSB_ERR_BAD_ARG, "T*C overflows");
+    int rc = check_shape(N, T * C, n);
+    if (rc != SSB_OK) return rc;
+    const int64_t blocks = N * ((C + 31) / 32);
+    if (blocks > 0x7fffffffLL) return fail(SSB_ERR_BAD_ARG, "N*ceil(C/32) exceeds the grid limit");
+    return SSB_OK;
+}
+
+template <typename real>
+int cl_fwd(const real *gate, const real *value, real *out, int64_t N, int64_t T, int64_t C, void *stream) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_fwd: NULL tensor pointer");
+    if (!aligned_to(gate, sizeof(real)) || !aligned_to(value, sizeof(real)) || !aligned_to(out, sizeof(real)))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_fwd: pointers must be aligned to the element size");
+    const int grid = (int)(N * ((C + 31) / 32));
+    ssb::cl_fwd_kernel<real, kClWarps, kClSteps><<<grid, kClWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(gate, value, out, N, T, C);
+    return check_launch("cl_fwd_kernel");
+}
+
+template <typename real>
+int cl_bwd(const real *gate, const real *h, const real *gout, real *ggate, real *gvalue, int64_t N, int64_t T,
+           int64_t C, void *stream) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !h || !gout || !ggate || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_bwd: NULL tensor pointer");
+    if (!aligned_to(gate, sizeof(real)) || !aligned_to(h, sizeof(real)) || !aligned_to(gout, sizeof(real)) ||
+        !aligned_to(ggate, sizeof(real)) || !aligned_to(gvalue, sizeof(real)))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_bwd: pointers must be aligned to the element size");
+    const int grid = (int)(N * ((C + 31) / 32));
+    ssb::cl_bwd_kernel<real, kClWarps, kClSteps><<<grid, kClWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(gate, h, gout, ggate, gvalue, N, T, C);
+    return check_launch("cl_bwd_kernel");
+}
+}  // namespace
+
+extern "C" {
+
+int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, void *stream) {
+    return cl_fwd<float>(gate, value, out, N, T, C, stream);
+}
+int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, int64_t N, int64_t T, int64_t C, void *stream) {
+    return cl_fwd<double>(gate, value, out, N, T, C, stream);
+}
+int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
+                        int64_t T, int64_t C, void *stream) {
+    return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
+}
+int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate, double *gvalue,
+                        int64_t N, int64_t T, int64_t C, void *stream) {
+    return cl_bwd<double>(gate, h, gout, ggate, gvalue, N, T, C, stream);
+}
+
+// ---- sequence sharding -----------------------------------------------------------------
+int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows, int64_t T, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (rows == 0) return SSB_OK;
+    if (!agg || (n > 0 && (!gate || !value))) return fail(SSB_ERR_BAD_ARG, "ssb_shard_reduce_fwd_f32: NULL pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(agg, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_shard_reduce_fwd_f32: pointers must be 4-byte aligned");
+    return launch_warp_fwd<float, true>(gate, value, nullptr, rows, T, nullptr, agg, static_cast<cudaStream_t>(stream));
+}
+
+int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (rows == 0) return SSB_OK;
+    if (!agg || (n > 0 && (!gate || !gout))) return fail(SSB_ERR_BAD_ARG, "ssb_shard_reduce_bwd_f32: NULL pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(gout, 4) || !aligned_to(agg, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_shard_reduce_bwd_f32: pointers must be 4-byte aligned");
+    return launch_warp_bwd<float, true>(gate, nullptr, gout, nullptr, nullptr, rows, T, nullptr, nullptr, agg,
+                                        static_cast<cudaStream_t>(stream));
+}
+
+int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse, int64_t rows, float *carry, void *stream) {
+    if (rows < 0 || n_shards < 1 || shard < 0 || shard >= n_shards)
+        return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_f32: bad shard %d of %d or rows=%lld", shard, n_shards, (long long)rows);
+    if (rows == 0) return SSB_OK;
+    if (!aggs || !carry) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_f32: NULL pointer");
+    const int block = 256;
+    const int64_t grid = (rows + block - 1) / block;
+    if (grid > 0x7fffffffLL) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_f32: too many rows");
+    ssb::shard_carry_kernel<float><<<(int)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(aggs, n_shards, shard, reverse, rows, carry);
+    return check_launch("shard_carry_kernel");
+}
+
+int ssb_device_status(int *detail) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    int word[2] = {0, 0};
+    e = cudaMemcpyFromSymbol(word, ssb::g_status_word, sizeof(word));
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    if (detail) *detail = word[1];
+    if (word[0] != 0) {
+        const int zero[2] = {0, 0};
+        (void)cudaMemcpyToSymbol(ssb::g_status_word, zero, sizeof(zero));
+        return fail(word[0], "a device-side wait ran out (kernel code %d)", word[1]);
+    }
+    return SSB_OK;
+}
+
+}  // extern "C"
