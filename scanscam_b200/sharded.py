@@ -67,9 +67,9 @@ def _gather_maps(agg: torch.Tensor, group) -> torch.Tensor:
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return agg.unsqueeze(0).contiguous()
-    gathered = torch.empty((world,) + tuple(agg.shape), dtype=agg.dtype, device=agg.device)
+    gathered = torch.empty((world * agg.shape[0],) + tuple(agg.shape[1:]), dtype=agg.dtype, device=agg.device)
     dist.all_gather_into_tensor(gathered, agg.contiguous(), group=group)
-    return gathered
+    return gathered.view((world,) + tuple(agg.shape))
 
 
 def _rank(group) -> int:

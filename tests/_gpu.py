@@ -1,0 +1,89 @@
+"""Helpers for the GPU parity tests: call the C-ABI with torch device buffers, compare with the
+CPU oracle."""
+import numpy as np
+import torch
+
+import oracle
+from scanscam_b200 import _native
+
+AUTO, WARP, TMA = _native.VARIANT_AUTO, _native.VARIANT_WARP, _native.VARIANT_TMA
+
+
+def tma_variant(tuning):
+    return TMA | (tuning << 8)
+
+
+def fwd(a, b, h_in=None, variant=AUTO):
+    """a, b: CUDA [rows, T] contiguous float32/float64 -> h (through ssb_scan_fwd_*)."""
+    lib = _native.load()
+    out = torch.empty_like(a)
+    rows, T = a.shape
+    st = _native.stream_of(a)
+    if a.dtype == torch.float32:
+        rc = lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), rows, T, _native.ptr(h_in),
+                                     variant, None, 0, st)
+    else:
+        rc = lib.ssb_scan_fwd_f64(a.data_ptr(), b.data_ptr(), out.data_ptr(), rows, T, _native.ptr(h_in), st)
+    _native.check(rc)
+    return out
+
+
+def bwd(a, h, g, c_in=None, h_prev=None, variant=AUTO):
+    lib = _native.load()
+    ga, gb = torch.empty_like(a), torch.empty_like(a)
+    rows, T = a.shape
+    st = _native.stream_of(a)
+    if a.dtype == torch.float32:
+        rc = lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
+                                     _native.ptr(c_in), _native.ptr(h_prev), variant, None, 0, st)
+    else:
+        rc = lib.ssb_scan_bwd_f64(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
+                                  _native.ptr(c_in), _native.ptr(h_prev), st)
+    _native.check(rc)
+    return ga, gb
+
+
+def cl_fwd(a, b):
+    lib = _native.load()
+    out = torch.empty_like(a)
+    N, T, C = a.shape
+    fn = lib.ssb_scan_cl_fwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_fwd_f64
+    _native.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, _native.stream_of(a)))
+    return out
+
+
+def cl_bwd(a, h, g):
+    lib = _native.load()
+    ga, gb = torch.empty_like(a), torch.empty_like(a)
+    N, T, C = a.shape
+    fn = lib.ssb_scan_cl_bwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_bwd_f64
+    _native.check(fn(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C,
+                     _native.stream_of(a)))
+    return ga, gb
+
+
+def device_ok():
+    """Synchronises and asserts that no kernel reported a timed-out wait."""
+    detail = _native.ctypes.c_int(0)
+    _native.check(_native.load().ssb_device_status(_native.ctypes.byref(detail)))
+
+
+def max_norm_err(x, ref):
+    """max|x - ref| / max|ref| : the parity metric (elementwise relative error is meaningless
+    near zero crossings, where the fp32 oracle itself is several percent from fp64)."""
+    x = x.detach().cpu().numpy() if isinstance(x, torch.Tensor) else x
+    return float(np.abs(x.astype(np.float64) - ref.astype(np.float64)).max() / (np.abs(ref).max() + 1e-300))
+
+
+def allclose_ref(x, ref, atol=1e-4, rtol=1e-5):
+    """The reference tests' own criterion (scanscam/cuda_test.py:79-80: atol=1e-4, default rtol)."""
+    x = x.detach().cpu().numpy() if isinstance(x, torch.Tensor) else x
+    return bool(np.all(np.abs(x - ref) <= atol + rtol * np.abs(ref)))
+
+
+def oracle_all(a, b, g):
+    """CPU oracle on torch CPU tensors -> numpy (h, ga, gb); bwd is fed the oracle's own h."""
+    an, bn, gn = a.numpy(), b.numpy(), g.numpy()
+    h = oracle.scan_forward(an, bn)
+    ga, gb = oracle.scan_backward(an, h, gn)
+    return h, ga, gb

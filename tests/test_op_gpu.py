@@ -1,0 +1,130 @@
+"""The Python operator layer on a GPU: scan()/Scan through autograd on both layouts, the
+wrapper names of the reference's cuda module, and the reference's error behaviour."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import _gpu  # noqa: E402
+
+import oracle  # noqa: E402
+import scanscam_b200  # noqa: E402
+from scanscam_b200 import cuda, op, sharded  # noqa: E402
+from scanscam_b200.workloads import make_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+GRID = [(32, 5), (16, 2, 5), (32, 64), (1, 1024), (32, 1024), (32, 1025), (1, 1025)]
+
+
+@pytest.mark.parametrize("shape", GRID + [(4, 8, 4096)])
+@pytest.mark.parametrize("permute", [False, True])
+def test_scan_autograd_matches_oracle(shape, permute):
+    """permute=True feeds the layouts of scanscam/cuda_test.py:28-29: x.mT.contiguous().mT."""
+    a, b, g = make_inputs("randn", shape, seed=21)
+    T = shape[-1]
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, T) for x in (a, b, g)))
+    da, db = a.cuda(), b.cuda()
+    if permute:
+        da, db = da.mT.contiguous().mT, db.mT.contiguous().mT
+    da.requires_grad_(True)
+    db.requires_grad_(True)
+    h = scanscam_b200.scan(da, db)
+    assert h.shape == da.shape
+    h.backward(g.cuda())
+    assert _gpu.allclose_ref(h.reshape(-1, T), h_ref)
+    assert _gpu.allclose_ref(db.grad.reshape(-1, T), gb_ref)
+    assert _gpu.allclose_ref(da.grad.reshape(-1, T), ga_ref)
+
+
+def test_channels_last_path_is_taken_and_correct():
+    a, b, g = make_inputs("sigmoid2", (3, 50, 200), seed=5)      # [N, C, T] logical
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, 200) for x in (a, b, g)))
+    da = a.cuda().mT.contiguous().mT.requires_grad_(True)          # dense as [N, T, C]
+    db = b.cuda().mT.contiguous().mT.requires_grad_(True)
+    assert op.is_transpose_contig(da)
+    h = scanscam_b200.scan(da, db)
+    assert op.is_transpose_contig(h)                                # stays channels-last
+    h.backward(g.cuda().mT.contiguous().mT)                         # the branch the reference gets wrong
+    assert _gpu.allclose_ref(h.reshape(-1, 200), h_ref)
+    assert _gpu.allclose_ref(db.grad.reshape(-1, 200), gb_ref)
+    assert _gpu.allclose_ref(da.grad.reshape(-1, 200), ga_ref)
+
+
+# the reference's channels-last grid, scanscam/cuda_test.py:129-163 (largest case trimmed in N)
+@pytest.mark.parametrize("shape", [(8, 4096, 512), (64, 4096, 8), (3, 107, 197), (3, 293, 283), (5, 6113, 107)])
+@pytest.mark.parametrize("cpb", [1, 32])
+def test_transposed_wrappers(shape, cpb):
+    a, b, g = make_inputs("randn", shape, seed=31)
+    an, bn, gn = a.numpy(), b.numpy(), g.numpy()
+    h_ref = oracle.scan_forward_channels_last(an, bn)
+    ga_ref, gb_ref = oracle.scan_backward_channels_last(an, h_ref, gn)
+    h = cuda.transposed_linear_scan_forward(a.cuda(), b.cuda(), cpb)
+    ga, gb = cuda.transposed_linear_scan_backward(a.cuda(), torch.from_numpy(h_ref).cuda(), g.cuda(), cpb)
+    assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(gb, gb_ref) and _gpu.allclose_ref(ga, ga_ref)
+
+
+@pytest.mark.parametrize("fn_name", ["simple_linear_scan_forward", "coalesced_linear_scan_forward",
+                                     "blocked_linear_scan_forward"])
+def test_forward_wrapper_names(fn_name):
+    a, b, _ = make_inputs("randn", (16, 2, 1025), seed=2)
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy())
+    h = getattr(cuda, fn_name)(a.cuda(), b.cuda())
+    assert h.shape == (16, 2, 1025) and _gpu.allclose_ref(h, h_ref)
+
+
+@pytest.mark.parametrize("fn_name", ["simple_linear_scan_backward", "blocked_linear_scan_backward"])
+def test_backward_wrapper_names(fn_name):
+    a, b, g = make_inputs("randn", (16, 2, 1025), seed=3)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, 1025) for x in (a, b, g)))
+    ga, gb = getattr(cuda, fn_name)(a.cuda(), torch.from_numpy(h_ref).cuda().reshape(a.shape), g.cuda())
+    assert ga.shape == a.shape
+    assert _gpu.allclose_ref(ga.reshape(-1, 1025), ga_ref) and _gpu.allclose_ref(gb.reshape(-1, 1025), gb_ref)
+
+
+def test_gradcheck_fp64():
+    a = torch.rand(3, 37, dtype=torch.float64, device="cuda", requires_grad=True)
+    b = torch.randn(3, 37, dtype=torch.float64, device="cuda", requires_grad=True)
+    assert torch.autograd.gradcheck(scanscam_b200.scan, (a, b), eps=1e-6, atol=1e-6)
+
+
+def test_error_behaviour_matches_the_reference():
+    x = torch.rand(4, 8, device="cuda")
+    with pytest.raises(AssertionError):
+        scanscam_b200.scan(x, torch.rand(4, 9, device="cuda"))
+    with pytest.raises(AssertionError):
+        scanscam_b200.scan(torch.rand(8, device="cuda"), torch.rand(8, device="cuda"))
+    with pytest.raises(NotImplementedError, match="not implemented for 'Half'"):
+        scanscam_b200.scan(x.half(), x.half())
+    import scanscam_ext
+
+    with pytest.raises(RuntimeError, match="contiguous"):
+        scanscam_ext.blocked_linear_scan(x.t(), x.t(), torch.empty(8, 4, device="cuda"))
+    with pytest.raises(RuntimeError, match="same dtype"):
+        scanscam_ext.blocked_linear_scan(x, x.double(), torch.empty_like(x))
+
+
+def test_runs_on_the_current_stream():
+    a, b, _ = make_inputs("sigmoid2", (64, 4096), seed=8)
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy())
+    side = torch.cuda.Stream()
+    da, db = a.cuda(), b.cuda()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        h = scanscam_b200.scan(da, db)
+    side.synchronize()
+    assert _gpu.allclose_ref(h, h_ref)
+
+
+def test_sequence_parallel_module_single_rank():
+    """Without a process group the sequence-parallel entry point is the plain scan."""
+    a, b, g = make_inputs("nearunit", (8, 8192), seed=13)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    h = sharded.scan_sequence_parallel(da, db)
+    h.backward(g.cuda())
+    assert _gpu.max_norm_err(h, h_ref) < 1e-4
+    assert _gpu.max_norm_err(db.grad, gb_ref) < 1e-4 and _gpu.max_norm_err(da.grad, ga_ref) < 1e-4

@@ -1,0 +1,242 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C-ABI (ctypes + raw device
+pointers).  Tolerances: the reference tests' allclose(atol=1e-4, rtol=1e-5) on the reference's
+shape grid, and max-norm relative error <= 1e-4 on the benchmark configurations (observed
+errors are ~1e-6; anything near 1e-5 would already mean a bug, not reassociation)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import _gpu  # noqa: E402
+from _gpu import AUTO, TMA, WARP  # noqa: E402
+
+import oracle  # noqa: E402
+from scanscam_b200 import _native  # noqa: E402
+from scanscam_b200.workloads import WORKLOADS, make_inputs, workload_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "scan_golden.npz"))
+GOLDEN_ROWS = sorted({k.split("/")[0] for k in GOLDEN.files if not k.startswith("cl_")})
+GOLDEN_CL = sorted({k.split("/")[0] for k in GOLDEN.files if k.startswith("cl_")})
+
+# the reference's own shape grids (scanscam/cuda_test.py:19-126)
+REF_SHAPES = [(32, 5), (16, 2, 5), (32, 64), (32, 128), (32, 256), (32, 512), (32, 513), (1, 1024), (32, 1024),
+              (32, 1025), (1, 1025), (32, 4095), (32, 4096), (32, 4097), (32, 4100), (32, 16384), (32, 16388)]
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda() if isinstance(x, np.ndarray) else x.cuda()
+
+
+def variants_for(T, dtype=torch.float32):
+    v = [AUTO, WARP]
+    if dtype == torch.float32 and T % 32 == 0:
+        v += [TMA, _gpu.tma_variant(1), _gpu.tma_variant(6)]
+    return v
+
+
+@pytest.mark.parametrize("name", GOLDEN_ROWS)
+def test_golden_vectors(name):
+    c = {k: GOLDEN[f"{name}/{k}"] for k in ("a", "b", "g", "h", "ga", "gb")}
+    shape = c["a"].shape
+    T = shape[-1]
+    a, b, g, h_ref = (dev(c[k].reshape(-1, T)) for k in ("a", "b", "g", "h"))
+    for variant in variants_for(T, a.dtype):
+        h = _gpu.fwd(a, b, variant=variant)
+        ga, gb = _gpu.bwd(a, h_ref, g, variant=variant)
+        for got, key in ((h, "h"), (ga, "ga"), (gb, "gb")):
+            ref = c[key].reshape(-1, T)
+            assert _gpu.allclose_ref(got, ref), (name, variant, key, _gpu.max_norm_err(got, ref))
+            assert _gpu.max_norm_err(got, ref) < TOL
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("name", GOLDEN_CL)
+def test_golden_vectors_channels_last(name):
+    c = {k: GOLDEN[f"{name}/{k}"] for k in ("a", "b", "g", "h", "ga", "gb")}
+    a, b, g, h_ref = (dev(c[k]) for k in ("a", "b", "g", "h"))
+    h = _gpu.cl_fwd(a, b)
+    ga, gb = _gpu.cl_bwd(a, h_ref, g)
+    for got, key in ((h, "h"), (ga, "ga"), (gb, "gb")):
+        assert _gpu.allclose_ref(got, c[key]), (name, key, _gpu.max_norm_err(got, c[key]))
+
+
+@pytest.mark.parametrize("shape", REF_SHAPES)
+@pytest.mark.parametrize("gates", ["randn", "sigmoid2"])
+def test_reference_shape_grid(shape, gates):
+    a, b, g = make_inputs(gates, shape, seed=hash(shape) % 1000)
+    T = shape[-1]
+    a2, b2, g2 = (x.reshape(-1, T) for x in (a, b, g))
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a2, b2, g2)
+    da, db, dg, dh = a2.cuda(), b2.cuda(), g2.cuda(), dev(h_ref)
+    for variant in variants_for(T):
+        h = _gpu.fwd(da, db, variant=variant)
+        ga, gb = _gpu.bwd(da, dh, dg, variant=variant)
+        assert _gpu.allclose_ref(h, h_ref), (variant, _gpu.max_norm_err(h, h_ref))
+        assert _gpu.allclose_ref(gb, gb_ref), (variant, _gpu.max_norm_err(gb, gb_ref))
+        assert _gpu.allclose_ref(ga, ga_ref), (variant, _gpu.max_norm_err(ga, ga_ref))
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("shape", [(3, 7), (5, 64), (2, 1000), (9, 2049), (2, 4098)])
+def test_fp64(shape):
+    a, b, g = make_inputs("randn", shape, seed=7, dtype=torch.float64)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    h = _gpu.fwd(a.cuda(), b.cuda())
+    ga, gb = _gpu.bwd(a.cuda(), dev(h_ref), g.cuda())
+    for got, ref in ((h, h_ref), (ga, ga_ref), (gb, gb_ref)):
+        assert _gpu.max_norm_err(got, ref) < 1e-12
+
+
+def test_unaligned_base_pointers():
+    """Views that start 4 bytes into an allocation: the 16-byte fast paths must not be taken."""
+    a, b, g = make_inputs("sigmoid2", (8, 1028), seed=4)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+
+    def shifted(x):
+        buf = torch.empty(x.numel() + 1, device="cuda")
+        view = buf[1:].view(x.shape)
+        view.copy_(x)
+        assert view.data_ptr() % 16 == 4
+        return view
+
+    da, db, dg, dh = shifted(a), shifted(b), shifted(g), shifted(torch.from_numpy(h_ref))
+    h = _gpu.fwd(da, db)
+    ga, gb = _gpu.bwd(da, dh, dg)
+    assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
+    with pytest.raises(_native.NativeError) as err:
+        _gpu.fwd(da, db, variant=TMA)
+    assert err.value.status == _native.ERR_UNSUPPORTED
+
+
+def test_edge_shapes_and_errors():
+    one = torch.full((3, 1), 2.0, device="cuda")
+    assert torch.equal(_gpu.fwd(one, one), one)
+    ga, gb = _gpu.bwd(one, one, one)
+    assert torch.equal(gb, one) and torch.equal(ga, torch.zeros_like(one))
+    empty = torch.empty((4, 0), device="cuda")
+    assert _gpu.fwd(empty, empty).shape == (4, 0)
+    a = torch.rand(4, 100, device="cuda")
+    with pytest.raises(_native.NativeError) as err:
+        _gpu.fwd(a, a, variant=TMA)  # T % 32 != 0
+    assert err.value.status == _native.ERR_UNSUPPORTED
+    with pytest.raises(_native.NativeError):
+        _gpu.fwd(a, a, variant=99)
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("gates,shape", [("sigmoid2", (64, 4096)), ("resets", (40, 2048)), ("nearunit", (4, 65536))])
+@pytest.mark.parametrize("variant", [WARP, TMA])
+def test_shard_carries(gates, shape, variant):
+    """A call with carry-in must continue a scan exactly where another call stopped."""
+    a, b, g = make_inputs(gates, shape, seed=9)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    T = shape[1]
+    cut = T // 2
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    left = [x[:, :cut].contiguous() for x in (da, db, dg, dh)]
+    right = [x[:, cut:].contiguous() for x in (da, db, dg, dh)]
+    h_l = _gpu.fwd(left[0], left[1], variant=variant)
+    h_r = _gpu.fwd(right[0], right[1], h_in=h_l[:, -1].contiguous(), variant=variant)
+    assert _gpu.max_norm_err(torch.cat([h_l, h_r], 1), h_ref) < TOL
+    ga_r, gb_r = _gpu.bwd(right[0], right[3], right[2], h_prev=left[3][:, -1].contiguous(), variant=variant)
+    c_in = (right[0][:, 0] * gb_r[:, 0]).contiguous()
+    ga_l, gb_l = _gpu.bwd(left[0], left[3], left[2], c_in=c_in, variant=variant)
+    assert _gpu.max_norm_err(torch.cat([gb_l, gb_r], 1), gb_ref) < TOL
+    assert _gpu.max_norm_err(torch.cat([ga_l, ga_r], 1), ga_ref) < TOL
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("n_shards", [2, 8])
+def test_virtual_t_shards_on_one_gpu(n_shards):
+    """reduce -> (gather) -> carry -> scan-with-carry, all shards on one device, vs. unsharded."""
+    lib = _native.load()
+    rows, T = 48, 4096 * n_shards
+    a, b, g = make_inputs("nearunit", (rows, T), seed=12)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    step = T // n_shards
+    parts = [[x[:, s * step:(s + 1) * step].contiguous() for x in (da, db, dg, dh)] for s in range(n_shards)]
+    st = _native.stream_of(da)
+    fmaps = torch.empty(n_shards, rows, 2, device="cuda")
+    bmaps = torch.empty(n_shards, rows, 2, device="cuda")
+    for s, (pa, pb, pg, _) in enumerate(parts):
+        _native.check(lib.ssb_shard_reduce_fwd_f32(pa.data_ptr(), pb.data_ptr(), fmaps[s].data_ptr(), rows, step, st))
+        _native.check(lib.ssb_shard_reduce_bwd_f32(pa.data_ptr(), pg.data_ptr(), bmaps[s].data_ptr(), rows, step, st))
+    hs, gas, gbs = [], [], []
+    for s, (pa, pb, pg, ph) in enumerate(parts):
+        h_in = torch.empty(rows, device="cuda")
+        c_in = torch.empty(rows, device="cuda")
+        _native.check(lib.ssb_shard_carry_f32(fmaps.data_ptr(), n_shards, s, 0, rows, h_in.data_ptr(), st))
+        _native.check(lib.ssb_shard_carry_f32(bmaps.data_ptr(), n_shards, s, 1, rows, c_in.data_ptr(), st))
+        hs.append(_gpu.fwd(pa, pb, h_in=h_in))
+        ga, gb = _gpu.bwd(pa, ph, pg, c_in=c_in, h_prev=h_in)
+        gas.append(ga)
+        gbs.append(gb)
+    assert _gpu.max_norm_err(torch.cat(hs, 1), h_ref) < TOL
+    assert _gpu.max_norm_err(torch.cat(gbs, 1), gb_ref) < TOL
+    assert _gpu.max_norm_err(torch.cat(gas, 1), ga_ref) < TOL
+    # the maps themselves: A is the product of the shard's gates, B its zero-started end value
+    A_ref = a[:, :step].double().prod(dim=1)
+    np.testing.assert_allclose(fmaps[0, :, 0].cpu().double().numpy(), A_ref.numpy(), rtol=1e-4)
+    np.testing.assert_allclose(fmaps[0, :, 1].cpu().numpy(), h_ref[:, step - 1], rtol=1e-5, atol=1e-6)
+    _gpu.device_ok()
+
+
+# ---- benchmark configurations ------------------------------------------------------------
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg5"])
+def test_benchmark_configs_against_oracle(name):
+    """Full-size parity: cfg1 (the CPU-runnable case), cfg2 (headline), cfg5 (exact-zero gates)."""
+    w = WORKLOADS[name]
+    a, b, g = (x.reshape(w.rows, w.steps) for x in workload_inputs(name))
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    for variant in (AUTO, WARP):
+        h = _gpu.fwd(da, db, variant=variant)
+        assert _gpu.max_norm_err(h, h_ref) < TOL
+        ga, gb = _gpu.bwd(da, dev(h_ref), dg, variant=variant)       # isolates the backward
+        assert _gpu.max_norm_err(gb, gb_ref) < TOL and _gpu.max_norm_err(ga, ga_ref) < TOL
+        ga2, gb2 = _gpu.bwd(da, h, dg, variant=variant)              # end to end, kernel's own h
+        assert _gpu.max_norm_err(ga2, ga_ref) < TOL
+        del h, ga, gb, ga2, gb2
+    _gpu.device_ok()
+
+
+def test_cfg4_wide_short_rows_sampled():
+    """cfg4 at full size on the GPU; the oracle checks a strided sample of rows."""
+    w = WORKLOADS["cfg4"]
+    a, b, g = (x.reshape(w.rows, w.steps) for x in workload_inputs("cfg4"))
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    h = _gpu.fwd(da, db)
+    ga, gb = _gpu.bwd(da, h, dg)
+    idx = torch.arange(0, w.rows, 37)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a[idx].contiguous(), b[idx].contiguous(), g[idx].contiguous())
+    assert _gpu.max_norm_err(h[idx.cuda()], h_ref) < TOL
+    assert _gpu.max_norm_err(gb[idx.cuda()], gb_ref) < TOL and _gpu.max_norm_err(ga[idx.cuda()], ga_ref) < TOL
+    _gpu.device_ok()
+
+
+def test_cfg3_long_context_properties():
+    """cfg3's sequence length (2**20) and gate distribution on a slice of its rows: oracle parity
+    on those rows, plus two size-independent properties -- linearity in the value input and
+    agreement between the T-sharded composition and the single call."""
+    T = WORKLOADS["cfg3"].steps
+    rows = 16
+    a, b, g = make_inputs("nearunit", (rows, T), seed=0)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    for variant in (TMA, WARP):
+        h = _gpu.fwd(da, db, variant=variant)
+        ga, gb = _gpu.bwd(da, dev(h_ref), dg, variant=variant)
+        assert _gpu.max_norm_err(h, h_ref) < TOL
+        assert _gpu.max_norm_err(gb, gb_ref) < TOL and _gpu.max_norm_err(ga, ga_ref) < TOL
+    # linearity: scan(a, b + 2*g) == scan(a, b) + 2*scan(a, g)
+    lhs = _gpu.fwd(da, (db + 2 * dg).contiguous())
+    rhs = _gpu.fwd(da, db) + 2 * _gpu.fwd(da, dg)
+    assert float((lhs - rhs).abs().max() / rhs.abs().max()) < 1e-5
+    _gpu.device_ok()
