@@ -15,6 +15,7 @@
 
 #include "scan_cl.cuh"
 #include "scan_common.cuh"
+#include "scan_flat.cuh"
 #include "scan_tma.cuh"
 #include "scan_warp.cuh"
 
@@ -184,9 +185,89 @@ int launch_tma_bwd(const float *gate, const float *h, const float *gout, float *
     return check_launch("tma_rows_bwd_kernel");
 }
 
+// ------------------------------------------------------------------------------------
+// Flat streaming family
+// ------------------------------------------------------------------------------------
+bool flat_eligible(int64_t rows, int64_t T) {
+    return T % 4 == 0 && T >= 4 && rows * (T / 4) < (int64_t)1 << 40;
+}
+
+// TAG makes one instantiation (and one cached occupancy) per kernel instantiation.
+thread_local int t_grid_per_sm = 0;  // tuning override for this call: CTAs per SM (0 = as many as fit)
+
+template <int TAG, typename K>
+int flat_grid(K kern, int threads, int64_t units) {
+    static std::atomic<int> cached_occ{0};
+    int occ = cached_occ.load(std::memory_order_relaxed);
+    if (occ == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, 0) != cudaSuccess || occ <= 0) {
+            (void)cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ.store(occ, std::memory_order_relaxed);
+    }
+    const int per_sm = (t_grid_per_sm > 0 && t_grid_per_sm < occ) ? t_grid_per_sm : occ;
+    const int64_t cap = (int64_t)sm_count() * per_sm;
+    return (int)(units < cap ? (units > 0 ? units : 1) : cap);
+}
+
+int64_t flat_units(int64_t rows, int64_t T4, int cap) {
+    if (T4 > cap) return rows;
+    const int64_t rps = cap / T4;
+    return (rows + rps - 1) / rps;
+}
+
+template <int THREADS, int U>
+int launch_flat_fwd(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                    const float *h_in, cudaStream_t st) {
+    auto kern = ssb::flat::flat_fwd_kernel<THREADS, U>;
+    const int grid = flat_grid<THREADS * 64 + U * 2>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
+    kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(value),
+                                   reinterpret_cast<float4 *>(out), rows, T / 4, h_in);
+    return check_launch("flat_fwd_kernel");
+}
+
+template <int THREADS, int U>
+int launch_flat_bwd(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
+                    int64_t rows, int64_t T, const float *c_in, const float *h_prev, cudaStream_t st) {
+    auto kern = ssb::flat::flat_bwd_kernel<THREADS, U>;
+    const int grid = flat_grid<THREADS * 64 + U * 2 + 1>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
+    kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(h),
+                                   reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(ggate),
+                                   reinterpret_cast<float4 *>(gvalue), rows, T / 4, c_in, h_prev);
+    return check_launch("flat_bwd_kernel");
+}
+
+// Tuning table of the flat family: id -> (threads per CTA, float4s per thread).
+#define SSB_FLAT_CONFIGS(X) \
+    X(0, 256, 4) X(1, 512, 2) X(2, 1024, 1) X(3, 256, 2) X(4, 128, 4) X(5, 512, 1) X(6, 128, 8) \
+    X(7, 64, 16) X(8, 64, 8) X(9, 256, 1) X(10, 128, 2) X(11, 64, 4) X(12, 128, 1) X(13, 32, 16)
+
+int dispatch_flat_fwd(int tuning, const float *gate, const float *value, float *out, int64_t rows,
+                      int64_t T, const float *h_in, cudaStream_t st) {
+    switch (tuning) {
+#define X(ID, TH, UU) case ID: return launch_flat_fwd<TH, UU>(gate, value, out, rows, T, h_in, st);
+        SSB_FLAT_CONFIGS(X)
+#undef X
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown forward flat tuning id %d", tuning);
+    }
+}
+
+int dispatch_flat_bwd(int tuning, const float *gate, const float *h, const float *gout, float *ggate,
+                      float *gvalue, int64_t rows, int64_t T, const float *c_in, const float *h_prev,
+                      cudaStream_t st) {
+    switch (tuning) {
+#define X(ID, TH, UU) case ID: return launch_flat_bwd<TH, UU>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        SSB_FLAT_CONFIGS(X)
+#undef X
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown backward flat tuning id %d", tuning);
+    }
+}
+
 // `variant` carries the family in its low byte and a tuning id in bits 8..15 (0 = default).
 int family_of(int variant) { return variant & 0xff; }
 int tuning_of(int variant) { return (variant >> 8) & 0xff; }
+int grid_per_sm_of(int variant) { return (variant >> 16) & 0xff; }
 
 int dispatch_tma_fwd(int tuning, const float *gate, const float *value, float *out, int64_t rows,
                      int64_t T, const float *h_in, cudaStream_t st) {
@@ -201,6 +282,8 @@ int dispatch_tma_fwd(int tuning, const float *gate, const float *value, float *o
         case 7: return launch_tma_fwd<32, 4, 4>(gate, value, out, rows, T, h_in, st);
         case 8: return launch_tma_fwd<32, 2, 6>(gate, value, out, rows, T, h_in, st);
         case 9: return launch_tma_fwd<16, 4, 6>(gate, value, out, rows, T, h_in, st);
+        case 10: return launch_tma_fwd<16, 2, 16>(gate, value, out, rows, T, h_in, st);
+        case 11: return launch_tma_fwd<16, 3, 12>(gate, value, out, rows, T, h_in, st);
         default: return fail(SSB_ERR_UNSUPPORTED, "unknown forward TMA tuning id %d", tuning);
     }
 }
@@ -218,13 +301,23 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
         case 6: return launch_tma_bwd<32, 2, 5>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case 7: return launch_tma_bwd<32, 3, 4>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case 8: return launch_tma_bwd<16, 3, 6>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 10: return launch_tma_bwd<16, 2, 11>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 11: return launch_tma_bwd<16, 2, 12>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         default: return fail(SSB_ERR_UNSUPPORTED, "unknown backward TMA tuning id %d", tuning);
     }
 }
 
-int pick_family(int64_t rows, int64_t T, bool all_aligned16) {
-    (void)rows;
-    if (all_aligned16 && tma_eligible(rows, T) && T >= 256) return SSB_VARIANT_TMA;
+// Default kernel choice, from sweeps on B200 over T = 64 .. 4M at 268 MB per tensor:
+//   * aligned fp32 with T % 4 == 0 -> the flat family.  128 threads x 8 float4s (16 KB spans,
+//     4 CTAs per SM) is the best or within 3 % of the best forward for every T; the backward
+//     prefers it while rows fit in a span and 256 threads x 1 float4 once rows are longer.
+//   * anything else (odd T, unaligned views) -> one warp per row.
+// The TMA family is within a few percent of these on T >= 256 and is reachable by pinning it.
+int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16) {
+    if (all_aligned16 && flat_eligible(rows, T)) {
+        if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);
+        return SSB_VARIANT_FLAT | (6 << 8);
+    }
     return SSB_VARIANT_WARP;
 }
 
@@ -267,8 +360,8 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
         return fail(SSB_ERR_ALIGNMENT, "ssb_scan_fwd_f32: pointers must be 4-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
-    int family = family_of(variant);
-    if (family == SSB_VARIANT_AUTO) family = pick_family(rows, T, al16);
+    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(false, rows, T, al16);
+    const int family = family_of(variant);
     switch (family) {
         case SSB_VARIANT_WARP:
             return launch_warp_fwd<float, false>(gate, value, out, rows, T, h_in, nullptr, st);
@@ -276,6 +369,11 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA forward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             return dispatch_tma_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
+        case SSB_VARIANT_FLAT:
+            if (!al16 || !flat_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "flat forward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return dispatch_flat_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
         default:
             return fail(SSB_ERR_UNSUPPORTED, "forward variant %d is not available", variant);
     }
@@ -313,8 +411,8 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                       aligned_to(ggate, 16) && aligned_to(gvalue, 16);
-    int family = family_of(variant);
-    if (family == SSB_VARIANT_AUTO) family = pick_family(rows, T, al16);
+    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(true, rows, T, al16);
+    const int family = family_of(variant);
     switch (family) {
         case SSB_VARIANT_WARP:
             return launch_warp_bwd<float, false>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr, st);
@@ -322,6 +420,11 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA backward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             return dispatch_tma_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case SSB_VARIANT_FLAT:
+            if (!al16 || !flat_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "flat backward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return dispatch_flat_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         default:
             return fail(SSB_ERR_UNSUPPORTED, "backward variant %d is not available", variant);
     }

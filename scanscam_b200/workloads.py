@@ -40,6 +40,7 @@ WORKLOADS = {
     "cfg2": Workload("cfg2", (8, 2048, 4096), "sigmoid2", "rows", "training-size layer (headline)"),
     "cfg3": Workload("cfg3", (1, 1024, 1048576), "nearunit", "T", "long-context stress, near-unit gates"),
     "cfg4": Workload("cfg4", (64, 8192, 512), "sigmoid0", "rows", "wide, short sequences"),
+    "cfg2q": Workload("cfg2q", (2, 2048, 4096), "sigmoid2", "rows", "a quarter of cfg2: small case for profiler captures"),
     "cfg5": Workload("cfg5", (16, 4096, 2048), "resets", "rows", "mixed gates with exact zeros"),
 }
 

@@ -6,11 +6,15 @@ import torch
 import oracle
 from scanscam_b200 import _native
 
-AUTO, WARP, TMA = _native.VARIANT_AUTO, _native.VARIANT_WARP, _native.VARIANT_TMA
+AUTO, WARP, TMA, FLAT = _native.VARIANT_AUTO, _native.VARIANT_WARP, _native.VARIANT_TMA, _native.VARIANT_FLAT
 
 
 def tma_variant(tuning):
     return TMA | (tuning << 8)
+
+
+def flat_variant(tuning):
+    return FLAT | (tuning << 8)
 
 
 def fwd(a, b, h_in=None, variant=AUTO):

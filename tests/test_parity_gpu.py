@@ -11,7 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import _gpu  # noqa: E402
-from _gpu import AUTO, TMA, WARP  # noqa: E402
+from _gpu import AUTO, FLAT, TMA, WARP  # noqa: E402
 
 import oracle  # noqa: E402
 from scanscam_b200 import _native  # noqa: E402
@@ -37,6 +37,8 @@ def variants_for(T, dtype=torch.float32):
     v = [AUTO, WARP]
     if dtype == torch.float32 and T % 32 == 0:
         v += [TMA, _gpu.tma_variant(1), _gpu.tma_variant(6)]
+    if dtype == torch.float32 and T % 4 == 0:
+        v += [_gpu.flat_variant(t) for t in range(7)]
     return v
 
 
@@ -80,6 +82,30 @@ def test_reference_shape_grid(shape, gates):
         assert _gpu.allclose_ref(h, h_ref), (variant, _gpu.max_norm_err(h, h_ref))
         assert _gpu.allclose_ref(gb, gb_ref), (variant, _gpu.max_norm_err(gb, gb_ref))
         assert _gpu.allclose_ref(ga, ga_ref), (variant, _gpu.max_norm_err(ga, ga_ref))
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("shape", [(1000, 4), (77, 100), (13, 1028), (5, 5000), (3, 4092), (2, 8196), (300, 36)])
+def test_row_packing_shapes(shape):
+    """T % 4 == 0 but not a divisor of the 4096-element span: whole rows are packed per span,
+    long rows are walked in pieces with a ragged last piece."""
+    a, b, g = make_inputs("randn", shape, seed=17)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    h_in = torch.randn(shape[0], device="cuda")
+    c_in = torch.randn(shape[0], device="cuda")
+    h_ref2 = oracle.scan_forward(a.numpy(), b.numpy(), h_in=h_in.cpu().numpy())
+    ga_ref2, gb_ref2 = oracle.scan_backward(a.numpy(), h_ref, g.numpy(), gb_in=c_in.cpu().numpy(),
+                                            h_prev=h_in.cpu().numpy())
+    for variant in variants_for(shape[1]):
+        h = _gpu.fwd(da, db, variant=variant)
+        ga, gb = _gpu.bwd(da, dh, dg, variant=variant)
+        assert _gpu.allclose_ref(h, h_ref), (variant, _gpu.max_norm_err(h, h_ref))
+        assert _gpu.allclose_ref(gb, gb_ref) and _gpu.allclose_ref(ga, ga_ref), variant
+        h2 = _gpu.fwd(da, db, h_in=h_in, variant=variant)
+        assert _gpu.allclose_ref(h2, h_ref2), (variant, "carry-in")
+        ga2, gb2 = _gpu.bwd(da, dh, dg, c_in=c_in, h_prev=h_in, variant=variant)
+        assert _gpu.allclose_ref(gb2, gb_ref2) and _gpu.allclose_ref(ga2, ga_ref2), (variant, "bwd carries")
     _gpu.device_ok()
 
 
@@ -131,7 +157,7 @@ def test_edge_shapes_and_errors():
 
 
 @pytest.mark.parametrize("gates,shape", [("sigmoid2", (64, 4096)), ("resets", (40, 2048)), ("nearunit", (4, 65536))])
-@pytest.mark.parametrize("variant", [WARP, TMA])
+@pytest.mark.parametrize("variant", [WARP, TMA, FLAT, _gpu.flat_variant(2), _gpu.flat_variant(3)])
 def test_shard_carries(gates, shape, variant):
     """A call with carry-in must continue a scan exactly where another call stopped."""
     a, b, g = make_inputs(gates, shape, seed=9)
@@ -196,7 +222,7 @@ def test_benchmark_configs_against_oracle(name):
     a, b, g = (x.reshape(w.rows, w.steps) for x in workload_inputs(name))
     h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
     da, db, dg = a.cuda(), b.cuda(), g.cuda()
-    for variant in (AUTO, WARP):
+    for variant in (AUTO, WARP, TMA, FLAT):
         h = _gpu.fwd(da, db, variant=variant)
         assert _gpu.max_norm_err(h, h_ref) < TOL
         ga, gb = _gpu.bwd(da, dev(h_ref), dg, variant=variant)       # isolates the backward
@@ -230,7 +256,7 @@ def test_cfg3_long_context_properties():
     a, b, g = make_inputs("nearunit", (rows, T), seed=0)
     h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
     da, db, dg = a.cuda(), b.cuda(), g.cuda()
-    for variant in (TMA, WARP):
+    for variant in (TMA, WARP, FLAT, _gpu.flat_variant(3)):
         h = _gpu.fwd(da, db, variant=variant)
         ga, gb = _gpu.bwd(da, dev(h_ref), dg, variant=variant)
         assert _gpu.max_norm_err(h, h_ref) < TOL
