@@ -40,10 +40,11 @@ if REPO not in sys.path:
 METRIC = "scan Gelem/s fwd+bwd fp32"
 BYTES_FWD, BYTES_BWD = 12, 20  # algorithmic bytes per element: read a,b write h | read a,h,g write ga,gb
 
-# DRAM traffic per element of the backward kernel measured with ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum over one launch, divided by the elements of that launch); see profiles/.
-# None until a capture exists for the kernel variant in use.
-NCU_BWD_TRAFFIC_BYTES_PER_ELEM = None
+# DRAM traffic per element of the backward kernel measured with ncu on the full cfg2 launch
+# (dram__bytes_read.sum + dram__bytes_write.sum = 805.4 MB + 489.7 MB over 67 108 864 elements; the
+# reads equal the algorithmic 12 B/element, the writes fall short of 8 B/element because the last
+# ~45 MB of results are still in L2 when the kernel ends).  See profiles/flat_kernels_cfg2.md.
+NCU_BWD_TRAFFIC_BYTES_PER_ELEM = 19.30
 
 
 def parse_args():
@@ -298,34 +299,43 @@ def run_gpu_arm(args, workload):
         step()
     barrier()
 
+    # ---- timed region: exactly K steps between barrier+synchronize, device-timed --------------
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    ev[0].record(stream)
-    for i in range(args.steps):
-        if t_sharded:
-            step()
-            ev[2 * i + 1].record(stream)
-        else:
-            fwd()
-            ev[2 * i + 1].record(stream)
-            bwd()
-        ev[2 * i + 2].record(stream)
+    t_begin.record(stream)
+    for _ in range(args.steps):
+        step()
+    t_end.record(stream)
     barrier()
-    total_ms = ev[0].elapsed_time(ev[2 * args.steps])
+    total_ms = t_begin.elapsed_time(t_end)
     sampler_how = "NVML samples every 20 ms during the timed region"
     if total_ms < 600.0:
         # too short for a meaningful clock record: keep sampling over a further 0.6 s of the same steps
-        t_end = time.perf_counter() + 0.6
-        while time.perf_counter() < t_end:
+        t_stop = time.perf_counter() + 0.6
+        while time.perf_counter() < t_stop:
             for _ in range(20):
                 step()
             torch.cuda.synchronize()
         sampler_how = "NVML samples every 20 ms during the timed region and a 0.6 s continuation of the same steps"
     sampler.stop()
-    fwd_ms = [ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)]
-    bwd_ms = [ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)]
+
+    # ---- per-kernel durations for the roofline: the same K steps again, an event after every
+    # launch (kept out of the region above, where the extra event records would cost ~1 %) -----
+    fwd_ms, bwd_ms = [0.0], [0.0]
+    if not t_sharded:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+        barrier()
+        ev[0].record(stream)
+        for i in range(args.steps):
+            fwd()
+            ev[2 * i + 1].record(stream)
+            bwd()
+            ev[2 * i + 2].record(stream)
+        barrier()
+        fwd_ms = [ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)]
+        bwd_ms = [ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)]
 
     detail = _native.ctypes.c_int(0)
     _native.check(lib.ssb_device_status(_native.ctypes.byref(detail)))
@@ -340,18 +350,14 @@ def run_gpu_arm(args, workload):
     # ---- end to end through the public operator, host buffers -------------------------------
     e2e = None
     if not args.no_e2e and not t_sharded:
+        from scanscam_b200.host import HostScanPipeline
+
         pin = [x.pin_memory() for x in (a_cpu, b_cpu, g_cpu)]
-        outs = [torch.empty_like(x).pin_memory() for x in (a_cpu, b_cpu, g_cpu)]
+        outs = tuple(torch.empty_like(x).pin_memory() for x in (a_cpu, b_cpu, g_cpu))
+        pipe = HostScanPipeline(rows, T_local, chunks=16)
 
         def e2e_step():
-            da = pin[0].to("cuda", non_blocking=True).requires_grad_(True)
-            db = pin[1].to("cuda", non_blocking=True).requires_grad_(True)
-            dg = pin[2].to("cuda", non_blocking=True)
-            hh = scanscam_b200.scan(da, db)
-            hh.backward(dg)
-            outs[0].copy_(hh.detach(), non_blocking=True)
-            outs[1].copy_(da.grad, non_blocking=True)
-            outs[2].copy_(db.grad, non_blocking=True)
+            pipe.run(pin[0], pin[1], pin[2], outs)
 
         e2e_step()
         barrier()
@@ -365,11 +371,17 @@ def run_gpu_arm(args, workload):
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = float(te.cpu()) / args.e2e_steps
+        # spot-check the host results of the last step against the device-resident run
+        torch.cuda.synchronize()
+        fwd()
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0][:64], h[:64].cpu()), "end-to-end pipeline result differs from the resident run"
         e2e = {"value": n_local * world / (e2e_ms * 1e-3) / 1e9, "unit": "Gelem/s",
                "h2d_bytes_per_step": 3 * 4 * n_local, "d2h_bytes_per_step": 3 * 4 * n_local,
                "ms_per_step": e2e_ms, "steps": args.e2e_steps,
-               "api": "scanscam_b200.scan(gate, value) + .backward(grad) on tensors copied from pinned host memory; "
-                      "h, grad_gate, grad_value copied back to pinned host memory"}
+               "api": "scanscam_b200.host.HostScanPipeline.run(gate, value, grad): pinned host tensors in, "
+                      "h / grad_gate / grad_value written to pinned host tensors; 16 row chunks, copies in both "
+                      "directions overlapped with the kernels on three streams"}
 
     if rank != 0:
         if world > 1:

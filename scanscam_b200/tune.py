@@ -1,0 +1,103 @@
+"""Kernel-variant sweep: times every kernel family / tuning id on given shapes.
+
+    python -m scanscam_b200.tune cfg2,cfg5,1024x262144 [--iters 30] [--families warp,flat,tma]
+
+For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
+``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
+milliseconds and as algorithmic GB/s (12 B/element forward, 20 B/element backward).  This is
+how the default choices in ``pick_variant`` (csrc/scanscam_b200.cu) were made.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import _native
+from .workloads import WORKLOADS
+
+FLAT_IDS = range(14)                 # SSB_FLAT_CONFIGS in csrc/scanscam_b200.cu
+TMA_IDS = (0, 1, 5, 6, 8, 10)
+
+
+def variants(families):
+    out = []
+    if "warp" in families:
+        out.append(("warp", _native.VARIANT_WARP))
+    if "flat" in families:
+        out += [(f"flat{t}", _native.VARIANT_FLAT | (t << 8)) for t in FLAT_IDS]
+    if "tma" in families:
+        out += [(f"tma{t}", _native.VARIANT_TMA | (t << 8)) for t in TMA_IDS]
+    return out
+
+
+def time_variant(lib, rows, T, variant, tensors, iters):
+    a, b, g, h, ga, gb = tensors
+    st = torch.cuda.current_stream().cuda_stream
+
+    def fwd():
+        return lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, variant, None, 0, st)
+
+    def bwd():
+        return lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
+                                       None, None, variant, None, 0, st)
+
+    res = {}
+    for kind, fn, nbytes in (("fwd", fwd, 12), ("bwd", bwd, 20)):
+        rc = fn()
+        if rc != _native.OK:
+            res[kind] = None  # variant does not support this shape
+            continue
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / iters)
+        res[kind] = {"ms": best, "GBps": nbytes * rows * T / best / 1e6}
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("shapes")
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--families", default="warp,flat,tma")
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    lib = _native.load()
+    results = {}
+    for name in args.shapes.split(","):
+        if name in WORKLOADS:
+            rows, T = WORKLOADS[name].rows, WORKLOADS[name].steps
+        else:
+            rows, T = (int(v) for v in name.lower().split("x"))
+        a = torch.rand(rows, T, device="cuda") * 0.2 + 0.8
+        tensors = [a, torch.randn_like(a), torch.randn_like(a)] + [torch.empty_like(a) for _ in range(3)]
+        print(f"# {name}: rows={rows} T={T} ({rows * T * 4 / 1e6:.0f} MB per tensor)")
+        print(f"{'variant':10s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s}")
+        for label, v in variants(args.families.split(",")):
+            r = time_variant(lib, rows, T, v, tensors, args.iters)
+            results[f"{name}/{label}"] = r
+
+            def cell(x):
+                return f"{x['GBps']:9.0f} {x['ms']:8.4f}" if x else f"{'-':>9s} {'-':>8s}"
+
+            print(f"{label:10s} {cell(r['fwd'])} {cell(r['bwd'])}", flush=True)
+        del tensors, a
+    detail = _native.ctypes.c_int(0)
+    _native.check(lib.ssb_device_status(_native.ctypes.byref(detail)))
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump(results, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
