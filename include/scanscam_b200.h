@@ -99,8 +99,17 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
                         size_t workspace_bytes, void *stream);
 
 /* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
- * The workspace must be 256-byte aligned; its contents need not be initialised. */
+ * The workspace must be 256-byte aligned; its contents need not be initialised (the entry
+ * point clears what it needs on the stream it launches on).  A workspace must not be shared
+ * by calls that can overlap on the GPU. */
 size_t ssb_scan_workspace_bytes(int64_t rows, int64_t T, int variant);
+
+/* The variant (family | tuning id << 8) the library would pick for this problem; the same
+ * choice SSB_VARIANT_AUTO makes when `can_provide_workspace` is 0.  With a non-zero
+ * `can_provide_workspace` the answer may be SSB_VARIANT_LOOKBACK (long rows: T > 4096), which
+ * the caller then has to give ssb_scan_workspace_bytes() of scratch through the _ex entry
+ * points.  `aligned16` says whether every tensor pointer is 16-byte aligned. */
+int ssb_scan_recommend(int64_t rows, int64_t T, int backward, int aligned16, int can_provide_workspace);
 
 /* ------------------------------------------------------------------------------------
  * Channels-last layout, [N, T, C] scanned over T.
@@ -134,9 +143,13 @@ int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout,
  *   right (fold of shards n_shards-1 .. shard+1 from zero).
  * ---------------------------------------------------------------------------------- */
 int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows,
-                             int64_t T, void *stream);
+                             int64_t T, void *workspace, size_t workspace_bytes, void *stream);
 int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows,
-                             int64_t T, void *stream);
+                             int64_t T, void *workspace, size_t workspace_bytes, void *stream);
+/* Scratch the two reduce entry points can use (0 = they never use any for this shape).  With a
+ * workspace of that size long rows are reduced by many CTAs per row; without one (NULL, 0) one
+ * warp walks each row, which is slower for long rows and few of them. */
+size_t ssb_shard_reduce_workspace_bytes(int64_t rows, int64_t T);
 int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse, int64_t rows,
                         float *carry, void *stream);
 

@@ -16,6 +16,7 @@
 #include "scan_cl.cuh"
 #include "scan_common.cuh"
 #include "scan_flat.cuh"
+#include "scan_lookback.cuh"
 #include "scan_tma.cuh"
 #include "scan_warp.cuh"
 
@@ -264,6 +265,100 @@ int dispatch_flat_bwd(int tuning, const float *gate, const float *h, const float
     }
 }
 
+// ------------------------------------------------------------------------------------
+// Look-back family (long rows)
+// ------------------------------------------------------------------------------------
+// Tuning table: id -> (threads per CTA, float4s per thread); span capacity = product.
+#define SSB_LOOKBACK_CONFIGS(X) X(0, 128, 8) X(1, 256, 4) X(2, 256, 2) X(3, 128, 4) X(4, 512, 2) X(5, 256, 1) X(6, 64, 16)
+
+int lookback_cap(int tuning) {
+    switch (tuning) {
+#define X(ID, TH, UU) case ID: return TH * UU;
+        SSB_LOOKBACK_CONFIGS(X)
+#undef X
+        default: return 0;
+    }
+}
+
+bool lookback_eligible(int64_t rows, int64_t T, int tuning) {
+    const int cap = lookback_cap(tuning);
+    return cap > 0 && flat_eligible(rows, T) && T / 4 > cap;
+}
+
+size_t lookback_bytes(int64_t rows, int64_t T, int tuning) {
+    const int cap = lookback_cap(tuning);
+    if (cap == 0 || T % 4 != 0) return 0;
+    const int64_t pieces = (T / 4 + cap - 1) / cap;
+    return ssb::lookback::kHeaderBytes + (size_t)rows * (size_t)pieces * sizeof(ssb::lookback::Record);
+}
+
+template <int THREADS, int U, bool BWD>
+int launch_lookback(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
+                    int64_t T, const float *carry_in, const float *h_prev, void *workspace, size_t need,
+                    cudaStream_t st) {
+    auto kern = ssb::lookback::lookback_kernel<THREADS, U, BWD>;
+    const int64_t T4 = T / 4;
+    ssb::lookback::Order order;
+    order.rows = rows;
+    order.pieces = (T4 + THREADS * U - 1) / (THREADS * U);
+    const int grid_cap = flat_grid<THREADS * 64 + U * 2 + (BWD ? 1 : 0) + 100000>(kern, THREADS, (int64_t)1 << 40);
+    int64_t k = (grid_cap + rows - 1) / rows;
+    if (k < 1) k = 1;
+    if (k > order.pieces) k = order.pieces;
+    order.k = k;
+    order.wave = rows * k;
+    const int64_t tickets = ((order.pieces + k - 1) / k) * order.wave;
+    const int grid = (int)(tickets < grid_cap ? tickets : grid_cap);
+    if (cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess) return check_launch("cudaMemsetAsync(workspace)");
+    kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1),
+                                   reinterpret_cast<const float4 *>(in2), reinterpret_cast<float4 *>(out1),
+                                   reinterpret_cast<float4 *>(out2), T4, order, carry_in, h_prev,
+                                   static_cast<unsigned char *>(workspace));
+    return check_launch("lookback_kernel");
+}
+
+template <bool BWD>
+int dispatch_lookback(int tuning, const float *gate, const float *in1, const float *in2, float *out1, float *out2,
+                      int64_t rows, int64_t T, const float *carry_in, const float *h_prev, void *workspace,
+                      size_t workspace_bytes, cudaStream_t st) {
+    if (!lookback_eligible(rows, T, tuning))
+        return fail(SSB_ERR_UNSUPPORTED, "look-back kernels need 16-byte aligned tensors, T %% 4 == 0 and rows longer than one span (T=%lld)", (long long)T);
+    const size_t need = lookback_bytes(rows, T, tuning);
+    if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 256))
+        return fail(SSB_ERR_WORKSPACE, "look-back needs a 256-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+    switch (tuning) {
+#define X(ID, TH, UU) case ID: return launch_lookback<TH, UU, BWD>(gate, in1, in2, out1, out2, rows, T, carry_in, h_prev, workspace, need, st);
+        SSB_LOOKBACK_CONFIGS(X)
+#undef X
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown look-back tuning id %d", tuning);
+    }
+}
+
+// Row aggregates through per-span maps in a workspace (long rows).
+constexpr int kMapsThreads = 256, kMapsU = 4;
+
+size_t span_maps_bytes(int64_t rows, int64_t T) {
+    if (T % 4 != 0 || T / 4 <= kMapsThreads * kMapsU) return 0;
+    const int64_t pieces = (T / 4 + kMapsThreads * kMapsU - 1) / (kMapsThreads * kMapsU);
+    return (size_t)rows * (size_t)pieces * sizeof(float2);
+}
+
+template <bool BWD>
+int launch_span_maps(const float *gate, const float *in1, float *agg, int64_t rows, int64_t T, void *workspace,
+                     cudaStream_t st) {
+    const int64_t T4 = T / 4;
+    const int64_t pieces = (T4 + kMapsThreads * kMapsU - 1) / (kMapsThreads * kMapsU);
+    auto kern = ssb::lookback::span_maps_kernel<kMapsThreads, kMapsU, BWD>;
+    const int grid = flat_grid<200000 + (BWD ? 1 : 0)>(kern, kMapsThreads, rows * pieces);
+    kern<<<grid, kMapsThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1),
+                                        rows, T4, pieces, static_cast<float2 *>(workspace));
+    int rc = check_launch("span_maps_kernel");
+    if (rc != SSB_OK) return rc;
+    const int64_t blocks = (rows * 32 + 255) / 256;
+    ssb::lookback::fold_maps_kernel<BWD><<<(int)blocks, 256, 0, st>>>(static_cast<const float2 *>(workspace), rows, pieces, agg);
+    return check_launch("fold_maps_kernel");
+}
+
 // `variant` carries the family in its low byte and a tuning id in bits 8..15 (0 = default).
 int family_of(int variant) { return variant & 0xff; }
 int tuning_of(int variant) { return (variant >> 8) & 0xff; }
@@ -313,7 +408,8 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 //     prefers it while rows fit in a span and 256 threads x 1 float4 once rows are longer.
 //   * anything else (odd T, unaligned views) -> one warp per row.
 // The TMA family is within a few percent of these on T >= 256 and is reachable by pinning it.
-int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16) {
+int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
+    if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
     if (all_aligned16 && flat_eligible(rows, T)) {
         if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);
         return SSB_VARIANT_FLAT | (6 << 8);
@@ -343,14 +439,23 @@ const char *ssb_status_string(int status) {
 const char *ssb_last_error(void) { return t_last_error; }
 
 size_t ssb_scan_workspace_bytes(int64_t rows, int64_t T, int variant) {
-    (void)rows; (void)T; (void)variant;
-    return 0;
+    if (rows <= 0 || T <= 0 || family_of(variant) != SSB_VARIANT_LOOKBACK) return 0;
+    return lookback_bytes(rows, T, tuning_of(variant));
+}
+
+int ssb_scan_recommend(int64_t rows, int64_t T, int backward, int aligned16, int can_provide_workspace) {
+    if (rows <= 0 || T <= 0) return SSB_VARIANT_WARP;
+    return pick_variant(backward != 0, rows, T, aligned16 != 0, can_provide_workspace != 0);
+}
+
+size_t ssb_shard_reduce_workspace_bytes(int64_t rows, int64_t T) {
+    if (rows <= 0 || T <= 0) return 0;
+    return span_maps_bytes(rows, T);
 }
 
 int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
                         const float *h_in, int variant, void *workspace, size_t workspace_bytes,
                         void *stream) {
-    (void)workspace; (void)workspace_bytes;
     int64_t n;
     int rc = check_shape(rows, T, &n);
     if (rc != SSB_OK) return rc;
@@ -374,6 +479,11 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
                 return fail(SSB_ERR_UNSUPPORTED, "flat forward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
+        case SSB_VARIANT_LOOKBACK:
+            if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back forward needs 16-byte aligned tensors");
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return dispatch_lookback<false>(tuning_of(variant), gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr,
+                                            workspace, workspace_bytes, st);
         default:
             return fail(SSB_ERR_UNSUPPORTED, "forward variant %d is not available", variant);
     }
@@ -399,7 +509,6 @@ int ssb_scan_fwd_f64(const double *gate, const double *value, double *out, int64
 int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
                         int64_t rows, int64_t T, const float *c_in, const float *h_prev, int variant,
                         void *workspace, size_t workspace_bytes, void *stream) {
-    (void)workspace; (void)workspace_bytes;
     int64_t n;
     int rc = check_shape(rows, T, &n);
     if (rc != SSB_OK) return rc;
@@ -425,6 +534,11 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
                 return fail(SSB_ERR_UNSUPPORTED, "flat backward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case SSB_VARIANT_LOOKBACK:
+            if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back backward needs 16-byte aligned tensors");
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return dispatch_lookback<true>(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev,
+                                           workspace, workspace_bytes, st);
         default:
             return fail(SSB_ERR_UNSUPPORTED, "backward variant %d is not available", variant);
     }
@@ -515,7 +629,8 @@ int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout,
 }
 
 // ---- sequence sharding -----------------------------------------------------------------
-int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows, int64_t T, void *stream) {
+int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows, int64_t T,
+                             void *workspace, size_t workspace_bytes, void *stream) {
     int64_t n;
     int rc = check_shape(rows, T, &n);
     if (rc != SSB_OK) return rc;
@@ -523,10 +638,15 @@ int ssb_shard_reduce_fwd_f32(const float *gate, const float *value, float *agg, 
     if (!agg || (n > 0 && (!gate || !value))) return fail(SSB_ERR_BAD_ARG, "ssb_shard_reduce_fwd_f32: NULL pointer");
     if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(agg, 4))
         return fail(SSB_ERR_ALIGNMENT, "ssb_shard_reduce_fwd_f32: pointers must be 4-byte aligned");
+    const size_t need = span_maps_bytes(rows, T);
+    if (workspace != nullptr && need > 0 && workspace_bytes >= need && aligned_to(workspace, 16) && aligned_to(gate, 16) &&
+        aligned_to(value, 16))
+        return launch_span_maps<false>(gate, value, agg, rows, T, workspace, static_cast<cudaStream_t>(stream));
     return launch_warp_fwd<float, true>(gate, value, nullptr, rows, T, nullptr, agg, static_cast<cudaStream_t>(stream));
 }
 
-int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T, void *stream) {
+int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T,
+                             void *workspace, size_t workspace_bytes, void *stream) {
     int64_t n;
     int rc = check_shape(rows, T, &n);
     if (rc != SSB_OK) return rc;
@@ -534,6 +654,10 @@ int ssb_shard_reduce_bwd_f32(const float *gate, const float *gout, float *agg, i
     if (!agg || (n > 0 && (!gate || !gout))) return fail(SSB_ERR_BAD_ARG, "ssb_shard_reduce_bwd_f32: NULL pointer");
     if (!aligned_to(gate, 4) || !aligned_to(gout, 4) || !aligned_to(agg, 4))
         return fail(SSB_ERR_ALIGNMENT, "ssb_shard_reduce_bwd_f32: pointers must be 4-byte aligned");
+    const size_t need = span_maps_bytes(rows, T);
+    if (workspace != nullptr && need > 0 && workspace_bytes >= need && aligned_to(workspace, 16) && aligned_to(gate, 16) &&
+        aligned_to(gout, 16))
+        return launch_span_maps<true>(gate, gout, agg, rows, T, workspace, static_cast<cudaStream_t>(stream));
     return launch_warp_bwd<float, true>(gate, nullptr, gout, nullptr, nullptr, rows, T, nullptr, nullptr, agg,
                                         static_cast<cudaStream_t>(stream));
 }

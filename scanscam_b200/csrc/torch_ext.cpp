@@ -40,6 +40,14 @@ void raise_on(int status, const char *op) {
 
 void *current_stream() { return static_cast<void *>(at::cuda::getCurrentCUDAStream().stream()); }
 
+bool aligned16(const torch::Tensor &t) { return reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0; }
+
+// Scratch for the kernels that want it, from PyTorch's caching allocator (stream-ordered, so
+// the tensor may be released as soon as the launch has been enqueued on the current stream).
+torch::Tensor scratch(size_t bytes, const torch::Tensor &like) {
+    return torch::empty({static_cast<int64_t>(bytes)}, like.options().dtype(torch::kUInt8));
+}
+
 const void *opt_ptr(const c10::optional<torch::Tensor> &t, const torch::Tensor &like, int64_t rows, const char *name) {
     if (!t.has_value() || !t->defined()) return nullptr;
     check_tensor(*t, name);
@@ -61,8 +69,14 @@ void scan_forward_impl(const torch::Tensor &gate, const torch::Tensor &value, to
     const void *hin = opt_ptr(h_in, gate, rows, "h_in");
     int rc;
     if (gate.scalar_type() == torch::kFloat32) {
+        if (variant == SSB_VARIANT_AUTO)
+            variant = ssb_scan_recommend(rows, T, 0, aligned16(gate) && aligned16(value) && aligned16(output), 1);
+        const size_t ws_bytes = ssb_scan_workspace_bytes(rows, T, (int)variant);
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
         rc = ssb_scan_fwd_f32_ex(gate.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(), rows, T,
-                                 static_cast<const float *>(hin), (int)variant, nullptr, 0, current_stream());
+                                 static_cast<const float *>(hin), (int)variant, ws_bytes ? ws.data_ptr() : nullptr,
+                                 ws_bytes, current_stream());
     } else {
         rc = ssb_scan_fwd_f64(gate.data_ptr<double>(), value.data_ptr<double>(), output.data_ptr<double>(), rows, T,
                               static_cast<const double *>(hin), current_stream());
@@ -86,10 +100,17 @@ void scan_backward_impl(const torch::Tensor &gate, const torch::Tensor &output, 
     const void *hp = opt_ptr(h_prev, gate, rows, "h_prev");
     int rc;
     if (gate.scalar_type() == torch::kFloat32) {
+        if (variant == SSB_VARIANT_AUTO)
+            variant = ssb_scan_recommend(rows, T, 1,
+                                         aligned16(gate) && aligned16(output) && aligned16(out_grad) &&
+                                             aligned16(gate_grad) && aligned16(value_grad), 1);
+        const size_t ws_bytes = ssb_scan_workspace_bytes(rows, T, (int)variant);
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
         rc = ssb_scan_bwd_f32_ex(gate.data_ptr<float>(), output.data_ptr<float>(), out_grad.data_ptr<float>(),
                                  gate_grad.data_ptr<float>(), value_grad.data_ptr<float>(), rows, T,
-                                 static_cast<const float *>(cin), static_cast<const float *>(hp), (int)variant, nullptr,
-                                 0, current_stream());
+                                 static_cast<const float *>(cin), static_cast<const float *>(hp), (int)variant,
+                                 ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     } else {
         rc = ssb_scan_bwd_f64(gate.data_ptr<double>(), output.data_ptr<double>(), out_grad.data_ptr<double>(),
                               gate_grad.data_ptr<double>(), value_grad.data_ptr<double>(), rows, T,
@@ -191,8 +212,12 @@ void shard_reduce_forward(torch::Tensor gate, torch::Tensor value, torch::Tensor
     check_tensor(agg, "agg");
     TORCH_CHECK(agg.scalar_type() == torch::kFloat32 && agg.numel() == 2 * gate.size(0), "agg must be float32 [rows, 2]");
     c10::cuda::CUDAGuard guard(gate.device());
+    const size_t ws_bytes = ssb_shard_reduce_workspace_bytes(gate.size(0), gate.size(1));
+    torch::Tensor ws;
+    if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
     raise_on(ssb_shard_reduce_fwd_f32(gate.data_ptr<float>(), value.data_ptr<float>(), agg.data_ptr<float>(),
-                                      gate.size(0), gate.size(1), current_stream()),
+                                      gate.size(0), gate.size(1), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                                      current_stream()),
              "shard_reduce_forward");
 }
 
@@ -203,8 +228,12 @@ void shard_reduce_backward(torch::Tensor gate, torch::Tensor outGrad, torch::Ten
     check_tensor(agg, "agg");
     TORCH_CHECK(agg.scalar_type() == torch::kFloat32 && agg.numel() == 2 * gate.size(0), "agg must be float32 [rows, 2]");
     c10::cuda::CUDAGuard guard(gate.device());
+    const size_t ws_bytes = ssb_shard_reduce_workspace_bytes(gate.size(0), gate.size(1));
+    torch::Tensor ws;
+    if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
     raise_on(ssb_shard_reduce_bwd_f32(gate.data_ptr<float>(), outGrad.data_ptr<float>(), agg.data_ptr<float>(),
-                                      gate.size(0), gate.size(1), current_stream()),
+                                      gate.size(0), gate.size(1), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                                      current_stream()),
              "shard_reduce_backward");
 }
 

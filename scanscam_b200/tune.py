@@ -19,6 +19,7 @@ from .workloads import WORKLOADS
 
 FLAT_IDS = range(14)                 # SSB_FLAT_CONFIGS in csrc/scanscam_b200.cu
 TMA_IDS = (0, 1, 5, 6, 8, 10)
+LOOKBACK_IDS = range(7)              # SSB_LOOKBACK_CONFIGS
 
 
 def variants(families):
@@ -29,19 +30,25 @@ def variants(families):
         out += [(f"flat{t}", _native.VARIANT_FLAT | (t << 8)) for t in FLAT_IDS]
     if "tma" in families:
         out += [(f"tma{t}", _native.VARIANT_TMA | (t << 8)) for t in TMA_IDS]
+    if "lookback" in families:
+        out += [(f"lookback{t}", _native.VARIANT_LOOKBACK | (t << 8)) for t in LOOKBACK_IDS]
     return out
 
 
 def time_variant(lib, rows, T, variant, tensors, iters):
     a, b, g, h, ga, gb = tensors
     st = torch.cuda.current_stream().cuda_stream
+    ws_bytes = lib.ssb_scan_workspace_bytes(rows, T, variant)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=a.device)
+    ws_ptr = ws.data_ptr() if ws_bytes else None
 
     def fwd():
-        return lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, variant, None, 0, st)
+        return lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, variant, ws_ptr,
+                                       ws_bytes, st)
 
     def bwd():
         return lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
-                                       None, None, variant, None, 0, st)
+                                       None, None, variant, ws_ptr, ws_bytes, st)
 
     res = {}
     for kind, fn, nbytes in (("fwd", fwd, 12), ("bwd", bwd, 20)):
@@ -69,7 +76,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("shapes")
     ap.add_argument("--iters", type=int, default=30)
-    ap.add_argument("--families", default="warp,flat,tma")
+    ap.add_argument("--families", default="warp,flat,tma,lookback")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
     lib = _native.load()

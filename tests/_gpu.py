@@ -7,6 +7,19 @@ import oracle
 from scanscam_b200 import _native
 
 AUTO, WARP, TMA, FLAT = _native.VARIANT_AUTO, _native.VARIANT_WARP, _native.VARIANT_TMA, _native.VARIANT_FLAT
+LOOKBACK = _native.VARIANT_LOOKBACK
+
+
+def lookback_variant(tuning):
+    return LOOKBACK | (tuning << 8)
+
+
+def workspace_for(rows, T, variant, device="cuda"):
+    """(tensor or None, nbytes) of scratch the variant asks for."""
+    need = _native.load().ssb_scan_workspace_bytes(rows, T, variant)
+    if need == 0:
+        return None, 0
+    return torch.empty(need, dtype=torch.uint8, device=device), need
 
 
 def tma_variant(tuning):
@@ -17,29 +30,31 @@ def flat_variant(tuning):
     return FLAT | (tuning << 8)
 
 
-def fwd(a, b, h_in=None, variant=AUTO):
+def fwd(a, b, h_in=None, variant=AUTO, workspace=None):
     """a, b: CUDA [rows, T] contiguous float32/float64 -> h (through ssb_scan_fwd_*)."""
     lib = _native.load()
     out = torch.empty_like(a)
     rows, T = a.shape
     st = _native.stream_of(a)
     if a.dtype == torch.float32:
+        ws, ws_bytes = workspace_for(rows, T, variant, a.device) if workspace is None else workspace
         rc = lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), rows, T, _native.ptr(h_in),
-                                     variant, None, 0, st)
+                                     variant, _native.ptr(ws), ws_bytes, st)
     else:
         rc = lib.ssb_scan_fwd_f64(a.data_ptr(), b.data_ptr(), out.data_ptr(), rows, T, _native.ptr(h_in), st)
     _native.check(rc)
     return out
 
 
-def bwd(a, h, g, c_in=None, h_prev=None, variant=AUTO):
+def bwd(a, h, g, c_in=None, h_prev=None, variant=AUTO, workspace=None):
     lib = _native.load()
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     rows, T = a.shape
     st = _native.stream_of(a)
     if a.dtype == torch.float32:
+        ws, ws_bytes = workspace_for(rows, T, variant, a.device) if workspace is None else workspace
         rc = lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
-                                     _native.ptr(c_in), _native.ptr(h_prev), variant, None, 0, st)
+                                     _native.ptr(c_in), _native.ptr(h_prev), variant, _native.ptr(ws), ws_bytes, st)
     else:
         rc = lib.ssb_scan_bwd_f64(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
                                   _native.ptr(c_in), _native.ptr(h_prev), st)

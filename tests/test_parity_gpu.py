@@ -11,7 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import _gpu  # noqa: E402
-from _gpu import AUTO, FLAT, TMA, WARP  # noqa: E402
+from _gpu import AUTO, FLAT, LOOKBACK, TMA, WARP  # noqa: E402
 
 import oracle  # noqa: E402
 from scanscam_b200 import _native  # noqa: E402
@@ -192,8 +192,12 @@ def test_virtual_t_shards_on_one_gpu(n_shards):
     fmaps = torch.empty(n_shards, rows, 2, device="cuda")
     bmaps = torch.empty(n_shards, rows, 2, device="cuda")
     for s, (pa, pb, pg, _) in enumerate(parts):
-        _native.check(lib.ssb_shard_reduce_fwd_f32(pa.data_ptr(), pb.data_ptr(), fmaps[s].data_ptr(), rows, step, st))
-        _native.check(lib.ssb_shard_reduce_bwd_f32(pa.data_ptr(), pg.data_ptr(), bmaps[s].data_ptr(), rows, step, st))
+        ws_bytes = lib.ssb_shard_reduce_workspace_bytes(rows, step) if s % 2 == 0 else 0  # both code paths
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+        _native.check(lib.ssb_shard_reduce_fwd_f32(pa.data_ptr(), pb.data_ptr(), fmaps[s].data_ptr(), rows, step,
+                                                   ws.data_ptr() if ws_bytes else None, ws_bytes, st))
+        _native.check(lib.ssb_shard_reduce_bwd_f32(pa.data_ptr(), pg.data_ptr(), bmaps[s].data_ptr(), rows, step,
+                                                   ws.data_ptr() if ws_bytes else None, ws_bytes, st))
     hs, gas, gbs = [], [], []
     for s, (pa, pb, pg, ph) in enumerate(parts):
         h_in = torch.empty(rows, device="cuda")
@@ -211,6 +215,97 @@ def test_virtual_t_shards_on_one_gpu(n_shards):
     A_ref = a[:, :step].double().prod(dim=1)
     np.testing.assert_allclose(fmaps[0, :, 0].cpu().double().numpy(), A_ref.numpy(), rtol=1e-4)
     np.testing.assert_allclose(fmaps[0, :, 1].cpu().numpy(), h_ref[:, step - 1], rtol=1e-5, atol=1e-6)
+    _gpu.device_ok()
+
+
+# ---- long rows: spans of one row on different CTAs, carries by decoupled look-back ----------
+LONG_SHAPES = [(3, 8192), (1, 1048576), (5, 40000), (64, 16384), (700, 8196), (2, 4100), (17, 262144)]
+
+
+@pytest.mark.parametrize("shape", LONG_SHAPES)
+@pytest.mark.parametrize("gates", ["nearunit", "randn", "resets"])
+def test_lookback_long_rows(shape, gates):
+    rows, T = shape
+    a, b, g = make_inputs(gates, shape, seed=23)
+    carry = torch.randn(rows) * 0.5
+    an, bn, gn, cn = a.numpy(), b.numpy(), g.numpy(), carry.numpy()
+    h_ref = oracle.scan_forward(an, bn, h_in=cn)
+    ga_ref, gb_ref = oracle.scan_backward(an, h_ref, gn, gb_in=cn, h_prev=cn)
+    da, db, dg, dh, dc = a.cuda(), b.cuda(), g.cuda(), dev(h_ref), carry.cuda()
+    lib = _native.load()
+    ran = 0
+    for tuning in range(7):
+        variant = _gpu.lookback_variant(tuning)
+        if lib.ssb_scan_workspace_bytes(rows, T, variant) == 0:
+            continue
+        ws = _gpu.workspace_for(rows, T, variant)
+        if ws[0] is not None:
+            ws[0].fill_(0xAB)  # stale contents must not matter
+        try:
+            h = _gpu.fwd(da, db, h_in=dc, variant=variant, workspace=ws)
+        except _native.NativeError as e:  # row not longer than this tuning's span
+            assert e.status == _native.ERR_UNSUPPORTED
+            continue
+        ga, gb = _gpu.bwd(da, dh, dg, c_in=dc, h_prev=dc, variant=variant, workspace=ws)
+        ran += 1
+        for got, ref, name in ((h, h_ref, "h"), (gb, gb_ref, "gb"), (ga, ga_ref, "ga")):
+            err = _gpu.max_norm_err(got, ref)
+            assert err < TOL, (shape, gates, tuning, name, err)
+        if gates != "randn":  # randn gates swing over many orders of magnitude; max-norm is the fair metric there
+            assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(gb, gb_ref)
+    assert ran >= 3
+    _gpu.device_ok()
+
+
+def test_lookback_workspace_contract():
+    lib = _native.load()
+    a = torch.rand(4, 16384, device="cuda")
+    v = _gpu.lookback_variant(0)
+    need = lib.ssb_scan_workspace_bytes(4, 16384, v)
+    assert need == 256 + 4 * 4 * 16          # header + rows * pieces(4096-element spans) * 16-byte records
+    assert lib.ssb_scan_workspace_bytes(4, 16384, WARP) == 0
+    with pytest.raises(_native.NativeError) as err:
+        _gpu.fwd(a, a, variant=v, workspace=(None, 0))
+    assert err.value.status == _native.ERR_WORKSPACE
+    small = torch.empty(need - 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_native.NativeError) as err:
+        _gpu.fwd(a, a, variant=v, workspace=(small, need - 16))
+    assert err.value.status == _native.ERR_WORKSPACE
+    short = torch.rand(4, 1024, device="cuda")
+    with pytest.raises(_native.NativeError) as err:
+        _gpu.fwd(short, short, variant=v, workspace=(torch.empty(4096, dtype=torch.uint8, device="cuda"), 4096))
+    assert err.value.status == _native.ERR_UNSUPPORTED
+    # the recommendation: look-back only for long rows and only when the caller can supply scratch
+    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) & 0xff == LOOKBACK
+    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
+    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == FLAT
+    assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff == WARP
+    assert lib.ssb_scan_recommend(64, 65536, 1, 0, 1) & 0xff == WARP
+    _gpu.device_ok()
+
+
+def test_shard_reduce_with_and_without_workspace():
+    lib = _native.load()
+    rows, T = 9, 70000
+    _, b, g = make_inputs("nearunit", (rows, T), seed=3)
+    a = 1.0 - 1e-5 * torch.rand(rows, T, generator=torch.Generator().manual_seed(3))  # product stays ~0.7
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    st = _native.stream_of(da)
+    need = lib.ssb_shard_reduce_workspace_bytes(rows, T)
+    assert need > 0 and lib.ssb_shard_reduce_workspace_bytes(rows, 1024) == 0
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    out = torch.empty(4, rows, 2, device="cuda")
+    _native.check(lib.ssb_shard_reduce_fwd_f32(da.data_ptr(), db.data_ptr(), out[0].data_ptr(), rows, T, None, 0, st))
+    _native.check(lib.ssb_shard_reduce_fwd_f32(da.data_ptr(), db.data_ptr(), out[1].data_ptr(), rows, T, ws.data_ptr(), need, st))
+    _native.check(lib.ssb_shard_reduce_bwd_f32(da.data_ptr(), dg.data_ptr(), out[2].data_ptr(), rows, T, None, 0, st))
+    _native.check(lib.ssb_shard_reduce_bwd_f32(da.data_ptr(), dg.data_ptr(), out[3].data_ptr(), rows, T, ws.data_ptr(), need, st))
+    o = out.cpu().double().numpy()
+    h_ref = oracle.scan_forward(a.double().numpy(), b.double().numpy())
+    A_ref = a.double().prod(dim=1).numpy()
+    for k in (0, 1):
+        np.testing.assert_allclose(o[k][:, 0], A_ref, rtol=1e-3)
+        np.testing.assert_allclose(o[k][:, 1], h_ref[:, -1], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(o[2], o[3], rtol=1e-4, atol=1e-5)
     _gpu.device_ok()
 
 
