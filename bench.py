@@ -276,13 +276,22 @@ def run_gpu_arm(args, workload):
 
         launches_per_step = 8
     else:
+        # Kernel choice and scratch exactly as the PyTorch extension does it: ask the library, give it
+        # the workspace it wants (allocated once here, outside the timed region, and reused).
+        v_fwd = args.variant or lib.ssb_scan_recommend(rows, T_local, 0, 1, 1)
+        v_bwd = args.variant or lib.ssb_scan_recommend(rows, T_local, 1, 1, 1)
+        ws_bytes = max(lib.ssb_scan_workspace_bytes(rows, T_local, v_fwd),
+                       lib.ssb_scan_workspace_bytes(rows, T_local, v_bwd))
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
+        ws_ptr = ws.data_ptr() if ws_bytes else None
+
         def fwd():
             _native.check(lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local, None,
-                                                  args.variant, None, 0, st))
+                                                  v_fwd, ws_ptr, ws_bytes, st))
 
         def bwd():
             _native.check(lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
-                                                  gb.data_ptr(), rows, T_local, None, None, args.variant, None, 0, st))
+                                                  gb.data_ptr(), rows, T_local, None, None, v_bwd, ws_ptr, ws_bytes, st))
 
         def step():
             fwd()
@@ -393,14 +402,18 @@ def run_gpu_arm(args, workload):
     fwd_avg_s = fwd_total / args.steps * 1e-3
     line = {
         "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if t_sharded else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {
-            "workload": f"{workload.name} {list(workload.shape)} fp32 fwd+bwd per GPU, gates {workload.gates}, seed = rank",
+            "workload": (f"{workload.name} {list(workload.shape)} fp32 fwd+bwd, one sequence set split along T over all ranks"
+                         if t_sharded else
+                         f"{workload.name} {list(workload.shape)} fp32 fwd+bwd per GPU, gates {workload.gates}, seed = rank"),
             "sharding": ("T split across ranks, NCCL all-gather of per-shard carries" if t_sharded
                          else "rows (batch x channel) per rank, no collective"),
             "l2": "no flush: each pass streams 0.8-1.3 GB, far more than the 126 MB L2",
             "variant": args.variant,
+            "kernels": (None if t_sharded else {"forward": v_fwd, "backward": v_bwd, "workspace_bytes": ws_bytes}),
         },
         "gpu_launches": launches_per_step * args.steps * world,
         "clocks": sampler.summary(sampler_how),
