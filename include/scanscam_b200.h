@@ -98,6 +98,39 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
                         const float *h_prev, int variant, void *workspace,
                         size_t workspace_bytes, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * Forward scan of long rows for callers that cannot hand over scratch memory.
+ * (No counterpart in the reference: it never splits a row and so never needs scratch.)
+ *
+ * Some hosts of this library have nowhere to get device memory from at call time: an
+ * inference server that reserved the whole GPU for its own pools at start-up and treats any
+ * later cudaMalloc as a bug (it synchronises the device and can fail or fragment), a binding
+ * from a language runtime that owns no CUDA allocator, code running between fixed-size
+ * arenas.  For them this entry point runs the same look-back kernel as
+ * ssb_scan_fwd_f32_ex(..., SSB_VARIANT_LOOKBACK, ...) on a scratch area that is built into the
+ * library image: SSB_STATIC_SCRATCH_BYTES of device memory that every GPU holds from the
+ * moment the library is loaded on it until the process exits.  The call itself allocates and
+ * frees nothing, on the device or through any library.
+ *
+ * Limits and rules:
+ *   - rows must be longer than one span (T > 4096), T % 4 == 0, all pointers 16-byte aligned;
+ *     other shapes need no scratch: use ssb_scan_fwd_f32.
+ *   - rows * ceil(T / 4096) must not exceed SSB_STATIC_SCRATCH_SPANS (65 536 spans, i.e. up to
+ *     268 million elements); larger problems are refused with SSB_ERR_WORKSPACE and a message
+ *     that names both sizes.
+ *   - every call on a device uses the same scratch area, which still holds the previous
+ *     call's records; the call clears, on `stream`, the part it is going to use before its
+ *     kernel starts.  Two calls that can run on the GPU at the same time (different streams,
+ *     different host threads) would overwrite each other's records: serialise them.
+ *   - the first call on each device looks up the device address of the scratch area (a
+ *     host-side query, done once per device with that device current).  Make that first call
+ *     outside of any stream capture.
+ * ---------------------------------------------------------------------------------- */
+#define SSB_STATIC_SCRATCH_SPANS 65536
+#define SSB_STATIC_SCRATCH_BYTES (256 + 16 * SSB_STATIC_SCRATCH_SPANS)
+int ssb_scan_fwd_f32_static(const float *gate, const float *value, float *out, int64_t rows,
+                            int64_t T, const float *h_in, void *stream);
+
 /* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
  * The workspace must be 256-byte aligned; its contents need not be initialised (the entry
  * point clears what it needs on the stream it launches on).  A workspace must not be shared

@@ -489,6 +489,74 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
     }
 }
 
+}  // extern "C"
+
+// ---- built-in scratch for callers that cannot allocate --------------------------------------
+namespace {
+
+static_assert(SSB_STATIC_SCRATCH_BYTES ==
+                  ssb::lookback::kHeaderBytes + SSB_STATIC_SCRATCH_SPANS * sizeof(ssb::lookback::Record),
+              "the header's figures describe the look-back workspace layout");
+
+// Lives in the library image: each GPU that loads the library carries these bytes until exit.
+// In host code this name is only a handle for the runtime's symbol queries, never a device
+// address; the launcher below asks the runtime for the address and hands that to the kernel.
+static __device__ __align__(256) unsigned char g_static_scratch[SSB_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+int static_scratch_address(void **out) {
+    static std::atomic<void *> cached[64];
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+    void *p = (dev >= 0 && dev < 64) ? cached[dev].load(std::memory_order_acquire) : nullptr;
+    if (p == nullptr) {
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return fail(SSB_ERR_LAUNCH, "cudaGetSymbolAddress(built-in scratch) on device %d: %s", dev,
+                        cudaGetErrorString(e));
+        }
+        if (dev >= 0 && dev < 64) cached[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return SSB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ssb_scan_fwd_f32_static(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
+                            const float *h_in, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_fwd_f32_static: NULL tensor pointer");
+    if (!aligned_to(gate, 16) || !aligned_to(value, 16) || !aligned_to(out, 16) || !aligned_to(h_in, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_fwd_f32_static: gate, value and out must be 16-byte aligned");
+    if (!lookback_eligible(rows, T, 0))
+        return fail(SSB_ERR_UNSUPPORTED,
+                    "ssb_scan_fwd_f32_static serves rows longer than one 4096-element span with T %% 4 == 0 "
+                    "(got T=%lld); other shapes need no scratch, call ssb_scan_fwd_f32",
+                    (long long)T);
+    const size_t need = lookback_bytes(rows, T, 0);
+    if (need > (size_t)SSB_STATIC_SCRATCH_BYTES)
+        return fail(SSB_ERR_WORKSPACE,
+                    "problem needs %zu bytes of scratch (%lld rows x %lld spans) but the built-in scratch holds "
+                    "%zu bytes (%d spans); pass your own workspace to ssb_scan_fwd_f32_ex instead",
+                    need, (long long)rows, (long long)((T / 4 + 1023) / 1024), (size_t)SSB_STATIC_SCRATCH_BYTES,
+                    SSB_STATIC_SCRATCH_SPANS);
+    void *scratch = nullptr;
+    if ((rc = static_scratch_address(&scratch)) != SSB_OK) return rc;
+    t_grid_per_sm = 0;
+    // launch_lookback clears `need` bytes of the scratch on the stream (ticket counter and record
+    // flags must start at zero; whatever the previous call left beyond that is never read).
+    return launch_lookback<128, 8, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, scratch, need,
+                                          static_cast<cudaStream_t>(stream));
+}
+
 int ssb_scan_fwd_f32(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
                      const float *h_in, void *stream) {
     return ssb_scan_fwd_f32_ex(gate, value, out, rows, T, h_in, SSB_VARIANT_AUTO, nullptr, 0, stream);
