@@ -160,6 +160,24 @@ int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, fl
 int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate,
                         double *gvalue, int64_t N, int64_t T, int64_t C, void *stream);
 
+/* Channels-last with scratch: the time axis is split across CTAs (decoupled look-back), so the
+ * whole GPU is busy even when N*C is small.  `workspace` of ssb_scan_cl_workspace_bytes(N,T,C)
+ * bytes, 256-byte aligned, contents irrelevant; NULL / 0 falls back to the kernels of the plain
+ * entry points above (one CTA walks the whole time axis of 32 channels), and so do shapes for
+ * which those are faster (few channels per row, or enough channel groups to fill the GPU but too
+ * few to keep look-back chains short). */
+size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C);
+/* Tuning knob for sweeps: selects the tile shape (warps x steps) the calling host thread's next
+ * ssb_scan_cl_*_ex calls use; 0 = default choice (tile shape and plain-vs-look-back), any other id
+ * forces the look-back kernels with that tile shape.  Returns the previous id.  Results do not
+ * depend on it. */
+int ssb_scan_cl_set_tuning(int tuning);
+int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T,
+                           int64_t C, void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate,
+                           float *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
+                           size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------------------
  * Sequence (T) sharding.  The reference never splits a sequence; these three entry
  * points are the pieces a caller needs to do it: each shard is the affine map

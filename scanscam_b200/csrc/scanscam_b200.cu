@@ -14,6 +14,7 @@
 #include <limits>
 
 #include "scan_cl.cuh"
+#include "scan_cl_lookback.cuh"
 #include "scan_common.cuh"
 #include "scan_flat.cuh"
 #include "scan_lookback.cuh"
@@ -648,6 +649,45 @@ int check_cl(int64_t N, int64_t T, int64_t C, int64_t *n) {
     return SSB_OK;
 }
 
+// Look-back channels-last kernels: W warps per CTA, L time steps per warp.  Tuning table:
+// id -> (W, L forward, L backward); the smallest tile (W*L) of the table bounds the workspace.
+#define SSB_CL2_CONFIGS(X) X(0, 8, 16, 16) X(1, 8, 16, 16) X(12, 8, 8, 4) X(2, 4, 4, 4) X(3, 8, 4, 2) X(4, 2, 16, 8) X(5, 4, 8, 8) X(6, 4, 8, 2) X(7, 4, 16, 8) \
+    X(8, 8, 16, 8) X(9, 4, 8, 4) X(10, 8, 32, 16) X(11, 8, 24, 16)
+constexpr int kCl2MinTile = 8;  // every instantiated tile (W*L) must cover at least this many steps
+
+thread_local int t_cl_tuning = 0;
+
+template <int VEC, int kCl2Warps, int L, bool BWD>
+int launch_cl2(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+               int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    static_assert(kCl2Warps * L >= kCl2MinTile, "ssb_scan_cl_workspace_bytes sizes the workspace for tiles of kCl2MinTile steps");
+    auto kern = ssb::cl2::cl_lookback_kernel<VEC, kCl2Warps, L, BWD>;
+    ssb::cl2::Geometry geo;
+    geo.N = N; geo.T = T; geo.C = C;
+    geo.cgroups = (C + 32 * VEC - 1) / (32 * VEC);
+    geo.pieces = (T + kCl2Warps * L - 1) / (kCl2Warps * L);
+    geo.n_tiles = N * geo.cgroups * geo.pieces;
+    if (ssb::cl2::workspace_bytes(geo.n_tiles, VEC) > workspace_bytes)
+        return fail(SSB_ERR_WORKSPACE, "channels-last look-back needs %zu bytes of workspace, got %zu",
+                    ssb::cl2::workspace_bytes(geo.n_tiles, VEC), workspace_bytes);
+    ssb::lookback::Order order;
+    order.rows = N * geo.cgroups;
+    order.pieces = geo.pieces;
+    t_grid_per_sm = 0;
+    const int grid_cap = flat_grid<300000 + VEC * 10000 + kCl2Warps * 1000 + L * 10 + (BWD ? 1 : 0)>(kern, kCl2Warps * 32, (int64_t)1 << 40);
+    int64_t k = (grid_cap + order.rows - 1) / order.rows;
+    if (k < 1) k = 1;
+    if (k > order.pieces) k = order.pieces;
+    order.k = k;
+    order.wave = order.rows * k;
+    const int64_t tickets = ((order.pieces + k - 1) / k) * order.wave;
+    const int grid = (int)(tickets < grid_cap ? tickets : grid_cap);
+    if (cudaMemsetAsync(workspace, 0, ssb::cl2::bytes_to_clear(geo.n_tiles), st) != cudaSuccess)
+        return check_launch("cudaMemsetAsync(workspace)");
+    kern<<<grid, kCl2Warps * 32, 0, st>>>(gate, in1, in2, out1, out2, geo, order, static_cast<unsigned char *>(workspace));
+    return check_launch("cl_lookback_kernel");
+}
+
 template <typename real>
 int cl_fwd(const real *gate, const real *value, real *out, int64_t N, int64_t T, int64_t C, void *stream) {
     int64_t n;
@@ -683,6 +723,87 @@ extern "C" {
 
 int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, void *stream) {
     return cl_fwd<float>(gate, value, out, N, T, C, stream);
+}
+
+}  // extern "C"
+
+namespace {
+// Measured on B200: splitting T across CTAs pays when the plain kernels cannot fill the GPU
+// (fewer than ~96 groups of 32 channels) or when there are at least 64 groups of 128 channels
+// to keep the look-back chains short; with very few channels per row the 4-channel lanes of
+// the look-back kernels are mostly idle and the plain kernels win.
+bool cl_prefers_lookback(int64_t N, int64_t C) {
+    if (C < 64) return false;
+    const int64_t groups32 = N * ((C + 31) / 32), groups128 = N * ((C + 127) / 128);
+    return groups128 >= 64 || groups32 < 96;
+}
+}  // namespace
+
+extern "C" {
+
+int ssb_scan_cl_set_tuning(int tuning) {
+    const int prev = t_cl_tuning;
+    t_cl_tuning = tuning;
+    return prev;
+}
+
+size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C) {
+    if (N <= 0 || T <= 0 || C <= 0) return 0;
+    size_t need = 0;
+    for (int vec : {1, 4}) {
+        const int64_t tiles = N * ((C + 32 * vec - 1) / (32 * vec)) * ((T + kCl2MinTile - 1) / kCl2MinTile);
+        const size_t b = ssb::cl2::workspace_bytes(tiles, vec);
+        need = b > need ? b : need;
+    }
+    return need;
+}
+
+int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C,
+                           void *workspace, size_t workspace_bytes, void *stream) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
+        (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
+        return cl_fwd<float>(gate, value, out, N, T, C, stream);
+    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_fwd_f32_ex: NULL tensor pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(out, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_fwd_f32_ex: pointers must be 4-byte aligned");
+    const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16) &&
+                     !(t_cl_tuning & 0x100);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (t_cl_tuning & 0xff) {
+#define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st) \
+                                              : launch_cl2<1, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
+        SSB_CL2_CONFIGS(X)
+#undef X
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last tuning id %d", t_cl_tuning);
+    }
+}
+
+int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
+                           int64_t T, int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
+        (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
+        return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
+    if (!gate || !h || !gout || !ggate || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_bwd_f32_ex: NULL tensor pointer");
+    if (!aligned_to(gate, 4) || !aligned_to(h, 4) || !aligned_to(gout, 4) || !aligned_to(ggate, 4) || !aligned_to(gvalue, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_bwd_f32_ex: pointers must be 4-byte aligned");
+    const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
+                     aligned_to(ggate, 16) && aligned_to(gvalue, 16) && !(t_cl_tuning & 0x100);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (t_cl_tuning & 0xff) {
+#define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st) \
+                                              : launch_cl2<1, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
+        SSB_CL2_CONFIGS(X)
+#undef X
+        default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last tuning id %d", t_cl_tuning);
+    }
 }
 int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, int64_t N, int64_t T, int64_t C, void *stream) {
     return cl_fwd<double>(gate, value, out, N, T, C, stream);

@@ -171,8 +171,12 @@ void transposed_linear_scan(torch::Tensor gate, torch::Tensor value, torch::Tens
     c10::cuda::CUDAGuard guard(gate.device());
     int rc;
     if (gate.scalar_type() == torch::kFloat32) {
-        rc = ssb_scan_cl_fwd_f32(gate.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(), gate.size(0),
-                                 gate.size(1), gate.size(2), current_stream());
+        const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        rc = ssb_scan_cl_fwd_f32_ex(gate.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(),
+                                    gate.size(0), gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr,
+                                    ws_bytes, current_stream());
     } else {
         rc = ssb_scan_cl_fwd_f64(gate.data_ptr<double>(), value.data_ptr<double>(), output.data_ptr<double>(),
                                  gate.size(0), gate.size(1), gate.size(2), current_stream());
@@ -193,9 +197,13 @@ void transposed_linear_scan_backward(torch::Tensor gate, torch::Tensor output, t
     c10::cuda::CUDAGuard guard(gate.device());
     int rc;
     if (gate.scalar_type() == torch::kFloat32) {
-        rc = ssb_scan_cl_bwd_f32(gate.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
-                                 gateGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), gate.size(0),
-                                 gate.size(1), gate.size(2), current_stream());
+        const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        rc = ssb_scan_cl_bwd_f32_ex(gate.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
+                                    gateGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), gate.size(0),
+                                    gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                                    current_stream());
     } else {
         rc = ssb_scan_cl_bwd_f64(gate.data_ptr<double>(), output.data_ptr<double>(), outGrad.data_ptr<double>(),
                                  gateGradOut.data_ptr<double>(), valueGradOut.data_ptr<double>(), gate.size(0),

@@ -1,6 +1,7 @@
 """Kernel-variant sweep: times every kernel family / tuning id on given shapes.
 
     python -m scanscam_b200.tune cfg2,cfg5,1024x262144 [--iters 30] [--families warp,flat,tma]
+    python -m scanscam_b200.tune cl:8x4096x512,cl:4x65536x256         (channels-last [N,T,C])
 
 For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
 ``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
@@ -72,6 +73,44 @@ def time_variant(lib, rows, T, variant, tensors, iters):
     return res
 
 
+def time_channels_last(lib, N, T, C, iters):
+    """Plain kernels, look-back kernels (forced, default tile) and the library's own choice."""
+    a = torch.rand(N, T, C, device="cuda") * 0.2 + 0.8
+    b, g = torch.randn_like(a), torch.randn_like(a)
+    h, ga, gb = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+    st = torch.cuda.current_stream().cuda_stream
+    need = lib.ssb_scan_cl_workspace_bytes(N, T, C)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    n = N * T * C
+
+    def run(fn):
+        assert fn() == _native.OK
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / iters)
+        return best
+
+    rows = []
+    for label, tuning, use_ws in (("plain", 0, False), ("lookback", 1, True), ("auto", 0, True)):
+        lib.ssb_scan_cl_set_tuning(tuning)
+        p, nb = (ws.data_ptr(), need) if use_ws else (None, 0)
+        tf = run(lambda: lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, p, nb, st))
+        tb = run(lambda: lib.ssb_scan_cl_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
+                                                    gb.data_ptr(), N, T, C, p, nb, st))
+        rows.append((label, 12 * n / tf / 1e6, tf, 20 * n / tb / 1e6, tb))
+    lib.ssb_scan_cl_set_tuning(0)
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("shapes")
@@ -82,6 +121,14 @@ def main():
     lib = _native.load()
     results = {}
     for name in args.shapes.split(","):
+        if name.startswith("cl:"):  # channels-last: cl:NxTxC
+            N, T, C = (int(v) for v in name[3:].lower().split("x"))
+            print(f"# channels-last [N,T,C] = {N}x{T}x{C} ({N * T * C * 4 / 1e6:.0f} MB per tensor)")
+            print(f"{'kernels':10s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s}")
+            for label, fg, tf, bg, tb in time_channels_last(lib, N, T, C, args.iters):
+                results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}}
+                print(f"{label:10s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f}", flush=True)
+            continue
         if name in WORKLOADS:
             rows, T = WORKLOADS[name].rows, WORKLOADS[name].steps
         else:

@@ -62,19 +62,39 @@ def bwd(a, h, g, c_in=None, h_prev=None, variant=AUTO, workspace=None):
     return ga, gb
 
 
-def cl_fwd(a, b):
+def cl_workspace(a):
+    need = _native.load().ssb_scan_cl_workspace_bytes(*a.shape)
+    return torch.empty(max(need, 1), dtype=torch.uint8, device=a.device), need
+
+
+def cl_fwd(a, b, scratch=False):
+    """scratch=True: the look-back kernels (float32 only), with a workspace as a caller would pass."""
     lib = _native.load()
     out = torch.empty_like(a)
     N, T, C = a.shape
+    if scratch:
+        ws, need = cl_workspace(a)
+        lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)  # always look-back
+        _native.check(lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, ws.data_ptr(),
+                                                 need, _native.stream_of(a)))
+        lib.ssb_scan_cl_set_tuning(0)
+        return out
     fn = lib.ssb_scan_cl_fwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_fwd_f64
     _native.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, _native.stream_of(a)))
     return out
 
 
-def cl_bwd(a, h, g):
+def cl_bwd(a, h, g, scratch=False):
     lib = _native.load()
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     N, T, C = a.shape
+    if scratch:
+        ws, need = cl_workspace(a)
+        lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)
+        _native.check(lib.ssb_scan_cl_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                                 N, T, C, ws.data_ptr(), need, _native.stream_of(a)))
+        lib.ssb_scan_cl_set_tuning(0)
+        return ga, gb
     fn = lib.ssb_scan_cl_bwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_bwd_f64
     _native.check(fn(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C,
                      _native.stream_of(a)))

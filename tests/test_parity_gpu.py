@@ -62,10 +62,47 @@ def test_golden_vectors(name):
 def test_golden_vectors_channels_last(name):
     c = {k: GOLDEN[f"{name}/{k}"] for k in ("a", "b", "g", "h", "ga", "gb")}
     a, b, g, h_ref = (dev(c[k]) for k in ("a", "b", "g", "h"))
-    h = _gpu.cl_fwd(a, b)
-    ga, gb = _gpu.cl_bwd(a, h_ref, g)
-    for got, key in ((h, "h"), (ga, "ga"), (gb, "gb")):
-        assert _gpu.allclose_ref(got, c[key]), (name, key, _gpu.max_norm_err(got, c[key]))
+    for scratch in ([False, True] if a.dtype == torch.float32 else [False]):
+        h = _gpu.cl_fwd(a, b, scratch=scratch)
+        ga, gb = _gpu.cl_bwd(a, h_ref, g, scratch=scratch)
+        for got, key in ((h, "h"), (ga, "ga"), (gb, "gb")):
+            assert _gpu.allclose_ref(got, c[key]), (name, scratch, key, _gpu.max_norm_err(got, c[key]))
+    _gpu.device_ok()
+
+
+# [N, T, C]: wide, narrow, odd C (scalar path), C % 4 == 0 but not a multiple of 128, one long
+# sequence with few channels (many tiles chained by look-back), T below one tile, unaligned base
+@pytest.mark.parametrize("shape", [(2, 300, 512), (3, 107, 197), (5, 613, 107), (2, 1000, 36), (1, 20000, 8),
+                                   (1, 70000, 128), (4, 5, 64), (2, 64, 4), (16, 257, 256)])
+@pytest.mark.parametrize("gates", ["randn", "nearunit"])
+def test_channels_last_with_scratch(shape, gates):
+    a, b, g = make_inputs(gates, shape, seed=29)
+    an, bn, gn = a.numpy(), b.numpy(), g.numpy()
+    h_ref = oracle.scan_forward_channels_last(an, bn)
+    ga_ref, gb_ref = oracle.scan_backward_channels_last(an, h_ref, gn)
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    for scratch in (True, 12, 7, False):  # default tile, two other tile shapes, plain kernels
+        h = _gpu.cl_fwd(da, db, scratch=scratch)
+        ga, gb = _gpu.cl_bwd(da, dh, dg, scratch=scratch)
+        for got, ref, name in ((h, h_ref, "h"), (gb, gb_ref, "gb"), (ga, ga_ref, "ga")):
+            assert _gpu.max_norm_err(got, ref) < TOL, (shape, gates, scratch, name, _gpu.max_norm_err(got, ref))
+            if gates == "nearunit" or shape[1] <= 1000:
+                assert _gpu.allclose_ref(got, ref), (shape, gates, scratch, name)
+    _gpu.device_ok()
+
+
+def test_channels_last_unaligned_view_with_scratch():
+    a, b, g = make_inputs("sigmoid2", (2, 200, 64), seed=4)
+    h_ref = oracle.scan_forward_channels_last(a.numpy(), b.numpy())
+
+    def shifted(x):
+        buf = torch.empty(x.numel() + 1, device="cuda")
+        view = buf[1:].view(x.shape)
+        view.copy_(x)
+        return view
+
+    h = _gpu.cl_fwd(shifted(a), shifted(b), scratch=True)
+    assert _gpu.allclose_ref(h, h_ref)
 
 
 @pytest.mark.parametrize("shape", REF_SHAPES)
