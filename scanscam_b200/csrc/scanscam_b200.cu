@@ -403,13 +403,18 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
     }
 }
 
-// Default kernel choice, from sweeps on B200 over T = 64 .. 4M at 268 MB per tensor:
-//   * aligned fp32 with T % 4 == 0 -> the flat family.  128 threads x 8 float4s (16 KB spans,
-//     4 CTAs per SM) is the best or within 3 % of the best forward for every T; the backward
-//     prefers it while rows fit in a span and 256 threads x 1 float4 once rows are longer.
+// Default kernel choice, from sweeps on B200 over T = 64 .. 16M at 67 MB .. 4 GB per tensor
+// (profiles/kernel_family_sweep_b200.md):
+//   * aligned fp32 with T % 4 == 0, rows that fit a 16 KB span (T <= 4096) -> flat, 128 threads x
+//     8 float4s: the best or within 2 % of the best in both directions at every T.
+//   * longer rows: look-back (same span shape) when the caller can supply scratch -- within 3 %
+//     of the best everywhere and the only family whose speed does not depend on the number of
+//     rows; without scratch the flat family walks each row with one CTA.
+//   * very long rows with 1024 or more of them: the TMA ring (one warp per row, 2-stage ring,
+//     8 warps per CTA) is 3-7 % ahead of look-back there and needs no scratch.
 //   * anything else (odd T, unaligned views) -> one warp per row.
-// The TMA family is within a few percent of these on T >= 256 and is reachable by pinning it.
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
+    if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
     if (all_aligned16 && flat_eligible(rows, T)) {
         if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);

@@ -17,19 +17,32 @@ import torch
 from .decorator import preprocess_backward_scan_args, preprocess_scan_args
 
 _import_error: Optional[BaseException] = None
-try:
-    from . import scanscam_ext  # type: ignore[attr-defined]
+scanscam_ext = None
+has_cuda_ops = False
 
+
+def _load_extension() -> None:
+    """(Re)tries to import the extension module; sets ``scanscam_ext`` and ``has_cuda_ops``."""
+    global scanscam_ext, has_cuda_ops, _import_error
+    try:
+        import importlib
+
+        module = importlib.import_module(__package__ + ".scanscam_ext")
+    except ImportError as exc:
+        scanscam_ext, has_cuda_ops, _import_error = None, False, exc
+        return
     # Let ``import scanscam_ext`` find the same module, as code written for the reference expects.
-    sys.modules.setdefault("scanscam_ext", scanscam_ext)
-    has_cuda_ops = hasattr(scanscam_ext, "simple_linear_scan")
-except ImportError as exc:  # pragma: no cover - exercised only on a broken install
-    scanscam_ext = None
-    has_cuda_ops = False
-    _import_error = exc
+    sys.modules.setdefault("scanscam_ext", module)
+    scanscam_ext, _import_error = module, None
+    has_cuda_ops = hasattr(module, "simple_linear_scan")
+
+
+_load_extension()
 
 
 def _ext():
+    if scanscam_ext is None:
+        _load_extension()  # it may have been built since this module was imported
     if scanscam_ext is None:
         raise RuntimeError(
             "scanscam_b200: the native extension is not built or failed to load "
