@@ -204,6 +204,12 @@ size_t ssb_shard_reduce_workspace_bytes(int64_t rows, int64_t T);
 int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse, int64_t rows,
                         float *carry, void *stream);
 
+/* Self-test of the bounded-wait machinery: launches one warp that looks back at a record which
+ * is never published.  The kernel returns by itself after the poll's time limit (about one
+ * second); afterwards ssb_device_status() reports SSB_ERR_DEVICE_WAIT once and the context
+ * stays usable.  `scratch`: 32 bytes of 16-byte aligned device memory. */
+int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream);
+
 /* Synchronises the current device, returns and clears its device-side status word:
  * SSB_OK, or SSB_ERR_DEVICE_WAIT if a kernel's bounded wait (mbarrier, look-back flag)
  * gave up since the last call.  *detail (optional) receives the kernel-specific code. */

@@ -150,8 +150,8 @@ flat_fwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ valu
 // ga_t = gb_t*h_{t-1}.  The gate of every row's first element is zeroed in the recurrence so
 // that nothing leaks into the previous row; long rows are walked right to left.
 // ---------------------------------------------------------------------------------------
-template <int THREADS, int U>
-__global__ void __launch_bounds__(THREADS)
+template <int THREADS, int U, int MIN_CTAS = 0>  // 0: no register cap requested
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 flat_bwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ hout,
                 const float4 *__restrict__ gout, float4 *__restrict__ ggate,
                 float4 *__restrict__ gvalue, int64_t rows, int64_t T4,

@@ -323,6 +323,22 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
     if (timed_out && lane == 0) report_device_wait(3);
 }
 
+// One warp runs the look-back on a single predecessor record that nobody will ever publish:
+// the poll gives up after its time limit, the carry falls back to 0 and the device status word
+// is set.  Used by the self-test entry point to exercise the give-up path without hanging.
+__global__ void wait_probe_kernel(Record *rec, float *carry_out) {
+    const int lane = threadIdx.x & 31;
+    bool timed_out = false;
+    Record none;
+    none.x = none.y = 0.f;
+    none.flag = none.unused = 0u;
+    const float c = look_back(rec, 1, lane, none, timed_out);
+    if (lane == 0) {
+        *carry_out = c;
+        if (timed_out) report_device_wait(3);
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Row aggregates for sequence sharding, two launches and no waiting: every span writes its own
 // map (A, B) to the workspace, then one warp per row folds the row's spans in order.

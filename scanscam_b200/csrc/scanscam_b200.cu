@@ -229,11 +229,11 @@ int launch_flat_fwd(const float *gate, const float *value, float *out, int64_t r
     return check_launch("flat_fwd_kernel");
 }
 
-template <int THREADS, int U>
+template <int THREADS, int U, int MIN_CTAS = 0>
 int launch_flat_bwd(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
                     int64_t rows, int64_t T, const float *c_in, const float *h_prev, cudaStream_t st) {
-    auto kern = ssb::flat::flat_bwd_kernel<THREADS, U>;
-    const int grid = flat_grid<THREADS * 64 + U * 2 + 1>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
+    auto kern = ssb::flat::flat_bwd_kernel<THREADS, U, MIN_CTAS>;
+    const int grid = flat_grid<THREADS * 64 + U * 2 + 1 + MIN_CTAS * 1000000>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
     kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(h),
                                    reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(ggate),
                                    reinterpret_cast<float4 *>(gvalue), rows, T / 4, c_in, h_prev);
@@ -262,6 +262,10 @@ int dispatch_flat_bwd(int tuning, const float *gate, const float *h, const float
 #define X(ID, TH, UU) case ID: return launch_flat_bwd<TH, UU>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         SSB_FLAT_CONFIGS(X)
 #undef X
+        // the default span shape with the register budget capped so that 4 or 5 CTAs fit per SM
+        case 14: return launch_flat_bwd<128, 8, 4>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 15: return launch_flat_bwd<128, 8, 5>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case 16: return launch_flat_bwd<256, 4, 2>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         default: return fail(SSB_ERR_UNSUPPORTED, "unknown backward flat tuning id %d", tuning);
     }
 }
@@ -866,6 +870,16 @@ int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse,
     if (grid > 0x7fffffffLL) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_f32: too many rows");
     ssb::shard_carry_kernel<float><<<(int)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(aggs, n_shards, shard, reverse, rows, carry);
     return check_launch("shard_carry_kernel");
+}
+
+int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream) {
+    if (scratch == nullptr || scratch_bytes < 32 || !aligned_to(scratch, 16))
+        return fail(SSB_ERR_WORKSPACE, "ssb_selftest_wait_timeout needs 32 bytes of 16-byte aligned device scratch");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(scratch, 0, 32, st) != cudaSuccess) return check_launch("cudaMemsetAsync(scratch)");
+    auto *rec = static_cast<ssb::lookback::Record *>(scratch);
+    ssb::lookback::wait_probe_kernel<<<1, 32, 0, st>>>(rec, reinterpret_cast<float *>(rec + 1));
+    return check_launch("wait_probe_kernel");
 }
 
 int ssb_device_status(int *detail) {

@@ -398,3 +398,26 @@ def test_cfg3_long_context_properties():
     rhs = _gpu.fwd(da, db) + 2 * _gpu.fwd(da, dg)
     assert float((lhs - rhs).abs().max() / rhs.abs().max()) < 1e-5
     _gpu.device_ok()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+    """Failure detection without a fault: a look-back poll on a record nobody publishes gives up
+    after its limit (~1 s), the kernel returns, the host reads the status, later launches work."""
+    import ctypes
+    import time
+
+    lib = _native.load()
+    _gpu.device_ok()
+    scratch = torch.empty(64, dtype=torch.uint8, device="cuda")
+    t0 = time.perf_counter()
+    _native.check(lib.ssb_selftest_wait_timeout(scratch.data_ptr(), 64, _native.stream_of(scratch)))
+    detail = ctypes.c_int(0)
+    rc = lib.ssb_device_status(ctypes.byref(detail))
+    waited = time.perf_counter() - t0
+    assert rc == _native.ERR_DEVICE_WAIT and detail.value == 3
+    assert 0.5 < waited < 10.0
+    assert lib.ssb_device_status(ctypes.byref(detail)) == _native.OK   # reported once, then cleared
+    a, b, _ = make_inputs("sigmoid2", (8, 8192), seed=1)
+    h = _gpu.fwd(a.cuda(), b.cuda(), variant=LOOKBACK)
+    assert _gpu.allclose_ref(h, oracle.scan_forward(a.numpy(), b.numpy()))
+    _gpu.device_ok()
