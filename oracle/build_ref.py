@@ -13,8 +13,11 @@ from __future__ import annotations
 import os
 import sys
 
+# Where the reference checkout is mounted; override with SCANSCAM_REFERENCE_DIR.
+DEFAULT_REFERENCE = os.environ.get("SCANSCAM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 
-def build_reference(ref_root: str = "/root/reference", verbose: bool = False) -> str | None:
+
+def build_reference(ref_root: str = DEFAULT_REFERENCE, verbose: bool = False) -> str | None:
     """Returns the path of the built module, or None when the sources are absent."""
     here = os.path.dirname(os.path.abspath(__file__))
     out_dir = os.path.join(here, "_ref")

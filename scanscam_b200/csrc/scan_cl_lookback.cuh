@@ -232,7 +232,7 @@ cl_lookback_kernel(const float *__restrict__ gate, const float *__restrict__ in1
                 for (int v = 0; v < VEC; v++) { ra.v[v] = 1.f; rb.v[v] = 0.f; }
                 if (back < seq) {
                     const int64_t r = rec - 1 - back;
-                    // Lane 0 polls the tile's flag; the verdict is shared so that all channels of
+                    // Lane 0 polls the tile's flag; the outcome is shared so that all channels of
                     // the tile take the same decision, then every lane reads its channels.
                     unsigned f = (round == 0 && early_flag == 2u) ? 2u : 0u;
                     if (lane == 0 && f == 0u) {

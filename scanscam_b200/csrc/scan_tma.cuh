@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity) {
     }
 }
 
-// Warp-wide bounded wait (all 32 lanes call it); the verdict is the same in every lane, so
+// Warp-wide bounded wait (all 32 lanes call it); the outcome is the same in every lane, so
 // the callers' control flow stays convergent even when a wait gives up.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     return __all_sync(kFullMask, mbar_wait_lane(bar, parity)) != 0;

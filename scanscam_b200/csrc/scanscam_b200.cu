@@ -15,6 +15,7 @@
 
 #include "scan_cl.cuh"
 #include "scan_cl_lookback.cuh"
+#include "scan_cl_tma.cuh"
 #include "scan_common.cuh"
 #include "scan_flat.cuh"
 #include "scan_lookback.cuh"
@@ -697,6 +698,80 @@ int launch_cl2(const float *gate, const float *in1, const float *in2, float *out
     return check_launch("cl_lookback_kernel");
 }
 
+// TMA-staged channels-last kernels.  Tuning ids 32 + k -> (CC, TT, stages, out buffers) forward | backward.
+#define SSB_CL3_CONFIGS(X)                                                         \
+    X(0, 64, 64, 3, 2, 64, 64, 2, 1) X(1, 64, 32, 3, 2, 64, 32, 3, 2) X(2, 128, 32, 3, 2, 128, 32, 2, 1) \
+    X(3, 64, 128, 2, 1, 64, 64, 2, 2) X(4, 32, 64, 4, 2, 32, 64, 3, 2) X(5, 128, 64, 2, 1, 128, 32, 2, 2)
+constexpr int kCl3MinTileElems = 32 * 64;  // smallest CC*TT of the table (bounds the workspace)
+
+bool cl3_eligible(int64_t N, int64_t T, int64_t C) {
+    return C % 4 == 0 && N <= 0x7fffffffLL && T <= 0x7ffffff0LL && C <= 0x7fffffffLL;
+}
+
+int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_t C, int cc, int tt) {
+    PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
+    if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)T, (cuuint64_t)N};
+    cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)T * (cuuint64_t)C * 4};
+    cuuint32_t box[3] = {(cuuint32_t)cc, (cuuint32_t)tt, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled([N,T,C]) failed with CUresult %d", (int)r);
+    return SSB_OK;
+}
+
+template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
+int launch_cl3(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+               int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    using Cfg = ssb::cl3::Config<CC, TT, STAGES, OUTBUF, BWD>;
+    static_assert(CC * TT >= kCl3MinTileElems, "workspace bound assumes tiles of at least kCl3MinTileElems elements");
+    static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
+    auto kern = ssb::cl3::cl_tma_kernel<CC, TT, STAGES, OUTBUF, BWD>;
+    ssb::cl2::Geometry geo;
+    geo.N = N; geo.T = T; geo.C = C;
+    geo.cgroups = (C + CC - 1) / CC;
+    geo.pieces = (T + TT - 1) / TT;
+    geo.n_tiles = N * geo.cgroups * geo.pieces;
+    const size_t need = ssb::cl3::workspace_bytes(geo.n_tiles, CC);
+    if (need > workspace_bytes)
+        return fail(SSB_ERR_WORKSPACE, "channels-last TMA kernels need %zu bytes of workspace, got %zu", need, workspace_bytes);
+    CUtensorMap mg, m1, m2, mo1, mo2;
+    int rc;
+    if ((rc = make_cl_map(&mg, gate, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m1, in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m2, BWD ? in2 : in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo1, out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo2, BWD ? out2 : out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(cl_tma_kernel)");
+    static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
+    int occ = cached_occ.load(std::memory_order_relaxed);
+    if (occ == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::THREADS, Cfg::SMEM_BYTES) != cudaSuccess || occ <= 0) {
+            (void)cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ.store(occ, std::memory_order_relaxed);
+    }
+    const int64_t grid_cap = (int64_t)sm_count() * occ;
+    ssb::lookback::Order order;
+    order.rows = N * geo.cgroups;
+    order.pieces = geo.pieces;
+    int64_t k = (grid_cap + order.rows - 1) / order.rows;
+    if (k < 1) k = 1;
+    if (k > order.pieces) k = order.pieces;
+    order.k = k;
+    order.wave = order.rows * k;
+    const int64_t tickets = ((order.pieces + k - 1) / k) * order.wave;
+    const int grid = (int)(tickets < grid_cap ? tickets : grid_cap);
+    if (cudaMemsetAsync(workspace, 0, ssb::cl3::maps_offset(geo.n_tiles), st) != cudaSuccess)
+        return check_launch("cudaMemsetAsync(workspace)");
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, geo, order, static_cast<unsigned char *>(workspace));
+    return check_launch("cl_tma_kernel");
+}
+
 template <typename real>
 int cl_fwd(const real *gate, const real *value, real *out, int64_t N, int64_t T, int64_t C, void *stream) {
     int64_t n;
@@ -764,6 +839,12 @@ size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C) {
         const size_t b = ssb::cl2::workspace_bytes(tiles, vec);
         need = b > need ? b : need;
     }
+    for (int cc : {32, 64, 128}) {  // TMA-staged tiles: at least kCl3MinTileElems elements each
+        const int tt = kCl3MinTileElems / cc;
+        const int64_t tiles = N * ((C + cc - 1) / cc) * ((T + tt - 1) / tt);
+        const size_t b = ssb::cl3::workspace_bytes(tiles, cc);
+        need = b > need ? b : need;
+    }
     return need;
 }
 
@@ -782,6 +863,16 @@ int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, in
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16) &&
                      !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) >= 32) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        switch ((t_cl_tuning & 0xff) - 32) {
+#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO) case ID: return launch_cl3<FC, FT, FS, FO, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
+            SSB_CL3_CONFIGS(X)
+#undef X
+            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last TMA tuning id %d", t_cl_tuning);
+        }
+    }
     switch (t_cl_tuning & 0xff) {
 #define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st) \
                                               : launch_cl2<1, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
@@ -806,6 +897,16 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                      aligned_to(ggate, 16) && aligned_to(gvalue, 16) && !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) >= 32) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        switch ((t_cl_tuning & 0xff) - 32) {
+#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO) case ID: return launch_cl3<BC, BT, BS, BO, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
+            SSB_CL3_CONFIGS(X)
+#undef X
+            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last TMA tuning id %d", t_cl_tuning);
+        }
+    }
     switch (t_cl_tuning & 0xff) {
 #define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st) \
                                               : launch_cl2<1, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);

@@ -1,6 +1,7 @@
 """Generate the golden vectors in this directory by running the reference itself.
 
-Run where a checkout of unixpickle/scanscam is available (default /root/reference) and
+Run where a checkout of unixpickle/scanscam is available (path as first argument, or the
+environment variable SCANSCAM_REFERENCE_DIR) and
 after ``python oracle/build_ref.py`` has compiled its CPU extension:
 
     python tests/golden/make_golden.py [path-to-reference]
@@ -113,4 +114,7 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    sys.path.insert(0, REPO)
+    from oracle.build_ref import DEFAULT_REFERENCE
+
+    main(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE)

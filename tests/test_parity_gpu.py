@@ -81,7 +81,10 @@ def test_channels_last_with_scratch(shape, gates):
     h_ref = oracle.scan_forward_channels_last(an, bn)
     ga_ref, gb_ref = oracle.scan_backward_channels_last(an, h_ref, gn)
     da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
-    for scratch in (True, 12, 7, False):  # default tile, two other tile shapes, plain kernels
+    modes = [True, 12, 7, False]  # look-back: default tile and two other tile shapes; plain kernels
+    if shape[2] % 4 == 0:
+        modes += [32, 33, 34, 35, 36, 37]  # TMA-staged tiles, every tile shape of the table
+    for scratch in modes:
         h = _gpu.cl_fwd(da, db, scratch=scratch)
         ga, gb = _gpu.cl_bwd(da, dh, dg, scratch=scratch)
         for got, ref, name in ((h, h_ref, "h"), (gb, gb_ref, "gb"), (ga, ga_ref, "ga")):
