@@ -49,7 +49,8 @@ typedef enum ssb_variant {
     SSB_VARIANT_WARP = 1,    /* one warp per row, register-resident, any T / any alignment */
     SSB_VARIANT_TMA = 2,     /* TMA-staged shared-memory tiles; needs T % 32 == 0, 16-B aligned base */
     SSB_VARIANT_LOOKBACK = 3, /* T split across CTAs with decoupled look-back; needs a workspace */
-    SSB_VARIANT_FLAT = 4     /* memcpy-like sweep, CTA-wide scan of 16 KB spans; needs T % 4 == 0, 16-B aligned base */
+    SSB_VARIANT_FLAT = 4,    /* memcpy-like sweep, CTA-wide scan of 16 KB spans; needs T % 4 == 0, 16-B aligned base */
+    SSB_VARIANT_FLAT_ANY = 5 /* the same sweep with per-element row boundaries: any T, 16-B aligned base */
 } ssb_variant_t;
 
 /* Library version (major*10000 + minor*100 + patch). */

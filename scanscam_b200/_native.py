@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libscanscam_b200.so")
 
 OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED = range(7)
-VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK, VARIANT_FLAT = range(5)
+VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK, VARIANT_FLAT, VARIANT_FLAT_ANY = range(6)
 
 _p, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 

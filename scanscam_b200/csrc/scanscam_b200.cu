@@ -18,6 +18,7 @@
 #include "scan_cl_tma.cuh"
 #include "scan_common.cuh"
 #include "scan_flat.cuh"
+#include "scan_flat_any.cuh"
 #include "scan_lookback.cuh"
 #include "scan_tma.cuh"
 #include "scan_warp.cuh"
@@ -241,6 +242,26 @@ int launch_flat_bwd(const float *gate, const float *h, const float *gout, float 
     return check_launch("flat_bwd_kernel");
 }
 
+// Flat sweep with per-element row boundaries (any T).
+bool flat_any_eligible(int64_t rows, int64_t T) { return T >= 1 && T <= 0x3ffffff0LL && rows * T < (int64_t)1 << 42; }
+
+template <int THREADS, int U, bool BWD>
+int launch_flat_any(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
+                    int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
+    const int64_t rpu = ssb::flat_any::rows_per_unit<THREADS * U>(T);
+    const int64_t units = (rows + rpu - 1) / rpu;
+    if constexpr (!BWD) {
+        auto kern = ssb::flat_any::flat_any_fwd_kernel<THREADS, U>;
+        const int grid = flat_grid<400000 + THREADS * 64 + U * 2>(kern, THREADS, units);
+        kern<<<grid, THREADS, 0, st>>>(gate, in1, out1, rows, T, carry_a);
+    } else {
+        auto kern = ssb::flat_any::flat_any_bwd_kernel<THREADS, U>;
+        const int grid = flat_grid<400000 + THREADS * 64 + U * 2 + 1>(kern, THREADS, units);
+        kern<<<grid, THREADS, 0, st>>>(gate, in1, in2, out1, out2, rows, T, carry_a, carry_b);
+    }
+    return check_launch("flat_any_kernel");
+}
+
 // Tuning table of the flat family: id -> (threads per CTA, float4s per thread).
 #define SSB_FLAT_CONFIGS(X) \
     X(0, 256, 4) X(1, 512, 2) X(2, 1024, 1) X(3, 256, 2) X(4, 128, 4) X(5, 512, 1) X(6, 128, 8) \
@@ -417,7 +438,8 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 //     rows; without scratch the flat family walks each row with one CTA.
 //   * very long rows with 1024 or more of them: the TMA ring (one warp per row, 2-stage ring,
 //     8 warps per CTA) is 3-7 % ahead of look-back there and needs no scratch.
-//   * anything else (odd T, unaligned views) -> one warp per row.
+//   * odd T on aligned tensors -> the per-element flat sweep or one warp per row, by length;
+//     unaligned views and fp64 -> one warp per row.
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
@@ -425,6 +447,10 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
         if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);
         return SSB_VARIANT_FLAT | (6 << 8);
     }
+    // Odd T: the per-element flat sweep (256 threads x 4 float4s) beats one warp per row for short
+    // rows (a warp is mostly idle below ~384 steps) and for rows longer than a span; in between
+    // the warp kernels are 10-30 % faster.
+    if (all_aligned16 && flat_any_eligible(rows, T) && (T < 384 || T > 4608)) return SSB_VARIANT_FLAT_ANY | (1 << 8);
     return SSB_VARIANT_WARP;
 }
 
@@ -490,6 +516,12 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
                 return fail(SSB_ERR_UNSUPPORTED, "flat forward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
+        case SSB_VARIANT_FLAT_ANY:
+            if (!al16 || !flat_any_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "the any-T flat forward needs 16-byte aligned tensors");
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return tuning_of(variant) == 1 ? launch_flat_any<256, 4, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st)
+                                           : launch_flat_any<128, 8, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         case SSB_VARIANT_LOOKBACK:
             if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back forward needs 16-byte aligned tensors");
             t_grid_per_sm = grid_per_sm_of(variant);
@@ -613,6 +645,12 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
                 return fail(SSB_ERR_UNSUPPORTED, "flat backward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
             t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        case SSB_VARIANT_FLAT_ANY:
+            if (!al16 || !flat_any_eligible(rows, T))
+                return fail(SSB_ERR_UNSUPPORTED, "the any-T flat backward needs 16-byte aligned tensors");
+            t_grid_per_sm = grid_per_sm_of(variant);
+            return tuning_of(variant) == 1 ? launch_flat_any<256, 4, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st)
+                                           : launch_flat_any<128, 8, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case SSB_VARIANT_LOOKBACK:
             if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back backward needs 16-byte aligned tensors");
             t_grid_per_sm = grid_per_sm_of(variant);

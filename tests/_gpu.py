@@ -8,6 +8,7 @@ from scanscam_b200 import _native
 
 AUTO, WARP, TMA, FLAT = _native.VARIANT_AUTO, _native.VARIANT_WARP, _native.VARIANT_TMA, _native.VARIANT_FLAT
 LOOKBACK = _native.VARIANT_LOOKBACK
+FLAT_ANY = _native.VARIANT_FLAT_ANY
 
 
 def lookback_variant(tuning):

@@ -11,7 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import _gpu  # noqa: E402
-from _gpu import AUTO, FLAT, LOOKBACK, TMA, WARP  # noqa: E402
+from _gpu import AUTO, FLAT, FLAT_ANY, LOOKBACK, TMA, WARP  # noqa: E402
 
 import oracle  # noqa: E402
 from scanscam_b200 import _native  # noqa: E402
@@ -39,6 +39,8 @@ def variants_for(T, dtype=torch.float32):
         v += [TMA, _gpu.tma_variant(1), _gpu.tma_variant(6)]
     if dtype == torch.float32 and T % 4 == 0:
         v += [_gpu.flat_variant(t) for t in range(7)]
+    if dtype == torch.float32:
+        v += [FLAT_ANY, FLAT_ANY | (1 << 8)]  # any T, two span shapes
     return v
 
 
@@ -125,7 +127,8 @@ def test_reference_shape_grid(shape, gates):
     _gpu.device_ok()
 
 
-@pytest.mark.parametrize("shape", [(1000, 4), (77, 100), (13, 1028), (5, 5000), (3, 4092), (2, 8196), (300, 36)])
+@pytest.mark.parametrize("shape", [(1000, 4), (77, 100), (13, 1028), (5, 5000), (3, 4092), (2, 8196), (300, 36),
+                                   (7, 3), (1000, 1), (5, 2), (33, 4097), (3, 12289), (2, 100003), (9, 4091), (700, 37)])
 def test_row_packing_shapes(shape):
     """T % 4 == 0 but not a divisor of the 4096-element span: whole rows are packed per span,
     long rows are walked in pieces with a ragged last piece."""
@@ -319,7 +322,7 @@ def test_lookback_workspace_contract():
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) & 0xff == LOOKBACK
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
     assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == FLAT
-    assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff == WARP
+    assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff in (WARP, FLAT_ANY)
     assert lib.ssb_scan_recommend(64, 65536, 1, 0, 1) & 0xff == WARP
     _gpu.device_ok()
 
