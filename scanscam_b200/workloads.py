@@ -41,6 +41,7 @@ WORKLOADS = {
     "cfg3": Workload("cfg3", (1, 1024, 1048576), "nearunit", "T", "long-context stress, near-unit gates"),
     "cfg4": Workload("cfg4", (64, 8192, 512), "sigmoid0", "rows", "wide, short sequences"),
     "cfg2q": Workload("cfg2q", (2, 2048, 4096), "sigmoid2", "rows", "a quarter of cfg2: small case for profiler captures"),
+    "cfg3q": Workload("cfg3q", (1, 64, 262144), "nearunit", "T", "64 long rows: small case of cfg3 for profiler captures"),
     "cfg5": Workload("cfg5", (16, 4096, 2048), "resets", "rows", "mixed gates with exact zeros"),
 }
 
