@@ -138,7 +138,6 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
     constexpr int CAP = THREADS * U;
     __shared__ float2 s_tot[2][NE];
     __shared__ float s_hw[2][NE];
-    __shared__ float s_carry[2];
     __shared__ int64_t s_ticket[2];
 
     unsigned long long *ticket = reinterpret_cast<unsigned long long *>(workspace);
@@ -176,7 +175,7 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
         Record early;
         early.x = early.y = 0.f;
         early.flag = early.unused = 0u;
-        if (warp == 0 && lane < seq) early = load_record(my_rec - 1 - lane);
+        if (lane < seq) early = load_record(my_rec - 1 - lane);
 
         float4 a[U], x[U], y[U];
         float edge = 0.f;
@@ -252,20 +251,16 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
         const float span_A = __shfl_sync(kFullMask, tA, BWD ? 0 : NE - 1);
         const float span_B = __shfl_sync(kFullMask, tB, BWD ? 0 : NE - 1);
 
-        // Carry entering the span.
+        // Carry entering the span.  Every warp performs the look-back for itself (the records are
+        // a few hundred bytes and sit in L2), so no warp waits at a barrier for another one's
+        // polling; only warp 0 publishes.  Warps may meet a predecessor in different states and
+        // compose the same carry in a different order: equal up to rounding.
         float carry = 0.f;
         if (seq > 0) {  // uniform for the CTA
-            if (warp == 0) {
-                if (lane == 0) store_record(my_rec, span_A, span_B, kFlagAgg);
-                // Only the pieces of this row processed before this one are predecessors.
-                const float c = look_back(my_rec - 1, seq, lane, early, timed_out);
-                if (lane == 0) {
-                    store_record(my_rec, fmaf(span_A, c, span_B), 0.f, kFlagPrefix);
-                    s_carry[buf] = c;
-                }
-            }
-            __syncthreads();
-            carry = s_carry[buf];
+            if (tid == 0) store_record(my_rec, span_A, span_B, kFlagAgg);
+            // Only the pieces of this row processed before this one are predecessors.
+            carry = look_back(my_rec - 1, seq, lane, early, timed_out);
+            if (tid == 0) store_record(my_rec, fmaf(span_A, carry, span_B), 0.f, kFlagPrefix);
         } else if (tid == 0) {
             store_record(my_rec, span_B, 0.f, kFlagPrefix);  // starts from 0: map(0) = B
         }
