@@ -132,6 +132,20 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
 int ssb_scan_fwd_f32_static(const float *gate, const float *value, float *out, int64_t rows,
                             int64_t T, const float *h_in, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * Gate logits in, sigmoid fused (no counterpart in the reference, whose callers compute
+ * gate = sigmoid(z) in a separate elementwise pass before `scan` and multiply by a(1-a) after
+ * its backward).  h_t = sigmoid(z_t) * h_{t-1} + b_t.  The backward writes the gradient with
+ * respect to z.  Saves one read and one write of a full tensor in each direction.
+ * fp32, rows layout, T % 4 == 0 and 16-byte aligned tensors (SSB_ERR_UNSUPPORTED otherwise:
+ * apply the sigmoid yourself and call ssb_scan_fwd_f32 / ssb_scan_bwd_f32).
+ * ---------------------------------------------------------------------------------- */
+int ssb_scan_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t rows,
+                             int64_t T, const float *h_in, void *stream);
+int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const float *gout,
+                             float *glogits, float *gvalue, int64_t rows, int64_t T, const float *c_in,
+                             const float *h_prev, void *stream);
+
 /* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
  * The workspace must be 256-byte aligned; its contents need not be initialised (the entry
  * point clears what it needs on the stream it launches on).  A workspace must not be shared

@@ -6,7 +6,8 @@ scanscam/op.py:13-55), ``cuda`` mirrors the reference's wrapper module (scanscam
 the extension module is importable as ``scanscam_ext``.  There is no CPU path: tensors must
 live on a CUDA device and the native libraries must be built (``python -m scanscam_b200.build``).
 """
+from .fused import scan_sigmoid_gate
 from .op import Scan, is_transpose_contig, scan
 
-__all__ = ["scan", "Scan", "is_transpose_contig"]
+__all__ = ["scan", "Scan", "is_transpose_contig", "scan_sigmoid_gate"]
 __version__ = "0.1.0"

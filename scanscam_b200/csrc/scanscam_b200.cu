@@ -661,6 +661,45 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
     }
 }
 
+int ssb_scan_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t rows, int64_t T,
+                             const float *h_in, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate_logits || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_sigmoid_fwd_f32: NULL tensor pointer");
+    if (!aligned_to(gate_logits, 16) || !aligned_to(value, 16) || !aligned_to(out, 16) || !aligned_to(h_in, 4) ||
+        !flat_eligible(rows, T))
+        return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_fwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+    t_grid_per_sm = 0;
+    auto kern = ssb::flat::flat_fwd_kernel<128, 8, true>;
+    const int grid = flat_grid<500000>(kern, 128, flat_units(rows, T / 4, 128 * 8));
+    kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(gate_logits),
+                                                             reinterpret_cast<const float4 *>(value),
+                                                             reinterpret_cast<float4 *>(out), rows, T / 4, h_in);
+    return check_launch("flat_fwd_kernel<sigmoid>");
+}
+
+int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const float *gout, float *glogits, float *gvalue,
+                             int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate_logits || !h || !gout || !glogits || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_sigmoid_bwd_f32: NULL tensor pointer");
+    if (!aligned_to(gate_logits, 16) || !aligned_to(h, 16) || !aligned_to(gout, 16) || !aligned_to(glogits, 16) ||
+        !aligned_to(gvalue, 16) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4) || !flat_eligible(rows, T))
+        return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_bwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+    t_grid_per_sm = 0;
+    auto kern = ssb::flat::flat_bwd_kernel<128, 8, 0, true>;
+    const int grid = flat_grid<500001>(kern, 128, flat_units(rows, T / 4, 128 * 8));
+    kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4 *>(gate_logits), reinterpret_cast<const float4 *>(h),
+        reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(glogits), reinterpret_cast<float4 *>(gvalue),
+        rows, T / 4, c_in, h_prev);
+    return check_launch("flat_bwd_kernel<sigmoid>");
+}
+
 int ssb_scan_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
                      int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream) {
     return ssb_scan_bwd_f32_ex(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, SSB_VARIANT_AUTO, nullptr, 0, stream);

@@ -153,6 +153,33 @@ void scan_backward_ex(torch::Tensor gate, torch::Tensor output, torch::Tensor ou
     scan_backward_impl(gate, output, outGrad, gateGradOut, valueGradOut, c_in, h_prev, variant, "scan_backward_ex");
 }
 
+// ---- gate logits in, sigmoid fused (not in the reference) --------------------------------
+void scan_sigmoid_forward(torch::Tensor logits, torch::Tensor value, torch::Tensor output) {
+    check_tensor(logits, "gate_logits");
+    TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kFloat32, "gate_logits must be 2-D float32");
+    check_same(logits, value, "value");
+    check_same(logits, output, "output");
+    c10::cuda::CUDAGuard guard(logits.device());
+    raise_on(ssb_scan_sigmoid_fwd_f32(logits.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(),
+                                      logits.size(0), logits.size(1), nullptr, current_stream()),
+             "scan_sigmoid_forward");
+}
+
+void scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output, torch::Tensor outGrad, torch::Tensor logitsGradOut,
+                           torch::Tensor valueGradOut) {
+    check_tensor(logits, "gate_logits");
+    TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kFloat32, "gate_logits must be 2-D float32");
+    check_same(logits, output, "output");
+    check_same(logits, outGrad, "outGrad");
+    check_same(logits, logitsGradOut, "logitsGradOut");
+    check_same(logits, valueGradOut, "valueGradOut");
+    c10::cuda::CUDAGuard guard(logits.device());
+    raise_on(ssb_scan_sigmoid_bwd_f32(logits.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
+                                      logitsGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), logits.size(0),
+                                      logits.size(1), nullptr, nullptr, current_stream()),
+             "scan_sigmoid_backward");
+}
+
 // ---- channels-last ---------------------------------------------------------------------
 void check_cpb(int64_t cpb) {
     // The reference asserts the same set (src/scanscam_cuda.cu:566); the value is a tuning hint
@@ -277,6 +304,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("scan_backward_ex", &scan_backward_ex, "Fused backward with optional carries and pinned kernel family",
           py::arg("gate"), py::arg("output"), py::arg("outGrad"), py::arg("gateGradOut"), py::arg("valueGradOut"),
           py::arg("c_in") = py::none(), py::arg("h_prev") = py::none(), py::arg("variant") = 0);
+    m.def("scan_sigmoid_forward", &scan_sigmoid_forward, "Forward scan with gate = sigmoid(logits) computed in the kernel");
+    m.def("scan_sigmoid_backward", &scan_sigmoid_backward, "Fused backward returning the gradient w.r.t. the gate logits");
     m.def("shard_reduce_forward", &shard_reduce_forward, "Per-row aggregate map (A, B) of a sequence shard");
     m.def("shard_reduce_backward", &shard_reduce_backward, "Per-row aggregate map (A, D) of the reverse recurrence");
     m.def("shard_carry", &shard_carry, "Fold gathered shard aggregates into the carry entering one shard");

@@ -111,6 +111,36 @@ def time_channels_last(lib, N, T, C, iters):
     return rows
 
 
+def time_fused_sigmoid(lib, rows, T, iters):
+    """Kernel times of the plain scan, the fused-sigmoid scan and the elementwise passes it replaces."""
+    z = torch.randn(rows, T, device="cuda")
+    b, g = torch.randn_like(z), torch.randn_like(z)
+    h, ga, gb, a = (torch.empty_like(z) for _ in range(4))
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    p = [t.data_ptr() for t in (z, b, g, h, ga, gb)]
+    return [
+        ("scan forward (gates given)", run(lambda: lib.ssb_scan_fwd_f32(p[0], p[1], p[3], rows, T, None, st))),
+        ("scan backward (gates given)", run(lambda: lib.ssb_scan_bwd_f32(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))),
+        ("fused forward (logits given)", run(lambda: lib.ssb_scan_sigmoid_fwd_f32(p[0], p[1], p[3], rows, T, None, st))),
+        ("fused backward (logits given)", run(lambda: lib.ssb_scan_sigmoid_bwd_f32(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))),
+        ("torch.sigmoid pass", run(lambda: torch.sigmoid(z, out=a))),
+        ("torch sigmoid-backward pass", run(lambda: torch.ops.aten.sigmoid_backward(ga, a))),
+    ]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("shapes")
@@ -121,6 +151,13 @@ def main():
     lib = _native.load()
     results = {}
     for name in args.shapes.split(","):
+        if name.startswith("fused:"):  # gate logits in: fused:ROWSxT
+            rows, T = (int(v) for v in name[6:].lower().split("x"))
+            print(f"# fused sigmoid gate, rows={rows} T={T} ({rows * T * 4 / 1e6:.0f} MB per tensor)")
+            for label, ms in time_fused_sigmoid(lib, rows, T, args.iters):
+                results[f"{name}/{label}"] = {"ms": ms}
+                print(f"{label:34s} {ms:8.4f} ms", flush=True)
+            continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))
             print(f"# channels-last [N,T,C] = {N}x{T}x{C} ({N * T * C * 4 / 1e6:.0f} MB per tensor)")

@@ -65,6 +65,8 @@ def test_cpu_tensors_are_refused_not_silently_served():
     a, b = torch.rand(4, 8), torch.rand(4, 8)
     with pytest.raises(RuntimeError, match="no CPU path"):
         scanscam_b200.scan(a, b)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        scanscam_b200.scan_sigmoid_gate(a, b)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         cuda.blocked_linear_scan_forward(a, b)
     with pytest.raises(RuntimeError, match="CUDA tensor"):

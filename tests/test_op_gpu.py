@@ -184,3 +184,28 @@ def test_scan_can_be_captured_in_a_cuda_graph():
         torch.cuda.synchronize()
         h_ref, ga_ref, gb_ref = _gpu.oracle_all(a2, b2, g2)
         assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
+
+
+@pytest.mark.parametrize("shape", [(64, 4096), (3, 5, 1024), (2, 20000), (1000, 8), (7, 1001)])
+def test_fused_sigmoid_gate_matches_unfused_oracle(shape):
+    """scan_sigmoid_gate(z, b) against the CPU oracle fed sigmoid(z) computed in fp32 on the host;
+    the last shape (T % 4 != 0) goes through the unfused composition."""
+    z, b, g = make_inputs("randn", shape, seed=61)
+    z = z * 2 + 1.5
+    T = shape[-1]
+    a = torch.sigmoid(z)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, T) for x in (a, b, g)))
+    gz_ref = ga_ref * (a * (1 - a)).reshape(-1, T).numpy()
+    dz, db = z.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    h = scanscam_b200.scan_sigmoid_gate(dz, db)
+    h.backward(g.cuda())
+    assert _gpu.max_norm_err(h.reshape(-1, T), h_ref) < 1e-4
+    assert _gpu.max_norm_err(db.grad.reshape(-1, T), gb_ref) < 1e-4
+    assert _gpu.max_norm_err(dz.grad.reshape(-1, T), gz_ref) < 1e-4
+    assert _gpu.allclose_ref(h.reshape(-1, T), h_ref, atol=1e-4, rtol=1e-4)
+    # and against the library's own unfused path
+    dz2, db2 = z.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    h2 = scanscam_b200.scan(torch.sigmoid(dz2), db2)
+    h2.backward(g.cuda())
+    assert float((h - h2).abs().max() / h2.abs().max()) < 1e-5
+    assert float((dz.grad - dz2.grad).abs().max() / dz2.grad.abs().max()) < 1e-5
