@@ -58,6 +58,7 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--e2e-steps", type=int, default=5)
+    p.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of as one CUDA graph")
     return p.parse_args()
 
 
@@ -310,12 +311,39 @@ def run_gpu_arm(args, workload):
 
     # ---- timed region: exactly K steps between barrier+synchronize, device-timed --------------
     sampler = ClockSampler(physical_gpu_index(local_rank))
+    # The K steps are recorded once into a CUDA graph and replayed as one launch (the kernels take
+    # raw pointers and a stream, so they capture like any other launch); with --no-graph, or when
+    # capture is not possible (the T-sharded path calls NCCL and allocates), they are launched one by one.
+    graph = None
+    if not args.no_graph and not t_sharded:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(stream)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    cap = torch.cuda.current_stream().cuda_stream
+                    for _ in range(args.steps):
+                        _native.check(lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local,
+                                                              None, v_fwd, ws_ptr, ws_bytes, cap))
+                        _native.check(lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
+                                                              gb.data_ptr(), rows, T_local, None, None, v_bwd, ws_ptr,
+                                                              ws_bytes, cap))
+            stream.wait_stream(side)
+            graph.replay()  # one untimed replay: instantiation and upload happen here
+            torch.cuda.synchronize()
+        except Exception as exc:  # pragma: no cover - depends on driver/torch support
+            print(f"bench.py: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+            graph = None
     sampler.start()
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_begin.record(stream)
-    for _ in range(args.steps):
-        step()
+    if graph is not None:
+        graph.replay()
+    else:
+        for _ in range(args.steps):
+            step()
     t_end.record(stream)
     barrier()
     total_ms = t_begin.elapsed_time(t_end)
@@ -413,6 +441,7 @@ def run_gpu_arm(args, workload):
                          else "rows (batch x channel) per rank, no collective"),
             "l2": "no flush: each pass streams 0.8-1.3 GB, far more than the 126 MB L2",
             "variant": args.variant,
+            "launch": "one CUDA graph of K x (forward, backward)" if graph is not None else "K x 2 stream launches",
             "kernels": (None if t_sharded else {"forward": v_fwd, "backward": v_bwd, "workspace_bytes": ws_bytes}),
         },
         "gpu_launches": launches_per_step * args.steps * world,
