@@ -197,10 +197,15 @@ bool flat_eligible(int64_t rows, int64_t T) {
 }
 
 // TAG makes one instantiation (and one cached occupancy) per kernel instantiation.
-thread_local int t_grid_per_sm = 0;  // tuning override for this call: CTAs per SM (0 = as many as fit)
+// Tuning override for the duration of one entry-point call: CTAs per SM (0 = as many as fit).
+thread_local int t_grid_per_sm = 0;
+struct GridScope {
+    explicit GridScope(int per_sm) { t_grid_per_sm = per_sm; }
+    ~GridScope() { t_grid_per_sm = 0; }
+};
 
 template <int TAG, typename K>
-int flat_grid(K kern, int threads, int64_t units) {
+int persistent_grid(K kern, int threads, int64_t units) {
     static std::atomic<int> cached_occ{0};
     int occ = cached_occ.load(std::memory_order_relaxed);
     if (occ == 0) {
@@ -225,7 +230,7 @@ template <int THREADS, int U>
 int launch_flat_fwd(const float *gate, const float *value, float *out, int64_t rows, int64_t T,
                     const float *h_in, cudaStream_t st) {
     auto kern = ssb::flat::flat_fwd_kernel<THREADS, U>;
-    const int grid = flat_grid<THREADS * 64 + U * 2>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
+    const int grid = persistent_grid<THREADS * 64 + U * 2>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
     kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(value),
                                    reinterpret_cast<float4 *>(out), rows, T / 4, h_in);
     return check_launch("flat_fwd_kernel");
@@ -235,7 +240,7 @@ template <int THREADS, int U, int MIN_CTAS = 0>
 int launch_flat_bwd(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,
                     int64_t rows, int64_t T, const float *c_in, const float *h_prev, cudaStream_t st) {
     auto kern = ssb::flat::flat_bwd_kernel<THREADS, U, MIN_CTAS>;
-    const int grid = flat_grid<THREADS * 64 + U * 2 + 1 + MIN_CTAS * 1000000>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
+    const int grid = persistent_grid<THREADS * 64 + U * 2 + 1 + MIN_CTAS * 1000000>(kern, THREADS, flat_units(rows, T / 4, THREADS * U));
     kern<<<grid, THREADS, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(h),
                                    reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(ggate),
                                    reinterpret_cast<float4 *>(gvalue), rows, T / 4, c_in, h_prev);
@@ -252,11 +257,11 @@ int launch_flat_any(const float *gate, const float *in1, const float *in2, float
     const int64_t units = (rows + rpu - 1) / rpu;
     if constexpr (!BWD) {
         auto kern = ssb::flat_any::flat_any_fwd_kernel<THREADS, U>;
-        const int grid = flat_grid<400000 + THREADS * 64 + U * 2>(kern, THREADS, units);
+        const int grid = persistent_grid<400000 + THREADS * 64 + U * 2>(kern, THREADS, units);
         kern<<<grid, THREADS, 0, st>>>(gate, in1, out1, rows, T, carry_a);
     } else {
         auto kern = ssb::flat_any::flat_any_bwd_kernel<THREADS, U>;
-        const int grid = flat_grid<400000 + THREADS * 64 + U * 2 + 1>(kern, THREADS, units);
+        const int grid = persistent_grid<400000 + THREADS * 64 + U * 2 + 1>(kern, THREADS, units);
         kern<<<grid, THREADS, 0, st>>>(gate, in1, in2, out1, out2, rows, T, carry_a, carry_b);
     }
     return check_launch("flat_any_kernel");
@@ -328,7 +333,7 @@ int launch_lookback(const float *gate, const float *in1, const float *in2, float
     ssb::lookback::Order order;
     order.rows = rows;
     order.pieces = (T4 + THREADS * U - 1) / (THREADS * U);
-    const int grid_cap = flat_grid<THREADS * 64 + U * 2 + (BWD ? 1 : 0) + 100000>(kern, THREADS, (int64_t)1 << 40);
+    const int grid_cap = persistent_grid<THREADS * 64 + U * 2 + (BWD ? 1 : 0) + 100000>(kern, THREADS, (int64_t)1 << 40);
     int64_t k = (grid_cap + rows - 1) / rows;
     if (k < 1) k = 1;
     if (k > order.pieces) k = order.pieces;
@@ -376,7 +381,7 @@ int launch_span_maps(const float *gate, const float *in1, float *agg, int64_t ro
     const int64_t T4 = T / 4;
     const int64_t pieces = (T4 + kMapsThreads * kMapsU - 1) / (kMapsThreads * kMapsU);
     auto kern = ssb::lookback::span_maps_kernel<kMapsThreads, kMapsU, BWD>;
-    const int grid = flat_grid<200000 + (BWD ? 1 : 0)>(kern, kMapsThreads, rows * pieces);
+    const int grid = persistent_grid<200000 + (BWD ? 1 : 0)>(kern, kMapsThreads, rows * pieces);
     kern<<<grid, kMapsThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1),
                                         rows, T4, pieces, static_cast<float2 *>(workspace));
     int rc = check_launch("span_maps_kernel");
@@ -501,6 +506,7 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
     if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(out, 4) || !aligned_to(h_in, 4))
         return fail(SSB_ERR_ALIGNMENT, "ssb_scan_fwd_f32: pointers must be 4-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const GridScope grid_scope(grid_per_sm_of(variant));
     const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
     if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(false, rows, T, al16);
     const int family = family_of(variant);
@@ -514,17 +520,14 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
         case SSB_VARIANT_FLAT:
             if (!al16 || !flat_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "flat forward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
-            t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
         case SSB_VARIANT_FLAT_ANY:
             if (!al16 || !flat_any_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "the any-T flat forward needs 16-byte aligned tensors");
-            t_grid_per_sm = grid_per_sm_of(variant);
             return tuning_of(variant) == 1 ? launch_flat_any<256, 4, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st)
                                            : launch_flat_any<128, 8, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         case SSB_VARIANT_LOOKBACK:
             if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back forward needs 16-byte aligned tensors");
-            t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_lookback<false>(tuning_of(variant), gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr,
                                             workspace, workspace_bytes, st);
         default:
@@ -593,7 +596,6 @@ int ssb_scan_fwd_f32_static(const float *gate, const float *value, float *out, i
                     SSB_STATIC_SCRATCH_SPANS);
     void *scratch = nullptr;
     if ((rc = static_scratch_address(&scratch)) != SSB_OK) return rc;
-    t_grid_per_sm = 0;
     // launch_lookback clears `need` bytes of the scratch on the stream (ticket counter and record
     // flags must start at zero; whatever the previous call left beyond that is never read).
     return launch_lookback<128, 8, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, scratch, need,
@@ -629,6 +631,7 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
         !aligned_to(gvalue, 4) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4))
         return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_f32: pointers must be 4-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const GridScope grid_scope(grid_per_sm_of(variant));
     const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                       aligned_to(ggate, 16) && aligned_to(gvalue, 16);
     if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(true, rows, T, al16);
@@ -643,17 +646,14 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
         case SSB_VARIANT_FLAT:
             if (!al16 || !flat_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "flat backward needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
-            t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_flat_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case SSB_VARIANT_FLAT_ANY:
             if (!al16 || !flat_any_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "the any-T flat backward needs 16-byte aligned tensors");
-            t_grid_per_sm = grid_per_sm_of(variant);
             return tuning_of(variant) == 1 ? launch_flat_any<256, 4, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st)
                                            : launch_flat_any<128, 8, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case SSB_VARIANT_LOOKBACK:
             if (!al16) return fail(SSB_ERR_UNSUPPORTED, "look-back backward needs 16-byte aligned tensors");
-            t_grid_per_sm = grid_per_sm_of(variant);
             return dispatch_lookback<true>(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev,
                                            workspace, workspace_bytes, st);
         default:
@@ -671,9 +671,8 @@ int ssb_scan_sigmoid_fwd_f32(const float *gate_logits, const float *value, float
     if (!aligned_to(gate_logits, 16) || !aligned_to(value, 16) || !aligned_to(out, 16) || !aligned_to(h_in, 4) ||
         !flat_eligible(rows, T))
         return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_fwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
-    t_grid_per_sm = 0;
     auto kern = ssb::flat::flat_fwd_kernel<128, 8, true>;
-    const int grid = flat_grid<500000>(kern, 128, flat_units(rows, T / 4, 128 * 8));
+    const int grid = persistent_grid<500000>(kern, 128, flat_units(rows, T / 4, 128 * 8));
     kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(gate_logits),
                                                              reinterpret_cast<const float4 *>(value),
                                                              reinterpret_cast<float4 *>(out), rows, T / 4, h_in);
@@ -690,9 +689,8 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
     if (!aligned_to(gate_logits, 16) || !aligned_to(h, 16) || !aligned_to(gout, 16) || !aligned_to(glogits, 16) ||
         !aligned_to(gvalue, 16) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4) || !flat_eligible(rows, T))
         return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_bwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
-    t_grid_per_sm = 0;
     auto kern = ssb::flat::flat_bwd_kernel<128, 8, 0, true>;
-    const int grid = flat_grid<500001>(kern, 128, flat_units(rows, T / 4, 128 * 8));
+    const int grid = persistent_grid<500001>(kern, 128, flat_units(rows, T / 4, 128 * 8));
     kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const float4 *>(gate_logits), reinterpret_cast<const float4 *>(h),
         reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(glogits), reinterpret_cast<float4 *>(gvalue),
@@ -760,8 +758,7 @@ int launch_cl2(const float *gate, const float *in1, const float *in2, float *out
     ssb::lookback::Order order;
     order.rows = N * geo.cgroups;
     order.pieces = geo.pieces;
-    t_grid_per_sm = 0;
-    const int grid_cap = flat_grid<300000 + VEC * 10000 + kCl2Warps * 1000 + L * 10 + (BWD ? 1 : 0)>(kern, kCl2Warps * 32, (int64_t)1 << 40);
+    const int grid_cap = persistent_grid<300000 + VEC * 10000 + kCl2Warps * 1000 + L * 10 + (BWD ? 1 : 0)>(kern, kCl2Warps * 32, (int64_t)1 << 40);
     int64_t k = (grid_cap + order.rows - 1) / order.rows;
     if (k < 1) k = 1;
     if (k > order.pieces) k = order.pieces;
