@@ -41,10 +41,10 @@ METRIC = "scan Gelem/s fwd+bwd fp32"
 BYTES_FWD, BYTES_BWD = 12, 20  # algorithmic bytes per element: read a,b write h | read a,h,g write ga,gb
 
 # DRAM traffic per element of the backward kernel measured with ncu on the full cfg2 launch
-# (dram__bytes_read.sum + dram__bytes_write.sum = 805.4 MB + 489.7 MB over 67 108 864 elements; the
+# (dram__bytes_read.sum + dram__bytes_write.sum = 805.4 MB + 493.2 MB over 67 108 864 elements; the
 # reads equal the algorithmic 12 B/element, the writes fall short of 8 B/element because the last
-# ~45 MB of results are still in L2 when the kernel ends).  See profiles/flat_kernels_cfg2.md.
-NCU_BWD_TRAFFIC_BYTES_PER_ELEM = 19.30
+# ~40 MB of results are still in L2 when the kernel ends).  See profiles/tma_flat_kernels_cfg2.md.
+NCU_BWD_TRAFFIC_BYTES_PER_ELEM = 19.35
 
 
 def parse_args():
@@ -55,6 +55,7 @@ def parse_args():
     p.add_argument("--workload", default="cfg2")
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
     p.add_argument("--variant", type=int, default=0, help="kernel family/tuning id passed to the C-ABI (0 = auto)")
+    p.add_argument("--variant-bwd", type=int, default=0, help="as --variant, for the backward only (0 = same as --variant)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--e2e-steps", type=int, default=5)
@@ -280,7 +281,7 @@ def run_gpu_arm(args, workload):
         # Kernel choice and scratch exactly as the PyTorch extension does it: ask the library, give it
         # the workspace it wants (allocated once here, outside the timed region, and reused).
         v_fwd = args.variant or lib.ssb_scan_recommend(rows, T_local, 0, 1, 1)
-        v_bwd = args.variant or lib.ssb_scan_recommend(rows, T_local, 1, 1, 1)
+        v_bwd = args.variant_bwd or args.variant or lib.ssb_scan_recommend(rows, T_local, 1, 1, 1)
         ws_bytes = max(lib.ssb_scan_workspace_bytes(rows, T_local, v_fwd),
                        lib.ssb_scan_workspace_bytes(rows, T_local, v_bwd))
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")

@@ -1,0 +1,204 @@
+// TMA-staged flat sweep for the aligned fp32 rows layout with power-of-two rows that fit a span
+// (T = 32 ... 32*LINES, T a power of two): the access pattern of scan_flat.cuh -- CTAs sweep
+// memory in consecutive spans of whole rows -- with the data movement of scan_tma.cuh.
+//
+//   * A span is LINES consecutive 128-byte lines (LINES*32 elements): R = LINES/(T/32) whole rows.
+//     The tensor is described to the TMA as [rows][T/32][32]; one `cp.async.bulk.tensor.3d` box
+//     {32, T/32, R} per input tensor brings a span into a ring stage (mbarrier completion,
+//     128-byte swizzle), up to STAGES-1 spans ahead of the arithmetic.
+//   * Thread t of the CTA owns line t: 32 consecutive elements, read as 8 conflict-free float4s.
+//     It folds them sequentially (no shuffles), a 5-step shuffle scan composes the 32 lines of a
+//     warp, the warps' totals cross through shared memory (one barrier), and the thread replays
+//     its 32 elements.  That is ~6 instructions per element against ~14 in the register kernels.
+//   * Results go to a swizzled staging tile and leave through one bulk tensor store per span.
+//   * Row starts are line starts (T % 32 == 0): the first gate of a row's first line is zeroed
+//     in the recurrence, exactly as in the other families.  The backward reads h_{t-1} of a
+//     line's first element straight from the h tile in shared memory.
+//
+// Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
+#pragma once
+
+#include <cuda.h>
+
+#include "scan_common.cuh"
+#include "scan_tma.cuh"
+
+namespace ssb {
+namespace tmaflat {
+
+template <int LINES, int STAGES, int OUTBUF, bool BWD>
+struct Config {
+    static constexpr int THREADS = LINES;
+    static constexpr int N_IN = BWD ? 3 : 2;
+    static constexpr int N_OUT = BWD ? 2 : 1;
+    static constexpr int TILE = LINES * 128;
+    static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 1024;
+    static_assert(LINES % 32 == 0 && LINES <= 256, "a span is whole warps of lines and fits a TMA box");
+};
+
+// Swizzled byte offset of float4 `j` (0..7) of line `t` inside a 1024-byte aligned tile.
+__device__ __forceinline__ uint32_t chunk_offset(int t, int j) { return (uint32_t)((t << 7) | ((j ^ (t & 7)) << 4)); }
+
+template <int LINES, int STAGES, int OUTBUF, bool BWD>
+__global__ void __launch_bounds__(LINES)
+tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
+                const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
+                const __grid_constant__ CUtensorMap map_out2, int64_t rows, int lines_per_row,
+                const float *__restrict__ carry_a,   // fwd: h_in | bwd: c_in
+                const float *__restrict__ carry_b) { // bwd: h_prev
+    using Cfg = Config<LINES, STAGES, OUTBUF, BWD>;
+    constexpr int N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT, TILE = Cfg::TILE, NW = LINES / 32;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ float2 s_tot[2][NW];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t smem0 = (tma::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t out_base = smem0 + STAGES * N_IN * TILE;
+    const uint32_t bar0 = tma::smem_u32(&full_bar[0]);
+    const int rows_per_span = LINES / lines_per_row;
+    const int64_t n_spans = (rows + rows_per_span - 1) / rows_per_span;
+    const int64_t my_spans = (int64_t)blockIdx.x < n_spans ? (n_spans - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // line of this thread inside its row, and whether it starts / ends a row
+    const int line_in_row = tid & (lines_per_row - 1);  // lines_per_row is a power of two
+    const bool row_start = line_in_row == 0, row_end = line_in_row == lines_per_row - 1;
+    const int row_in_span = tid / lines_per_row;
+
+    auto issue = [&](int64_t i) {  // thread 0: loads of this CTA's i-th span into stage i % STAGES
+        const int stage = (int)(i % STAGES);
+        const int64_t span = blockIdx.x + i * (int64_t)gridDim.x;
+        const int row0 = (int)(span * rows_per_span);
+        const uint32_t bar = bar0 + 8 * stage, dst = smem0 + stage * N_IN * TILE;
+        tma::mbar_expect_tx(bar, N_IN * TILE);
+        tma::load_box(dst, &map_gate, 0, 0, row0, bar);
+        tma::load_box(dst + TILE, &map_in1, 0, 0, row0, bar);
+        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, 0, 0, row0, bar);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) tma::mbar_init(bar0 + 8 * s, 1);
+        tma::fence_mbar_init();
+        for (int64_t i = 0; i < STAGES - 1 && i < my_spans; i++) issue(i);
+    }
+    __syncthreads();
+
+    uint32_t off[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) off[j] = chunk_offset(tid, j);
+    bool timed_out = false;
+    unsigned phase_bits = 0u;
+    int out_slot = 0, buf = 0;
+
+    for (int64_t i = 0; i < my_spans; i++) {
+        const int stage = (int)(i % STAGES);
+        const int64_t span = blockIdx.x + i * (int64_t)gridDim.x;
+        const int64_t row = span * rows_per_span + row_in_span;
+        const uint32_t in0 = smem0 + stage * N_IN * TILE;
+        if (!tma::mbar_wait_bounded(bar0 + 8 * stage, (phase_bits >> stage) & 1u)) timed_out = true;
+        phase_bits ^= 1u << stage;
+
+        float a[32], x[32], y[32];  // x: value | h ; y: unused | gout
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 va = tma::lds128(in0 + off[j]), vx = tma::lds128(in0 + TILE + off[j]);
+            a[4 * j] = va.x; a[4 * j + 1] = va.y; a[4 * j + 2] = va.z; a[4 * j + 3] = va.w;
+            x[4 * j] = vx.x; x[4 * j + 1] = vx.y; x[4 * j + 2] = vx.z; x[4 * j + 3] = vx.w;
+            if (BWD) {
+                const float4 vy = tma::lds128(in0 + 2 * TILE + off[j]);
+                y[4 * j] = vy.x; y[4 * j + 1] = vy.y; y[4 * j + 2] = vy.z; y[4 * j + 3] = vy.w;
+            }
+        }
+        float h_left = 0.f;  // backward: h just before this line's first element
+        if (BWD) {
+            if (row_start) {
+                if (carry_b != nullptr && row < rows) h_left = carry_b[row];
+            } else {
+                h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
+            }
+        }
+        // Row boundaries and caller-supplied carries.
+        if (!BWD) {
+            if (row_start) {
+                if (carry_a != nullptr && row < rows) x[0] = fmaf(a[0], carry_a[row], x[0]);
+                a[0] = 0.f;
+            }
+        } else {
+            if (row_start) a[0] = 0.f;
+            if (row_end && carry_a != nullptr && row < rows) y[31] += carry_a[row];
+            if (row >= rows) {  // rows past the end arrive as zeros; keep them inert
+#pragma unroll
+                for (int k = 0; k < 32; k++) a[k] = 0.f;
+            }
+        }
+        float A, B;
+        if (!BWD) {
+            A = a[0]; B = x[0];
+#pragma unroll
+            for (int k = 1; k < 32; k++) { B = fmaf(a[k], B, x[k]); A *= a[k]; }
+            warp_scan_forward<float>(A, B, lane);
+        } else {
+            A = 1.f; B = 0.f;
+#pragma unroll
+            for (int k = 31; k >= 0; k--) { B = a[k] * (y[k] + B); A *= a[k]; }
+            warp_scan_reverse<float>(A, B, lane);
+        }
+        if (lane == (BWD ? 0 : 31)) s_tot[buf][warp] = make_float2(A, B);
+        if (tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
+        __syncthreads();
+        // Every thread holds its span data in registers: the stage can be refilled now.
+        if (tid == 0 && i + STAGES - 1 < my_spans) issue(i + STAGES - 1);
+
+        // Start value of this warp (maps of the warps processed before it) and of this lane.
+        float wA = 1.f, wB = 0.f;
+        if (!BWD) {
+            for (int w = 0; w < warp; w++) { const float2 t = s_tot[buf][w]; wB = fmaf(t.x, wB, t.y); wA *= t.x; }
+        } else {
+            for (int w = NW - 1; w > warp; w--) { const float2 t = s_tot[buf][w]; wB = fmaf(t.x, wB, t.y); wA *= t.x; }
+        }
+        float lA = BWD ? __shfl_down_sync(kFullMask, A, 1) : __shfl_up_sync(kFullMask, A, 1);
+        float lB = BWD ? __shfl_down_sync(kFullMask, B, 1) : __shfl_up_sync(kFullMask, B, 1);
+        if (lane == (BWD ? 31 : 0)) { lA = 1.f; lB = 0.f; }
+        float s = fmaf(lA, wB, lB);  // the span starts from 0: it begins at a row start
+
+        const uint32_t ob = out_base + out_slot * N_OUT * TILE;
+        if (!BWD) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float4 o;
+                s = fmaf(a[4 * j], s, x[4 * j]); o.x = s;
+                s = fmaf(a[4 * j + 1], s, x[4 * j + 1]); o.y = s;
+                s = fmaf(a[4 * j + 2], s, x[4 * j + 2]); o.z = s;
+                s = fmaf(a[4 * j + 3], s, x[4 * j + 3]); o.w = s;
+                tma::sts128(ob + off[j], o);
+            }
+        } else {
+#pragma unroll
+            for (int j = 7; j >= 0; j--) {
+                float4 oa, og;
+                float gb;
+                gb = y[4 * j + 3] + s; s = a[4 * j + 3] * gb; og.w = gb; oa.w = gb * x[4 * j + 2];
+                gb = y[4 * j + 2] + s; s = a[4 * j + 2] * gb; og.z = gb; oa.z = gb * x[4 * j + 1];
+                gb = y[4 * j + 1] + s; s = a[4 * j + 1] * gb; og.y = gb; oa.y = gb * x[4 * j];
+                gb = y[4 * j] + s; s = a[4 * j] * gb; og.x = gb;
+                oa.x = gb * (j > 0 ? x[j > 0 ? 4 * j - 1 : 0] : h_left);
+                tma::sts128(ob + off[j], oa);
+                tma::sts128(ob + TILE + off[j], og);
+            }
+        }
+        tma::fence_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            const int row0 = (int)(span * rows_per_span);
+            tma::store_box(&map_out1, 0, 0, row0, ob);
+            if (BWD) tma::store_box(&map_out2, 0, 0, row0, ob + TILE);
+            tma::store_commit();
+        }
+        out_slot = (out_slot + 1 == OUTBUF) ? 0 : out_slot + 1;
+        buf ^= 1;
+    }
+    if (tid == 0) tma::store_wait_read<0>();
+    if (timed_out && lane == 0) report_device_wait(6);
+}
+
+}  // namespace tmaflat
+}  // namespace ssb

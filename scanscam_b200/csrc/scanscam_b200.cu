@@ -21,6 +21,7 @@
 #include "scan_flat_any.cuh"
 #include "scan_lookback.cuh"
 #include "scan_tma.cuh"
+#include "scan_tma_flat.cuh"
 #include "scan_warp.cuh"
 
 namespace {
@@ -391,6 +392,68 @@ int launch_span_maps(const float *gate, const float *in1, float *agg, int64_t ro
     return check_launch("fold_maps_kernel");
 }
 
+// ------------------------------------------------------------------------------------
+// TMA-staged flat sweep (power-of-two rows that fit a span); tuning ids 32 + k of the TMA family
+// ------------------------------------------------------------------------------------
+#define SSB_TMAFLAT_CONFIGS(X) /* id, lines, stages, out buffers (forward) | (backward) */ \
+    X(0, 128, 2, 2, 128, 2, 1) X(1, 128, 3, 2, 128, 2, 2) X(2, 64, 3, 2, 64, 3, 2) X(3, 64, 4, 2, 64, 2, 2) \
+    X(4, 128, 2, 1, 64, 2, 1) X(5, 256, 2, 1, 128, 3, 1) X(6, 32, 4, 2, 32, 4, 2)
+
+bool tmaflat_eligible(int64_t rows, int64_t T, int lines) {
+    if (T % 32 != 0 || rows > 0x7fffffffLL) return false;
+    const int64_t lpr = T / 32;
+    return lpr >= 1 && lpr <= lines && (lpr & (lpr - 1)) == 0;
+}
+
+int make_span_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, int lines) {
+    PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
+    if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    const int64_t lpr = T / 32;
+    cuuint64_t dims[3] = {32, (cuuint64_t)lpr, (cuuint64_t)rows};
+    cuuint64_t strides[2] = {128, (cuuint64_t)T * 4};
+    cuuint32_t box[3] = {32, (cuuint32_t)lpr, (cuuint32_t)(lines / lpr)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled(span) failed with CUresult %d", (int)r);
+    return SSB_OK;
+}
+
+template <int LINES, int STAGES, int OUTBUF, bool BWD>
+int launch_tmaflat(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
+                   int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
+    using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD>;
+    static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
+    if (!tmaflat_eligible(rows, T, LINES))
+        return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = 32 * 2^k <= %d (T=%lld)", LINES * 32, (long long)T);
+    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD>;
+    CUtensorMap mg, m1, m2, mo1, mo2;
+    int rc;
+    if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
+    if ((rc = make_span_map(&m1, in1, rows, T, LINES)) != SSB_OK) return rc;
+    if ((rc = make_span_map(&m2, BWD ? in2 : in1, rows, T, LINES)) != SSB_OK) return rc;
+    if ((rc = make_span_map(&mo1, out1, rows, T, LINES)) != SSB_OK) return rc;
+    if ((rc = make_span_map(&mo2, BWD ? out2 : out1, rows, T, LINES)) != SSB_OK) return rc;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(tma_flat_kernel)");
+    static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
+    int occ = cached_occ.load(std::memory_order_relaxed);
+    if (occ == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::THREADS, Cfg::SMEM_BYTES) != cudaSuccess || occ <= 0) {
+            (void)cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ.store(occ, std::memory_order_relaxed);
+    }
+    const int lpr = (int)(T / 32);
+    const int64_t spans = (rows + LINES / lpr - 1) / (LINES / lpr);
+    const int64_t cap = (int64_t)sm_count() * occ;
+    const int grid = (int)(spans < cap ? spans : cap);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, lpr, carry_a, carry_b);
+    return check_launch("tma_flat_kernel");
+}
+
 // `variant` carries the family in its low byte and a tuning id in bits 8..15 (0 = default).
 int family_of(int variant) { return variant & 0xff; }
 int tuning_of(int variant) { return (variant >> 8) & 0xff; }
@@ -436,8 +499,12 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 
 // Default kernel choice, from sweeps on B200 over T = 64 .. 16M at 67 MB .. 4 GB per tensor
 // (profiles/kernel_family_sweep_b200.md):
-//   * aligned fp32 with T % 4 == 0, rows that fit a 16 KB span (T <= 4096) -> flat, 128 threads x
-//     8 float4s: the best or within 2 % of the best in both directions at every T.
+//   * aligned fp32, T = 32 * 2^k <= 4096 (every benchmark configuration but the long-context
+//     one) -> the TMA-staged flat sweep: spans of whole rows brought in by bulk tensor copies,
+//     32 elements per thread.  Same speed as the register version below within +-1 % (203-209
+//     Gelem/s fwd+bwd on cfg2/4/5 either way), ~30 W less power, 10 % higher sustained SM clock.
+//   * other aligned fp32 with T % 4 == 0, rows that fit a 16 KB span (T <= 4096) -> flat, 128
+//     threads x 8 float4s: the best or within 2 % of the best in both directions at every T.
 //   * longer rows: look-back (same span shape) when the caller can supply scratch -- within 3 %
 //     of the best everywhere and the only family whose speed does not depend on the number of
 //     rows; without scratch the flat family walks each row with one CTA.
@@ -448,6 +515,12 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
+    if (all_aligned16 && tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr) {
+        // power-of-two rows that fit a span: the TMA-staged sweep (forward 128 lines x 2 stages;
+        // backward 128 lines x 3 stages for 4096-step rows, 64 lines x 2 stages below)
+        if (!backward) return SSB_VARIANT_TMA | (32 << 8);
+        return SSB_VARIANT_TMA | ((T > 2048 ? 37 : 36) << 8);
+    }
     if (all_aligned16 && flat_eligible(rows, T)) {
         if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);
         return SSB_VARIANT_FLAT | (6 << 8);
@@ -516,6 +589,14 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
         case SSB_VARIANT_TMA:
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA forward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            if (tuning_of(variant) >= 32) {
+                switch (tuning_of(variant) - 32) {
+#define X(ID, FL, FS, FO, BL, BS, BO) case ID: return launch_tmaflat<FL, FS, FO, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+                    SSB_TMAFLAT_CONFIGS(X)
+#undef X
+                    default: return fail(SSB_ERR_UNSUPPORTED, "unknown TMA flat tuning id %d", tuning_of(variant));
+                }
+            }
             return dispatch_tma_fwd(tuning_of(variant), gate, value, out, rows, T, h_in, st);
         case SSB_VARIANT_FLAT:
             if (!al16 || !flat_eligible(rows, T))
@@ -642,6 +723,14 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
         case SSB_VARIANT_TMA:
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA backward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            if (tuning_of(variant) >= 32) {
+                switch (tuning_of(variant) - 32) {
+#define X(ID, FL, FS, FO, BL, BS, BO) case ID: return launch_tmaflat<BL, BS, BO, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+                    SSB_TMAFLAT_CONFIGS(X)
+#undef X
+                    default: return fail(SSB_ERR_UNSUPPORTED, "unknown TMA flat tuning id %d", tuning_of(variant));
+                }
+            }
             return dispatch_tma_bwd(tuning_of(variant), gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         case SSB_VARIANT_FLAT:
             if (!al16 || !flat_eligible(rows, T))

@@ -41,6 +41,10 @@ def variants_for(T, dtype=torch.float32):
         v += [_gpu.flat_variant(t) for t in range(7)]
     if dtype == torch.float32:
         v += [FLAT_ANY, FLAT_ANY | (1 << 8)]  # any T, two span shapes
+    if dtype == torch.float32 and T % 32 == 0 and (T // 32) & (T // 32 - 1) == 0:
+        # TMA-staged flat sweep: tuning ids 32+k, usable while a row fits the id's span (lines of 32)
+        min_lines = [128, 128, 64, 64, 64, 128, 32]
+        v += [_gpu.tma_variant(32 + k) for k, lines in enumerate(min_lines) if T // 32 <= lines]
     return v
 
 
@@ -200,7 +204,8 @@ def test_edge_shapes_and_errors():
 
 
 @pytest.mark.parametrize("gates,shape", [("sigmoid2", (64, 4096)), ("resets", (40, 2048)), ("nearunit", (4, 65536))])
-@pytest.mark.parametrize("variant", [WARP, TMA, FLAT, _gpu.flat_variant(2), _gpu.flat_variant(3)])
+@pytest.mark.parametrize("variant", [WARP, TMA, FLAT, _gpu.flat_variant(2), _gpu.flat_variant(3), _gpu.tma_variant(32),
+                                     _gpu.tma_variant(34)])
 def test_shard_carries(gates, shape, variant):
     """A call with carry-in must continue a scan exactly where another call stopped."""
     a, b, g = make_inputs(gates, shape, seed=9)
@@ -210,7 +215,11 @@ def test_shard_carries(gates, shape, variant):
     da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
     left = [x[:, :cut].contiguous() for x in (da, db, dg, dh)]
     right = [x[:, cut:].contiguous() for x in (da, db, dg, dh)]
-    h_l = _gpu.fwd(left[0], left[1], variant=variant)
+    try:
+        h_l = _gpu.fwd(left[0], left[1], variant=variant)
+    except _native.NativeError as e:  # the TMA flat sweep only takes rows that fit one span
+        assert e.status == _native.ERR_UNSUPPORTED and (variant >> 8) >= 32
+        pytest.skip("shape outside this variant's range")
     h_r = _gpu.fwd(right[0], right[1], h_in=h_l[:, -1].contiguous(), variant=variant)
     assert _gpu.max_norm_err(torch.cat([h_l, h_r], 1), h_ref) < TOL
     ga_r, gb_r = _gpu.bwd(right[0], right[3], right[2], h_prev=left[3][:, -1].contiguous(), variant=variant)
@@ -321,7 +330,8 @@ def test_lookback_workspace_contract():
     # the recommendation: look-back only for long rows and only when the caller can supply scratch
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) & 0xff == LOOKBACK
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
-    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == FLAT
+    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
+    assert lib.ssb_scan_recommend(64, 4092, 0, 1, 1) & 0xff == FLAT
     assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff in (WARP, FLAT_ANY)
     assert lib.ssb_scan_recommend(64, 65536, 1, 0, 1) & 0xff == WARP
     _gpu.device_ok()
