@@ -241,7 +241,6 @@ flat_any_bwd_kernel(const float *__restrict__ gate, const float *__restrict__ ho
 #pragma unroll
             for (int j = 0; j < U; j++) {
                 float *av = reinterpret_cast<float *>(&a[j]), *gv = reinterpret_cast<float *>(&g[j]);
-#pragma unroll
                 const int64_t e4 = (first_vec + j * THREADS + tid) * 4;
 #pragma unroll
                 for (int k = 0; k < 4; k++) {

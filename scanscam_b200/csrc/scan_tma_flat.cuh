@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include "scan_common.cuh"
+#include "scan_flat.cuh"
 #include "scan_tma.cuh"
 
 namespace ssb {
@@ -39,7 +40,9 @@ struct Config {
 // Swizzled byte offset of float4 `j` (0..7) of line `t` inside a 1024-byte aligned tile.
 __device__ __forceinline__ uint32_t chunk_offset(int t, int j) { return (uint32_t)((t << 7) | ((j ^ (t & 7)) << 4)); }
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD>
+// SIGMOID: the gate tensor holds logits z; the gate is sigmoid(z) (flat::sigmoidf) and the
+// backward's first output is the gradient with respect to z.
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false>
 __global__ void __launch_bounds__(LINES)
 tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                 const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
@@ -102,6 +105,10 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         for (int j = 0; j < 8; j++) {
             const float4 va = tma::lds128(in0 + off[j]), vx = tma::lds128(in0 + TILE + off[j]);
             a[4 * j] = va.x; a[4 * j + 1] = va.y; a[4 * j + 2] = va.z; a[4 * j + 3] = va.w;
+            if (SIGMOID) {
+#pragma unroll
+                for (int k = 0; k < 4; k++) a[4 * j + k] = flat::sigmoidf(a[4 * j + k]);
+            }
             x[4 * j] = vx.x; x[4 * j + 1] = vx.y; x[4 * j + 2] = vx.z; x[4 * j + 3] = vx.w;
             if (BWD) {
                 const float4 vy = tma::lds128(in0 + 2 * TILE + off[j]);
@@ -116,6 +123,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
                 h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
             }
         }
+        const float a_first = a[0];  // the line's first gate before a row start zeroes it
         // Row boundaries and caller-supplied carries.
         if (!BWD) {
             if (row_start) {
@@ -181,6 +189,13 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
                 gb = y[4 * j + 1] + s; s = a[4 * j + 1] * gb; og.y = gb; oa.y = gb * x[4 * j];
                 gb = y[4 * j] + s; s = a[4 * j] * gb; og.x = gb;
                 oa.x = gb * (j > 0 ? x[j > 0 ? 4 * j - 1 : 0] : h_left);
+                if (SIGMOID) {  // d sigmoid(z) / dz = a (1 - a)
+                    const float a0 = j > 0 ? a[4 * j] : a_first;
+                    oa.x *= a0 * (1.f - a0);
+                    oa.y *= a[4 * j + 1] * (1.f - a[4 * j + 1]);
+                    oa.z *= a[4 * j + 2] * (1.f - a[4 * j + 2]);
+                    oa.w *= a[4 * j + 3] * (1.f - a[4 * j + 3]);
+                }
                 tma::sts128(ob + off[j], oa);
                 tma::sts128(ob + TILE + off[j], og);
             }

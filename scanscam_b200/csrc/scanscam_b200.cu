@@ -132,6 +132,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
 }
 
+// cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread.  A
+// thread that has made no runtime call yet (an autograd worker reaching a launch function whose
+// lookups are all cached) has none: bind the device's primary context and encode again.
+template <typename... Args>
+CUresult encode_tiled(PFN_cuTensorMapEncodeTiled_v12000 enc, Args... args) {
+    CUresult r = enc(args...);
+    if (r == CUDA_ERROR_INVALID_CONTEXT || r == CUDA_ERROR_NOT_INITIALIZED) {
+        if (cudaFree(nullptr) != cudaSuccess) (void)cudaGetLastError();
+        r = enc(args...);
+    }
+    return r;
+}
+
 bool tma_eligible(int64_t rows, int64_t T) {
     return T % 32 == 0 && T >= 32 && rows <= 0x7fffffffLL && T / 32 <= 0x7fffffffLL;
 }
@@ -145,7 +158,7 @@ int make_rows_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, i
     cuuint64_t strides[2] = {128, (cuuint64_t)T * 4};
     cuuint32_t box[3] = {32, (cuuint32_t)lines, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box,
+    CUresult r = encode_tiled(enc, map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box,
                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -413,21 +426,21 @@ int make_span_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, i
     cuuint64_t strides[2] = {128, (cuuint64_t)T * 4};
     cuuint32_t box[3] = {32, (cuuint32_t)lpr, (cuuint32_t)(lines / lpr)};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+    CUresult r = encode_tiled(enc, map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled(span) failed with CUresult %d", (int)r);
     return SSB_OK;
 }
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD>
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false>
 int launch_tmaflat(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
                    int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
     using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD>;
     static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
     if (!tmaflat_eligible(rows, T, LINES))
         return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = 32 * 2^k <= %d (T=%lld)", LINES * 32, (long long)T);
-    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD>;
+    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID>;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
@@ -760,6 +773,9 @@ int ssb_scan_sigmoid_fwd_f32(const float *gate_logits, const float *value, float
     if (!aligned_to(gate_logits, 16) || !aligned_to(value, 16) || !aligned_to(out, 16) || !aligned_to(h_in, 4) ||
         !flat_eligible(rows, T))
         return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_fwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+    if (tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr)
+        return launch_tmaflat<128, 2, 2, false, true>(gate_logits, value, nullptr, out, nullptr, rows, T, h_in, nullptr,
+                                                      static_cast<cudaStream_t>(stream));
     auto kern = ssb::flat::flat_fwd_kernel<128, 8, true>;
     const int grid = persistent_grid<500000>(kern, 128, flat_units(rows, T / 4, 128 * 8));
     kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(gate_logits),
@@ -778,6 +794,11 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
     if (!aligned_to(gate_logits, 16) || !aligned_to(h, 16) || !aligned_to(gout, 16) || !aligned_to(glogits, 16) ||
         !aligned_to(gvalue, 16) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4) || !flat_eligible(rows, T))
         return fail(SSB_ERR_UNSUPPORTED, "ssb_scan_sigmoid_bwd_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+    if (tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        return T > 2048 ? launch_tmaflat<128, 3, 1, true, true>(gate_logits, h, gout, glogits, gvalue, rows, T, c_in, h_prev, st)
+                        : launch_tmaflat<64, 2, 1, true, true>(gate_logits, h, gout, glogits, gvalue, rows, T, c_in, h_prev, st);
+    }
     auto kern = ssb::flat::flat_bwd_kernel<128, 8, 0, true>;
     const int grid = persistent_grid<500001>(kern, 128, flat_units(rows, T / 4, 128 * 8));
     kern<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -878,7 +899,7 @@ int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_
     cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)T * (cuuint64_t)C * 4};
     cuuint32_t box[3] = {(cuuint32_t)cc, (cuuint32_t)tt, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+    CUresult r = encode_tiled(enc, map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled([N,T,C]) failed with CUresult %d", (int)r);

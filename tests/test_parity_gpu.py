@@ -437,3 +437,60 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
     h = _gpu.fwd(a.cuda(), b.cuda(), variant=LOOKBACK)
     assert _gpu.allclose_ref(h, oracle.scan_forward(a.numpy(), b.numpy()))
     _gpu.device_ok()
+
+
+@pytest.mark.parametrize("shape", [(40, 4096), (130, 2048), (77, 256), (300, 32), (9, 8192), (50, 24)])
+def test_fused_sigmoid_entry_points_with_carries(shape):
+    """ssb_scan_sigmoid_{fwd,bwd}_f32 (logits in, gradient w.r.t. logits out) with a carry entering
+    every row from both sides, against the oracle fed sigmoid(z) computed on the host.  The shapes
+    cover both kernel families behind the entry points."""
+    rows, T = shape
+    z, b, g = make_inputs("randn", shape, seed=71)
+    z = z * 2 + 1.0
+    a = torch.sigmoid(z)
+    carry = torch.randn(rows)
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy(), h_in=carry.numpy())
+    ga_ref, gb_ref = oracle.scan_backward(a.numpy(), h_ref, g.numpy(), gb_in=carry.numpy(), h_prev=carry.numpy())
+    gz_ref = ga_ref * (a * (1 - a)).numpy()
+    lib = _native.load()
+    dz, db, dg, dc = z.cuda(), b.cuda(), g.cuda(), carry.cuda()
+    h, gz, gb = torch.empty_like(dz), torch.empty_like(dz), torch.empty_like(dz)
+    st = _native.stream_of(dz)
+    _native.check(lib.ssb_scan_sigmoid_fwd_f32(dz.data_ptr(), db.data_ptr(), h.data_ptr(), rows, T, dc.data_ptr(), st))
+    _native.check(lib.ssb_scan_sigmoid_bwd_f32(dz.data_ptr(), h.data_ptr(), dg.data_ptr(), gz.data_ptr(), gb.data_ptr(),
+                                               rows, T, dc.data_ptr(), dc.data_ptr(), st))
+    _gpu.device_ok()
+    assert _gpu.max_norm_err(h, h_ref) < 1e-4
+    assert _gpu.max_norm_err(gb, gb_ref) < 1e-4
+    assert _gpu.max_norm_err(gz, gz_ref) < 1e-4
+
+
+def test_tensor_map_paths_work_from_a_fresh_thread():
+    """A thread that has made no CUDA runtime call of its own (an autograd worker, say) reaches the
+    bulk-tensor kernels with every host-side lookup already cached; the tensor maps must still
+    encode there."""
+    import threading
+    a, b, g = make_inputs("sigmoid2", (48, 4096), seed=81)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    for variant in (AUTO, _gpu.tma_variant(0)):
+        _gpu.fwd(da, db, variant=variant)  # warm every cache on this thread
+        _gpu.bwd(da, _gpu.fwd(da, db), dg, variant=variant)
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def work():
+        try:
+            for variant in (AUTO, _gpu.tma_variant(0)):
+                h = _gpu.fwd(da, db, variant=variant)
+                results[variant] = (h,) + _gpu.bwd(da, h, dg, variant=variant)
+        except Exception as exc:  # noqa: BLE001 - reported by the assertion below
+            errors.append(exc)
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert not errors, errors
+    torch.cuda.synchronize()
+    for h, ga, gb in results.values():
+        assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
