@@ -146,6 +146,25 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
                              float *glogits, float *gvalue, int64_t rows, int64_t T, const float *c_in,
                              const float *h_prev, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * Backward that recomputes h (no counterpart in the reference, whose op.Scan.forward saves both
+ * `gate` and `output` for the backward, scanscam/op.py:36).  Takes what the forward took --
+ * gate a, value b, and the carry h_in entering each row (NULL = 0) -- plus gout and c_in, and
+ * returns the same two gradients as ssb_scan_bwd_f32, so that a caller can drop h between the
+ * passes (4 bytes per element of activation memory).
+ *   - rows with T = 32 * 2^k <= 4096: one kernel rebuilds h for each span on the fly; it reads
+ *     a, b, gout and writes the two gradients, the same 20 bytes per element as the ordinary
+ *     backward.  No workspace.
+ *   - any other shape: the forward kernel writes h into the caller's workspace and the ordinary
+ *     backward reads it back (32 bytes per element in total); the workspace holds h for the
+ *     duration of the call only.
+ * fp32, rows layout, tensors 16-byte aligned.
+ * ---------------------------------------------------------------------------------- */
+size_t ssb_scan_bwd_recompute_workspace_bytes(int64_t rows, int64_t T);
+int ssb_scan_bwd_recompute_f32(const float *gate, const float *value, const float *gout, float *ggate,
+                               float *gvalue, int64_t rows, int64_t T, const float *h_in,
+                               const float *c_in, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
  * The workspace must be 256-byte aligned; its contents need not be initialised (the entry
  * point clears what it needs on the stream it launches on).  A workspace must not be shared

@@ -8,6 +8,7 @@ live on a CUDA device and the native libraries must be built (``python -m scansc
 """
 from .fused import scan_sigmoid_gate
 from .op import Scan, is_transpose_contig, scan
+from .recompute import ScanRecompute, scan_recompute
 
-__all__ = ["scan", "Scan", "is_transpose_contig", "scan_sigmoid_gate"]
+__all__ = ["scan", "Scan", "is_transpose_contig", "scan_sigmoid_gate", "scan_recompute", "ScanRecompute"]
 __version__ = "0.1.0"

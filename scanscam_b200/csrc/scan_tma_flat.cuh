@@ -42,7 +42,11 @@ __device__ __forceinline__ uint32_t chunk_offset(int t, int j) { return (uint32_
 
 // SIGMOID: the gate tensor holds logits z; the gate is sigmoid(z) (flat::sigmoidf) and the
 // backward's first output is the gradient with respect to z.
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false>
+// RECOMPUTE (backward only): the second input is the forward's value tensor b instead of its output
+// h; the kernel rebuilds h for the span with a forward scan of (a, b) -- both scans share the one
+// barrier -- so a caller need not keep h between the passes.  carry_b is then the h entering each
+// row (the forward's h_in).
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false>
 __global__ void __launch_bounds__(LINES)
 tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                 const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
@@ -54,6 +58,8 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES];
     __shared__ float2 s_tot[2][NW];
+    __shared__ float2 s_fwd[RECOMPUTE ? 2 : 1][NW];  // RECOMPUTE: the forward scan's warp totals
+    static_assert(BWD || !RECOMPUTE, "only the backward recomputes");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t smem0 = (tma::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -119,7 +125,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         if (BWD) {
             if (row_start) {
                 if (carry_b != nullptr && row < rows) h_left = carry_b[row];
-            } else {
+            } else if (!RECOMPUTE) {
                 h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
             }
         }
@@ -131,6 +137,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
                 a[0] = 0.f;
             }
         } else {
+            if (RECOMPUTE && row_start) x[0] = fmaf(a[0], h_left, x[0]);
             if (row_start) a[0] = 0.f;
             if (row_end && carry_a != nullptr && row < rows) y[31] += carry_a[row];
             if (row >= rows) {  // rows past the end arrive as zeros; keep them inert
@@ -139,6 +146,14 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
             }
         }
         float A, B;
+        float FA = 1.f, FB = 0.f;  // RECOMPUTE: this line's map in the forward direction
+        if (RECOMPUTE) {
+            FA = a[0]; FB = x[0];
+#pragma unroll
+            for (int k = 1; k < 32; k++) { FB = fmaf(a[k], FB, x[k]); FA *= a[k]; }
+            warp_scan_forward<float>(FA, FB, lane);
+            if (lane == 31) s_fwd[buf][warp] = make_float2(FA, FB);
+        }
         if (!BWD) {
             A = a[0]; B = x[0];
 #pragma unroll
@@ -167,6 +182,16 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         float lB = BWD ? __shfl_down_sync(kFullMask, B, 1) : __shfl_up_sync(kFullMask, B, 1);
         if (lane == (BWD ? 31 : 0)) { lA = 1.f; lB = 0.f; }
         float s = fmaf(lA, wB, lB);  // the span starts from 0: it begins at a row start
+        if (RECOMPUTE) {  // turn x from b into h: h just before this line, then the line itself
+            float fB = 0.f;
+            for (int w = 0; w < warp; w++) { const float2 t = s_fwd[buf][w]; fB = fmaf(t.x, fB, t.y); }
+            float pA = __shfl_up_sync(kFullMask, FA, 1), pB = __shfl_up_sync(kFullMask, FB, 1);
+            if (lane == 0) { pA = 1.f; pB = 0.f; }
+            float hp = fmaf(pA, fB, pB);
+            if (!row_start) h_left = hp;
+#pragma unroll
+            for (int k = 0; k < 32; k++) { hp = fmaf(a[k], hp, x[k]); x[k] = hp; }
+        }
 
         const uint32_t ob = out_base + out_slot * N_OUT * TILE;
         if (!BWD) {

@@ -433,14 +433,14 @@ int make_span_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, i
     return SSB_OK;
 }
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false>
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false>
 int launch_tmaflat(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
                    int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
     using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD>;
     static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
     if (!tmaflat_eligible(rows, T, LINES))
         return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = 32 * 2^k <= %d (T=%lld)", LINES * 32, (long long)T);
-    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID>;
+    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID, RECOMPUTE>;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
@@ -806,6 +806,49 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
         reinterpret_cast<const float4 *>(gout), reinterpret_cast<float4 *>(glogits), reinterpret_cast<float4 *>(gvalue),
         rows, T / 4, c_in, h_prev);
     return check_launch("flat_bwd_kernel<sigmoid>");
+}
+
+// ---- backward that recomputes h -----------------------------------------------------------
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static bool recompute_in_kernel(int64_t rows, int64_t T) { return tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr; }
+
+size_t ssb_scan_bwd_recompute_workspace_bytes(int64_t rows, int64_t T) {
+    int64_t n;
+    if (check_shape(rows, T, &n) != SSB_OK || n == 0 || recompute_in_kernel(rows, T)) return 0;
+    const size_t fwd_ws = ssb_scan_workspace_bytes(rows, T, pick_variant(false, rows, T, true, true));
+    const size_t bwd_ws = ssb_scan_workspace_bytes(rows, T, pick_variant(true, rows, T, true, true));
+    return align256((size_t)rows * (size_t)T * 4) + (fwd_ws > bwd_ws ? fwd_ws : bwd_ws);
+}
+
+int ssb_scan_bwd_recompute_f32(const float *gate, const float *value, const float *gout, float *ggate, float *gvalue,
+                               int64_t rows, int64_t T, const float *h_in, const float *c_in, void *workspace,
+                               size_t workspace_bytes, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !value || !gout || !ggate || !gvalue)
+        return fail(SSB_ERR_BAD_ARG, "ssb_scan_bwd_recompute_f32: NULL tensor pointer");
+    if (!aligned_to(gate, 16) || !aligned_to(value, 16) || !aligned_to(gout, 16) || !aligned_to(ggate, 16) ||
+        !aligned_to(gvalue, 16) || !aligned_to(h_in, 4) || !aligned_to(c_in, 4))
+        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_recompute_f32: tensors must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (recompute_in_kernel(rows, T))
+        return T > 2048 ? launch_tmaflat<128, 3, 1, true, false, true>(gate, value, gout, ggate, gvalue, rows, T, c_in, h_in, st)
+                        : launch_tmaflat<64, 2, 1, true, false, true>(gate, value, gout, ggate, gvalue, rows, T, c_in, h_in, st);
+    // Other shapes: the forward kernel rebuilds h into the workspace, the ordinary backward reads it.
+    const size_t need = ssb_scan_bwd_recompute_workspace_bytes(rows, T);
+    if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 256))
+        return fail(SSB_ERR_WORKSPACE, "ssb_scan_bwd_recompute_f32 needs a 256-byte aligned workspace of %zu bytes (got %zu)",
+                    need, workspace_bytes);
+    float *h = static_cast<float *>(workspace);
+    const size_t h_bytes = align256((size_t)n * 4);
+    void *inner = static_cast<char *>(workspace) + h_bytes;
+    const size_t inner_bytes = workspace_bytes - h_bytes;
+    rc = ssb_scan_fwd_f32_ex(gate, value, h, rows, T, h_in, pick_variant(false, rows, T, true, true), inner, inner_bytes, stream);
+    if (rc != SSB_OK) return rc;
+    return ssb_scan_bwd_f32_ex(gate, h, gout, ggate, gvalue, rows, T, c_in, h_in, pick_variant(true, rows, T, true, true),
+                               inner, inner_bytes, stream);
 }
 
 int ssb_scan_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue,

@@ -180,6 +180,26 @@ void scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output, torch::Te
              "scan_sigmoid_backward");
 }
 
+// ---- backward that recomputes h from (gate, value) (not in the reference) -----------------
+void scan_backward_recompute(torch::Tensor gate, torch::Tensor value, torch::Tensor outGrad, torch::Tensor gateGradOut,
+                             torch::Tensor valueGradOut) {
+    check_tensor(gate, "gate");
+    TORCH_CHECK(gate.dim() == 2 && gate.scalar_type() == torch::kFloat32, "gate must be 2-D float32");
+    check_same(gate, value, "value");
+    check_same(gate, outGrad, "outGrad");
+    check_same(gate, gateGradOut, "gateGradOut");
+    check_same(gate, valueGradOut, "valueGradOut");
+    c10::cuda::CUDAGuard guard(gate.device());
+    const size_t ws_bytes = ssb_scan_bwd_recompute_workspace_bytes(gate.size(0), gate.size(1));
+    torch::Tensor ws;
+    if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+    raise_on(ssb_scan_bwd_recompute_f32(gate.data_ptr<float>(), value.data_ptr<float>(), outGrad.data_ptr<float>(),
+                                        gateGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), gate.size(0),
+                                        gate.size(1), nullptr, nullptr, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                                        current_stream()),
+             "scan_backward_recompute");
+}
+
 // ---- channels-last ---------------------------------------------------------------------
 void check_cpb(int64_t cpb) {
     // The reference asserts the same set (src/scanscam_cuda.cu:566); the value is a tuning hint
@@ -306,6 +326,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("c_in") = py::none(), py::arg("h_prev") = py::none(), py::arg("variant") = 0);
     m.def("scan_sigmoid_forward", &scan_sigmoid_forward, "Forward scan with gate = sigmoid(logits) computed in the kernel");
     m.def("scan_sigmoid_backward", &scan_sigmoid_backward, "Fused backward returning the gradient w.r.t. the gate logits");
+    m.def("scan_backward_recompute", &scan_backward_recompute,
+          "Fused backward from (gate, value, outGrad): rebuilds the forward's output instead of reading it");
     m.def("shard_reduce_forward", &shard_reduce_forward, "Per-row aggregate map (A, B) of a sequence shard");
     m.def("shard_reduce_backward", &shard_reduce_backward, "Per-row aggregate map (A, D) of the reverse recurrence");
     m.def("shard_carry", &shard_carry, "Fold gathered shard aggregates into the carry entering one shard");

@@ -131,11 +131,15 @@ def time_fused_sigmoid(lib, rows, T, iters):
         return e0.elapsed_time(e1) / iters
 
     p = [t.data_ptr() for t in (z, b, g, h, ga, gb)]
+    need = lib.ssb_scan_bwd_recompute_workspace_bytes(rows, T)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
     return [
         ("scan forward (gates given)", run(lambda: lib.ssb_scan_fwd_f32(p[0], p[1], p[3], rows, T, None, st))),
         ("scan backward (gates given)", run(lambda: lib.ssb_scan_bwd_f32(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))),
         ("fused forward (logits given)", run(lambda: lib.ssb_scan_sigmoid_fwd_f32(p[0], p[1], p[3], rows, T, None, st))),
         ("fused backward (logits given)", run(lambda: lib.ssb_scan_sigmoid_bwd_f32(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))),
+        ("recompute backward (a, b, g given)", run(lambda: lib.ssb_scan_bwd_recompute_f32(
+            p[0], p[1], p[2], p[4], p[5], rows, T, None, None, ws.data_ptr(), need, st))),
         ("torch.sigmoid pass", run(lambda: torch.sigmoid(z, out=a))),
         ("torch sigmoid-backward pass", run(lambda: torch.ops.aten.sigmoid_backward(ga, a))),
     ]
@@ -156,7 +160,7 @@ def main():
             print(f"# fused sigmoid gate, rows={rows} T={T} ({rows * T * 4 / 1e6:.0f} MB per tensor)")
             for label, ms in time_fused_sigmoid(lib, rows, T, args.iters):
                 results[f"{name}/{label}"] = {"ms": ms}
-                print(f"{label:34s} {ms:8.4f} ms", flush=True)
+                print(f"{label:36s} {ms:8.4f} ms", flush=True)
             continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))

@@ -209,3 +209,35 @@ def test_fused_sigmoid_gate_matches_unfused_oracle(shape):
     h2.backward(g.cuda())
     assert float((h - h2).abs().max() / h2.abs().max()) < 1e-5
     assert float((dz.grad - dz2.grad).abs().max() / dz2.grad.abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("shape,dtype,permute", [((8, 16, 4096), torch.float32, False), ((3, 5, 1000), torch.float32, False),
+                                                  ((2, 3, 7, 64), torch.float32, False), ((4, 33), torch.float64, False),
+                                                  ((2, 50, 96), torch.float32, True)])
+def test_scan_recompute_matches_scan(shape, dtype, permute):
+    """scan_recompute keeps (gate, value) for the backward, not the output, and returns the same
+    values and gradients as scan."""
+    a, b, g = (x.to(dtype) for x in make_inputs("sigmoid2", shape, seed=95))
+
+    def leaf(x):
+        x = x.cuda()
+        if permute:  # dense in [N, T, C] order, viewed as [N, C, T]
+            x = x.mT.contiguous().mT
+        return x.requires_grad_(True)
+
+    a1, b1, a2, b2 = leaf(a), leaf(b), leaf(a), leaf(b)
+    h1 = scanscam_b200.scan(a1, b1)
+    h2 = scanscam_b200.scan_recompute(a2, b2)
+    saved = h2.grad_fn.saved_tensors
+    assert len(saved) == 2 and saved[0].data_ptr() == a2.data_ptr() and saved[1].data_ptr() == b2.data_ptr()
+    dg = g.cuda()
+    h1.backward(dg)
+    h2.backward(dg)
+    assert torch.equal(h1, h2)
+    tol = 1e-5 if dtype == torch.float32 else 1e-12
+    for x, y in ((a1.grad, a2.grad), (b1.grad, b2.grad)):
+        assert float((x - y).abs().max() / y.abs().max()) < tol
+    T = shape[-1]
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, T) for x in (a, b, g)))
+    assert _gpu.max_norm_err(a2.grad.contiguous().reshape(-1, T), ga_ref) < 1e-4
+    assert _gpu.max_norm_err(b2.grad.contiguous().reshape(-1, T), gb_ref) < 1e-4

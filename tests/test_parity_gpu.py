@@ -494,3 +494,35 @@ def test_tensor_map_paths_work_from_a_fresh_thread():
     torch.cuda.synchronize()
     for h, ga, gb in results.values():
         assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
+
+
+@pytest.mark.parametrize("gates,shape", [("sigmoid2", (40, 4096)), ("resets", (130, 2048)), ("randn", (77, 256)),
+                                         ("sigmoid2", (300, 32)), ("sigmoid0", (1000, 512)), ("nearunit", (3, 70000)),
+                                         ("sigmoid2", (9, 8192)), ("resets", (50, 24)), ("sigmoid2", (7, 1001))])
+def test_recompute_backward_matches_oracle(gates, shape):
+    """ssb_scan_bwd_recompute_f32 takes (a, b, g) and rebuilds h itself: in one kernel for rows of
+    32 * 2^k <= 4096 steps, through the forward kernel and a workspace otherwise.  Carries enter
+    every row from both sides."""
+    rows, T = shape
+    a, b, g = make_inputs(gates, shape, seed=91)
+    carry = torch.randn(rows)
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy(), h_in=carry.numpy())
+    ga_ref, gb_ref = oracle.scan_backward(a.numpy(), h_ref, g.numpy(), gb_in=carry.numpy(), h_prev=carry.numpy())
+    lib = _native.load()
+    da, db, dg, dc = a.cuda(), b.cuda(), g.cuda(), carry.cuda()
+    ga, gb = torch.empty_like(da), torch.empty_like(da)
+    need = lib.ssb_scan_bwd_recompute_workspace_bytes(rows, T)
+    in_kernel = T % 32 == 0 and T <= 4096 and (T // 32) & (T // 32 - 1) == 0
+    assert (need == 0) == in_kernel
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    st = _native.stream_of(da)
+    if need:
+        rc = lib.ssb_scan_bwd_recompute_f32(da.data_ptr(), db.data_ptr(), dg.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                            rows, T, dc.data_ptr(), dc.data_ptr(), None, 0, st)
+        assert rc == _native.ERR_WORKSPACE
+    _native.check(lib.ssb_scan_bwd_recompute_f32(da.data_ptr(), db.data_ptr(), dg.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                                 rows, T, dc.data_ptr(), dc.data_ptr(), ws.data_ptr(), need, st))
+    _gpu.device_ok()
+    assert _gpu.max_norm_err(ga, ga_ref) < TOL and _gpu.max_norm_err(gb, gb_ref) < TOL
+    if gates != "randn":  # gates above 1 in magnitude grow the values beyond an absolute tolerance
+        assert _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
