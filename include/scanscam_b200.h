@@ -147,6 +147,25 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
                              const float *h_prev, void *stream);
 
 /* ------------------------------------------------------------------------------------
+ * 16-bit storage: bf16 or fp16 tensors in memory, fp32 arithmetic, fp32 per-row carries (no
+ * counterpart in the reference, whose dispatch covers float and double only,
+ * src/scanscam_cuda.cu:52, and raises for half types).  Halves the bytes the scan moves: forward
+ * 6, backward 10 bytes per element.  Same meaning of every argument as ssb_scan_fwd_f32 /
+ * ssb_scan_bwd_f32; tensor pointers address 16-bit elements and need 2-byte alignment (16-byte for
+ * the fast kernels: rows of T = 64 * 2^k <= 8192 go through the bulk-tensor sweep, T % 8 == 0
+ * through 16-byte loads, anything else element by element).  Every output element is the fp32
+ * result rounded to nearest-even once; the running state h is never rounded between steps.
+ * ---------------------------------------------------------------------------------- */
+int ssb_scan_fwd_bf16(const void *gate, const void *value, void *out, int64_t rows, int64_t T,
+                      const float *h_in, void *stream);
+int ssb_scan_bwd_bf16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue,
+                      int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream);
+int ssb_scan_fwd_f16(const void *gate, const void *value, void *out, int64_t rows, int64_t T,
+                     const float *h_in, void *stream);
+int ssb_scan_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue,
+                     int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream);
+
+/* ------------------------------------------------------------------------------------
  * Backward that recomputes h (no counterpart in the reference, whose op.Scan.forward saves both
  * `gate` and `output` for the backward, scanscam/op.py:36).  Takes what the forward took --
  * gate a, value b, and the carry h_in entering each row (NULL = 0) -- plus gout and c_in, and

@@ -6,6 +6,8 @@
 // exact-zero gates ("resets") and gates with |a| > 1 are handled like any other value.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -56,6 +58,81 @@ __device__ __forceinline__ void store_stream(real *p, const Pack<real, VEC> &r) 
     } else {
         static_assert(VEC == 1, "unsupported pack width");
         __stcs(p, r.v[0]);
+    }
+}
+
+// ---- 16-bit storage types (bf16 / fp16 in memory, fp32 arithmetic) -------------------------
+// Two packed 16-bit values <-> two floats.  `lo` is the element at the lower address.
+template <typename io_t>
+__device__ __forceinline__ void unpack2(uint32_t w, float &lo, float &hi);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float &lo, float &hi) {
+    lo = __uint_as_float(w << 16);  // a bf16 is the upper half of the fp32 with the same value
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float &lo, float &hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    lo = f.x;
+    hi = f.y;
+}
+template <typename io_t>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);  // round to nearest even
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+template <typename io_t>
+__device__ __forceinline__ float io_to_float(io_t x) { return static_cast<float>(x); }
+template <>
+__device__ __forceinline__ float io_to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <>
+__device__ __forceinline__ float io_to_float<__half>(__half x) { return __half2float(x); }
+
+// Loads VEC elements stored as io_t into a pack of `real`; io_t == real is the plain load above.
+// For a 16-bit io_t, VEC is 1 (scalar) or 8 (one 16-byte load).
+template <typename real, typename io_t, int VEC>
+__device__ __forceinline__ Pack<real, VEC> load_stream_io(const io_t *p) {
+    if constexpr (sizeof(io_t) == sizeof(real)) {
+        return load_stream<real, VEC>(reinterpret_cast<const real *>(p));
+    } else {
+        static_assert(sizeof(io_t) == 2 && sizeof(real) == 4 && (VEC == 1 || VEC == 8), "16-bit storage, fp32 arithmetic");
+        Pack<real, VEC> r;
+        if constexpr (VEC == 1) {
+            r.v[0] = io_to_float<io_t>(*p);
+        } else {
+            const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p));
+            unpack2<io_t>(t.x, r.v[0], r.v[1]);
+            unpack2<io_t>(t.y, r.v[2], r.v[3]);
+            unpack2<io_t>(t.z, r.v[4], r.v[5]);
+            unpack2<io_t>(t.w, r.v[6], r.v[7]);
+        }
+        return r;
+    }
+}
+
+template <typename real, typename io_t, int VEC>
+__device__ __forceinline__ void store_stream_io(io_t *p, const Pack<real, VEC> &r) {
+    if constexpr (sizeof(io_t) == sizeof(real)) {
+        store_stream<real, VEC>(reinterpret_cast<real *>(p), r);
+    } else {
+        static_assert(sizeof(io_t) == 2 && sizeof(real) == 4 && (VEC == 1 || VEC == 8), "16-bit storage, fp32 arithmetic");
+        if constexpr (VEC == 1) {
+            *p = static_cast<io_t>(r.v[0]);
+        } else {
+            uint4 t;
+            t.x = pack2<io_t>(r.v[0], r.v[1]);
+            t.y = pack2<io_t>(r.v[2], r.v[3]);
+            t.z = pack2<io_t>(r.v[4], r.v[5]);
+            t.w = pack2<io_t>(r.v[6], r.v[7]);
+            __stcs(reinterpret_cast<uint4 *>(p), t);
+        }
     }
 }
 

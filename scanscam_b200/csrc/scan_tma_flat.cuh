@@ -15,6 +15,13 @@
 //     in the recurrence, exactly as in the other families.  The backward reads h_{t-1} of a
 //     line's first element straight from the h tile in shared memory.
 //
+// Storage type IO: float, or a 16-bit type (bf16 / fp16) with fp32 arithmetic.  With 16-bit
+// storage a 128-byte line holds 64 elements and two threads share it: a thread still owns 32
+// consecutive elements (a "unit", four 16-byte chunks of 8), the tensor is described as
+// [rows][T/64][64], and everything between the unpack after the shared-memory read and the pack
+// before the shared-memory write is the fp32 code.  "Line" below means unit where it describes
+// what a thread owns.
+//
 // Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
 #pragma once
 
@@ -27,18 +34,28 @@
 namespace ssb {
 namespace tmaflat {
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD>
+template <int LINES, int STAGES, int OUTBUF, bool BWD, typename IO = float>
 struct Config {
-    static constexpr int THREADS = LINES;
+    static constexpr int TPL = 4 / (int)sizeof(IO);  // threads per 128-byte line
+    static constexpr int THREADS = LINES * TPL;
     static constexpr int N_IN = BWD ? 3 : 2;
     static constexpr int N_OUT = BWD ? 2 : 1;
     static constexpr int TILE = LINES * 128;
     static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 1024;
-    static_assert(LINES % 32 == 0 && LINES <= 256, "a span is whole warps of lines and fits a TMA box");
+    static_assert(sizeof(IO) == 4 || sizeof(IO) == 2, "fp32 or 16-bit storage");
+    static_assert(THREADS % 32 == 0 && LINES % 8 == 0 && LINES <= 256 && THREADS <= 512,
+                  "a span is whole warps of units, whole swizzle atoms, and fits a TMA box");
 };
 
 // Swizzled byte offset of float4 `j` (0..7) of line `t` inside a 1024-byte aligned tile.
 __device__ __forceinline__ uint32_t chunk_offset(int t, int j) { return (uint32_t)((t << 7) | ((j ^ (t & 7)) << 4)); }
+// Swizzled byte offset of 16-byte chunk `j` of the 32 elements thread `t` owns (j < 8 for fp32,
+// j < 4 for 16-bit storage, where threads 2l and 2l+1 share line l).
+template <typename IO>
+__device__ __forceinline__ uint32_t unit_chunk_offset(int t, int j) {
+    if constexpr (sizeof(IO) == 4) return chunk_offset(t, j);
+    else return chunk_offset(t >> 1, ((t & 1) << 2) | j);
+}
 
 // SIGMOID: the gate tensor holds logits z; the gate is sigmoid(z) (flat::sigmoidf) and the
 // backward's first output is the gradient with respect to z.
@@ -46,15 +63,17 @@ __device__ __forceinline__ uint32_t chunk_offset(int t, int j) { return (uint32_
 // h; the kernel rebuilds h for the span with a forward scan of (a, b) -- both scans share the one
 // barrier -- so a caller need not keep h between the passes.  carry_b is then the h entering each
 // row (the forward's h_in).
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false>
-__global__ void __launch_bounds__(LINES)
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float>
+__global__ void __launch_bounds__(LINES * (4 / (int)sizeof(IO)))
 tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                 const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
                 const __grid_constant__ CUtensorMap map_out2, int64_t rows, int lines_per_row,
                 const float *__restrict__ carry_a,   // fwd: h_in | bwd: c_in
                 const float *__restrict__ carry_b) { // bwd: h_prev
-    using Cfg = Config<LINES, STAGES, OUTBUF, BWD>;
-    constexpr int N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT, TILE = Cfg::TILE, NW = LINES / 32;
+    using Cfg = Config<LINES, STAGES, OUTBUF, BWD, IO>;
+    constexpr int N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT, TILE = Cfg::TILE, NW = Cfg::THREADS / 32;
+    constexpr bool F32 = sizeof(IO) == 4;
+    constexpr int NCH = F32 ? 8 : 4;  // 16-byte chunks per thread
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES];
     __shared__ float2 s_tot[2][NW];
@@ -65,7 +84,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     const uint32_t smem0 = (tma::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t out_base = smem0 + STAGES * N_IN * TILE;
     const uint32_t bar0 = tma::smem_u32(&full_bar[0]);
-    const int rows_per_span = LINES / lines_per_row;
+    const int rows_per_span = Cfg::THREADS / lines_per_row;  // lines_per_row: 32-element units per row
     const int64_t n_spans = (rows + rows_per_span - 1) / rows_per_span;
     const int64_t my_spans = (int64_t)blockIdx.x < n_spans ? (n_spans - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     // line of this thread inside its row, and whether it starts / ends a row
@@ -91,9 +110,9 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     }
     __syncthreads();
 
-    uint32_t off[8];
+    uint32_t off[NCH];
 #pragma unroll
-    for (int j = 0; j < 8; j++) off[j] = chunk_offset(tid, j);
+    for (int j = 0; j < NCH; j++) off[j] = unit_chunk_offset<IO>(tid, j);
     bool timed_out = false;
     unsigned phase_bits = 0u;
     int out_slot = 0, buf = 0;
@@ -107,8 +126,30 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         phase_bits ^= 1u << stage;
 
         float a[32], x[32], y[32];  // x: value | h ; y: unused | gout
+        if constexpr (!F32) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < 4; j++) {
+                const float4 va = tma::lds128(in0 + off[j]), vx = tma::lds128(in0 + TILE + off[j]);
+                const float wa[4] = {va.x, va.y, va.z, va.w}, wx[4] = {vx.x, vx.y, vx.z, vx.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    unpack2<IO>(__float_as_uint(wa[k]), a[8 * j + 2 * k], a[8 * j + 2 * k + 1]);
+                    unpack2<IO>(__float_as_uint(wx[k]), x[8 * j + 2 * k], x[8 * j + 2 * k + 1]);
+                }
+                if (SIGMOID) {
+#pragma unroll
+                    for (int k = 0; k < 8; k++) a[8 * j + k] = flat::sigmoidf(a[8 * j + k]);
+                }
+                if (BWD) {
+                    const float4 vy = tma::lds128(in0 + 2 * TILE + off[j]);
+                    const float wy[4] = {vy.x, vy.y, vy.z, vy.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) unpack2<IO>(__float_as_uint(wy[k]), y[8 * j + 2 * k], y[8 * j + 2 * k + 1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < (F32 ? 8 : 0); j++) {
             const float4 va = tma::lds128(in0 + off[j]), vx = tma::lds128(in0 + TILE + off[j]);
             a[4 * j] = va.x; a[4 * j + 1] = va.y; a[4 * j + 2] = va.z; a[4 * j + 3] = va.w;
             if (SIGMOID) {
@@ -126,7 +167,12 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
             if (row_start) {
                 if (carry_b != nullptr && row < rows) h_left = carry_b[row];
             } else if (!RECOMPUTE) {
-                h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
+                if constexpr (F32) {
+                    h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
+                } else {  // the word that holds the previous unit's last two elements
+                    float before;
+                    unpack2<IO>(__float_as_uint(tma::lds32(in0 + TILE + unit_chunk_offset<IO>(tid - 1, 3) + 12)), before, h_left);
+                }
             }
         }
         const float a_first = a[0];  // the line's first gate before a row start zeroes it
@@ -194,7 +240,39 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         }
 
         const uint32_t ob = out_base + out_slot * N_OUT * TILE;
-        if (!BWD) {
+        if constexpr (!F32) {
+            // In place: forward x <- h; backward y <- grad of value, a <- grad of gate.  Then pack.
+            if (!BWD) {
+#pragma unroll
+                for (int k = 0; k < 32; k++) { s = fmaf(a[k], s, x[k]); x[k] = s; }
+            } else {
+#pragma unroll
+                for (int k = 31; k >= 0; k--) {
+                    const float gb = y[k] + s, ak = (k == 0) ? a_first : a[k];
+                    s = a[k] * gb;
+                    y[k] = gb;
+                    a[k] = gb * (k > 0 ? x[k > 0 ? k - 1 : 0] : h_left);
+                    if (SIGMOID) a[k] *= ak * (1.f - ak);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float *src = BWD ? a : x;
+                float4 o;
+                o.x = __uint_as_float(pack2<IO>(src[8 * j], src[8 * j + 1]));
+                o.y = __uint_as_float(pack2<IO>(src[8 * j + 2], src[8 * j + 3]));
+                o.z = __uint_as_float(pack2<IO>(src[8 * j + 4], src[8 * j + 5]));
+                o.w = __uint_as_float(pack2<IO>(src[8 * j + 6], src[8 * j + 7]));
+                tma::sts128(ob + off[j], o);
+                if (BWD) {
+                    o.x = __uint_as_float(pack2<IO>(y[8 * j], y[8 * j + 1]));
+                    o.y = __uint_as_float(pack2<IO>(y[8 * j + 2], y[8 * j + 3]));
+                    o.z = __uint_as_float(pack2<IO>(y[8 * j + 4], y[8 * j + 5]));
+                    o.w = __uint_as_float(pack2<IO>(y[8 * j + 6], y[8 * j + 7]));
+                    tma::sts128(ob + TILE + off[j], o);
+                }
+            }
+        } else if (!BWD) {
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 float4 o;

@@ -20,10 +20,12 @@ namespace ssb {
 
 constexpr int kWarpKernelWarps = 8;  // warps per CTA
 
-template <typename real, int VEC, int U, bool REDUCE>
+// io_t is the storage type of the tensors (real itself, or bf16 / fp16 with real = float: the
+// arithmetic and the per-row carries stay in fp32).
+template <typename real, int VEC, int U, bool REDUCE, typename io_t = real>
 __global__ void __launch_bounds__(kWarpKernelWarps * 32)
-warp_rows_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ value,
-                     real *__restrict__ out, int64_t rows, int64_t T,
+warp_rows_fwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ value,
+                     io_t *__restrict__ out, int64_t rows, int64_t T,
                      const real *__restrict__ h_in, real *__restrict__ agg) {
     constexpr int CH = 32 * VEC * U;
     const int lane = threadIdx.x & 31;
@@ -31,8 +33,8 @@ warp_rows_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ val
     // Interleave so that consecutive rows land on different CTAs.
     for (int64_t row = (int64_t)(threadIdx.x >> 5) * gridDim.x + blockIdx.x; row < rows;
          row += n_warps) {
-        const real *g = gate + row * T;
-        const real *v = value + row * T;
+        const io_t *g = gate + row * T;
+        const io_t *v = value + row * T;
         real carry = (!REDUCE && h_in != nullptr) ? h_in[row] : real(0);
         real a_row = real(1);
         for (int64_t t0 = 0; t0 < T; t0 += CH) {
@@ -41,8 +43,8 @@ warp_rows_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ val
             for (int u = 0; u < U; u++) {
                 const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
                 if (idx < T) {  // T % VEC == 0 whenever VEC > 1, so a pack is all in or all out
-                    a[u] = load_stream<real, VEC>(g + idx);
-                    b[u] = load_stream<real, VEC>(v + idx);
+                    a[u] = load_stream_io<real, io_t, VEC>(g + idx);
+                    b[u] = load_stream_io<real, io_t, VEC>(v + idx);
                 } else {
 #pragma unroll
                     for (int k = 0; k < VEC; k++) { a[u].v[k] = real(1); b[u].v[k] = real(0); }
@@ -77,7 +79,7 @@ warp_rows_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ val
                         o.v[k] = h;
                     }
                     const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
-                    if (idx < T) store_stream<real, VEC>(out + row * T + idx, o);
+                    if (idx < T) store_stream_io<real, io_t, VEC>(out + row * T + idx, o);
                 } else {
                     a_row *= At;
                 }
@@ -97,11 +99,11 @@ warp_rows_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ val
 // recurrence is  gb_t = g_t + c_{t+1},  c_t = a_t * gb_t,  i.e. the map c -> a_t*c + a_t*g_t,
 // folded from the right; ga_t = gb_t * h_{t-1}.  This is the order of operations of the
 // reference's sequential loop (src/scanscam_cpu.hpp:64-77).
-template <typename real, int VEC, int U, bool REDUCE>
+template <typename real, int VEC, int U, bool REDUCE, typename io_t = real>
 __global__ void __launch_bounds__(kWarpKernelWarps * 32)
-warp_rows_bwd_kernel(const real *__restrict__ gate, const real *__restrict__ hout,
-                     const real *__restrict__ gout, real *__restrict__ ggate,
-                     real *__restrict__ gvalue, int64_t rows, int64_t T,
+warp_rows_bwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ hout,
+                     const io_t *__restrict__ gout, io_t *__restrict__ ggate,
+                     io_t *__restrict__ gvalue, int64_t rows, int64_t T,
                      const real *__restrict__ c_in, const real *__restrict__ h_prev,
                      real *__restrict__ agg) {
     constexpr int CH = 32 * VEC * U;
@@ -110,25 +112,25 @@ warp_rows_bwd_kernel(const real *__restrict__ gate, const real *__restrict__ hou
     const int64_t n_chunks = (T + CH - 1) / CH;
     for (int64_t row = (int64_t)(threadIdx.x >> 5) * gridDim.x + blockIdx.x; row < rows;
          row += n_warps) {
-        const real *ga_ = gate + row * T;
-        const real *gg_ = gout + row * T;
-        const real *hh_ = REDUCE ? nullptr : hout + row * T;
+        const io_t *ga_ = gate + row * T;
+        const io_t *gg_ = gout + row * T;
+        const io_t *hh_ = REDUCE ? nullptr : hout + row * T;
         real carry = (!REDUCE && c_in != nullptr) ? c_in[row] : real(0);
         real a_row = real(1);
         for (int64_t t0 = (n_chunks - 1) * CH; t0 >= 0; t0 -= CH) {
             Pack<real, VEC> a[U], g[U], h[U];
             real edge = real(0);  // h just left of this chunk
             if constexpr (!REDUCE) {
-                if (t0 > 0) edge = hh_[t0 - 1];
+                if (t0 > 0) edge = io_to_float<io_t>(hh_[t0 - 1]);
                 else if (h_prev != nullptr) edge = h_prev[row];
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
                 if (idx < T) {
-                    a[u] = load_stream<real, VEC>(ga_ + idx);
-                    g[u] = load_stream<real, VEC>(gg_ + idx);
-                    if constexpr (!REDUCE) h[u] = load_stream<real, VEC>(hh_ + idx);
+                    a[u] = load_stream_io<real, io_t, VEC>(ga_ + idx);
+                    g[u] = load_stream_io<real, io_t, VEC>(gg_ + idx);
+                    if constexpr (!REDUCE) h[u] = load_stream_io<real, io_t, VEC>(hh_ + idx);
                 } else {
 #pragma unroll
                     for (int k = 0; k < VEC; k++) {
@@ -176,8 +178,8 @@ warp_rows_bwd_kernel(const real *__restrict__ gate, const real *__restrict__ hou
                     }
                     const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
                     if (idx < T) {
-                        store_stream<real, VEC>(ggate + row * T + idx, oa);
-                        store_stream<real, VEC>(gvalue + row * T + idx, ob);
+                        store_stream_io<real, io_t, VEC>(ggate + row * T + idx, oa);
+                        store_stream_io<real, io_t, VEC>(gvalue + row * T + idx, ob);
                     }
                 } else {
                     a_row *= At;

@@ -412,35 +412,48 @@ int launch_span_maps(const float *gate, const float *in1, float *agg, int64_t ro
     X(0, 128, 2, 2, 128, 2, 1) X(1, 128, 3, 2, 128, 2, 2) X(2, 64, 3, 2, 64, 3, 2) X(3, 64, 4, 2, 64, 2, 2) \
     X(4, 128, 2, 1, 64, 2, 1) X(5, 256, 2, 1, 128, 3, 1) X(6, 32, 4, 2, 32, 4, 2)
 
-bool tmaflat_eligible(int64_t rows, int64_t T, int lines) {
-    if (T % 32 != 0 || rows > 0x7fffffffLL) return false;
-    const int64_t lpr = T / 32;
+// `elem_bytes`: 4 (fp32) or 2 (bf16 / fp16 storage); a 128-byte line holds 128 / elem_bytes elements.
+bool tmaflat_eligible(int64_t rows, int64_t T, int lines, int elem_bytes = 4) {
+    const int per_line = 128 / elem_bytes;
+    if (T % per_line != 0 || rows > 0x7fffffffLL) return false;
+    const int64_t lpr = T / per_line;
     return lpr >= 1 && lpr <= lines && (lpr & (lpr - 1)) == 0;
 }
 
-int make_span_map(CUtensorMap *map, const float *ptr, int64_t rows, int64_t T, int lines) {
+template <typename IO> constexpr CUtensorMapDataType tensor_map_type();
+template <> constexpr CUtensorMapDataType tensor_map_type<float>() { return CU_TENSOR_MAP_DATA_TYPE_FLOAT32; }
+template <> constexpr CUtensorMapDataType tensor_map_type<__nv_bfloat16>() { return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; }
+template <> constexpr CUtensorMapDataType tensor_map_type<__half>() { return CU_TENSOR_MAP_DATA_TYPE_FLOAT16; }
+
+template <typename IO>
+int make_span_map(CUtensorMap *map, const IO *ptr, int64_t rows, int64_t T, int lines) {
     PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
     if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
-    const int64_t lpr = T / 32;
-    cuuint64_t dims[3] = {32, (cuuint64_t)lpr, (cuuint64_t)rows};
-    cuuint64_t strides[2] = {128, (cuuint64_t)T * 4};
-    cuuint32_t box[3] = {32, (cuuint32_t)lpr, (cuuint32_t)(lines / lpr)};
+    constexpr int per_line = 128 / (int)sizeof(IO);
+    const int64_t lpr = T / per_line;
+    cuuint64_t dims[3] = {(cuuint64_t)per_line, (cuuint64_t)lpr, (cuuint64_t)rows};
+    cuuint64_t strides[2] = {128, (cuuint64_t)T * sizeof(IO)};
+    cuuint32_t box[3] = {(cuuint32_t)per_line, (cuuint32_t)lpr, (cuuint32_t)(lines / lpr)};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = encode_tiled(enc, map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+    CUresult r = encode_tiled(enc, map, tensor_map_type<IO>(), 3, const_cast<IO *>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled(span) failed with CUresult %d", (int)r);
     return SSB_OK;
 }
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false>
-int launch_tmaflat(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows,
+template <typename T> struct as_given { using type = T; };  // keeps a parameter out of template deduction
+
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float>
+int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::type *in2, IO *out1,
+                   typename as_given<IO>::type *out2, int64_t rows,
                    int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
-    using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD>;
+    using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD, IO>;
     static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
-    if (!tmaflat_eligible(rows, T, LINES))
-        return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = 32 * 2^k <= %d (T=%lld)", LINES * 32, (long long)T);
-    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID, RECOMPUTE>;
+    constexpr int per_line = 128 / (int)sizeof(IO);
+    if (!tmaflat_eligible(rows, T, LINES, (int)sizeof(IO)))
+        return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = %d * 2^k <= %d (T=%lld)", per_line, LINES * per_line, (long long)T);
+    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID, RECOMPUTE, IO>;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
@@ -459,11 +472,11 @@ int launch_tmaflat(const float *gate, const float *in1, const float *in2, float 
         }
         cached_occ.store(occ, std::memory_order_relaxed);
     }
-    const int lpr = (int)(T / 32);
-    const int64_t spans = (rows + LINES / lpr - 1) / (LINES / lpr);
+    const int upr = (int)(T / 32);  // 32-element units per row
+    const int64_t spans = (rows + Cfg::THREADS / upr - 1) / (Cfg::THREADS / upr);
     const int64_t cap = (int64_t)sm_count() * occ;
     const int grid = (int)(spans < cap ? spans : cap);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, lpr, carry_a, carry_b);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b);
     return check_launch("tma_flat_kernel");
 }
 
@@ -868,6 +881,90 @@ int ssb_scan_bwd_f64(const double *gate, const double *h, const double *gout, do
         return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_f64: pointers must be 8-byte aligned");
     return launch_warp_bwd<double, false>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr,
                                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ---- 16-bit storage (bf16 / fp16 in memory, fp32 arithmetic and carries) --------------------
+namespace {
+
+template <typename IO>
+int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows, int64_t T, const float *h_in,
+                 void *stream, const char *who) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate_ || !value_ || !out_) return fail(SSB_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+    if (!aligned_to(gate_, 2) || !aligned_to(value_, 2) || !aligned_to(out_, 2) || !aligned_to(h_in, 4))
+        return fail(SSB_ERR_ALIGNMENT, "%s: tensors must be 2-byte aligned, carries 4-byte aligned", who);
+    const IO *gate = static_cast<const IO *>(gate_), *value = static_cast<const IO *>(value_);
+    IO *out = static_cast<IO *>(out_);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
+    if (al16 && encode_fn() != nullptr) {
+        if (tmaflat_eligible(rows, T, 64, 2))
+            return launch_tmaflat<64, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+        if (tmaflat_eligible(rows, T, 128, 2))
+            return launch_tmaflat<128, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+    }
+    const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
+    if (al16 && T % 8 == 0)
+        ssb::warp_rows_fwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, nullptr);
+    else
+        ssb::warp_rows_fwd_kernel<float, 1, 4, false, IO><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, nullptr);
+    return check_launch("warp_rows_fwd_kernel<16-bit>");
+}
+
+template <typename IO>
+int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *ggate_, void *gvalue_, int64_t rows, int64_t T,
+                 const float *c_in, const float *h_prev, void *stream, const char *who) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate_ || !h_ || !gout_ || !ggate_ || !gvalue_) return fail(SSB_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+    if (!aligned_to(gate_, 2) || !aligned_to(h_, 2) || !aligned_to(gout_, 2) || !aligned_to(ggate_, 2) ||
+        !aligned_to(gvalue_, 2) || !aligned_to(c_in, 4) || !aligned_to(h_prev, 4))
+        return fail(SSB_ERR_ALIGNMENT, "%s: tensors must be 2-byte aligned, carries 4-byte aligned", who);
+    const IO *gate = static_cast<const IO *>(gate_), *h = static_cast<const IO *>(h_), *gout = static_cast<const IO *>(gout_);
+    IO *ggate = static_cast<IO *>(ggate_), *gvalue = static_cast<IO *>(gvalue_);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) && aligned_to(ggate, 16) &&
+                      aligned_to(gvalue, 16);
+    if (al16 && encode_fn() != nullptr) {
+        if (tmaflat_eligible(rows, T, 32, 2))
+            return launch_tmaflat<32, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        if (tmaflat_eligible(rows, T, 64, 2))
+            return launch_tmaflat<64, 3, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        if (tmaflat_eligible(rows, T, 128, 2))
+            return launch_tmaflat<128, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+    }
+    const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
+    if (al16 && T % 8 == 0)
+        ssb::warp_rows_bwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr);
+    else
+        ssb::warp_rows_bwd_kernel<float, 1, 4, false, IO><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr);
+    return check_launch("warp_rows_bwd_kernel<16-bit>");
+}
+
+}  // namespace
+
+extern "C" {
+
+int ssb_scan_fwd_bf16(const void *gate, const void *value, void *out, int64_t rows, int64_t T, const float *h_in, void *stream) {
+    return scan_fwd_h16<__nv_bfloat16>(gate, value, out, rows, T, h_in, stream, "ssb_scan_fwd_bf16");
+}
+int ssb_scan_fwd_f16(const void *gate, const void *value, void *out, int64_t rows, int64_t T, const float *h_in, void *stream) {
+    return scan_fwd_h16<__half>(gate, value, out, rows, T, h_in, stream, "ssb_scan_fwd_f16");
+}
+int ssb_scan_bwd_bf16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t rows, int64_t T,
+                      const float *c_in, const float *h_prev, void *stream) {
+    return scan_bwd_h16<__nv_bfloat16>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, stream, "ssb_scan_bwd_bf16");
+}
+int ssb_scan_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t rows, int64_t T,
+                     const float *c_in, const float *h_prev, void *stream) {
+    return scan_bwd_h16<__half>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, stream, "ssb_scan_bwd_f16");
 }
 
 }  // extern "C"

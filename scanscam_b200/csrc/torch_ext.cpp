@@ -27,7 +27,12 @@ void check_same(const torch::Tensor &ref, const torch::Tensor &x, const char *na
     TORCH_CHECK(x.device() == ref.device(), name, " must be on the same device as gate");
 }
 
-void check_dtype(const torch::Tensor &x, const char *op) {
+bool is_16bit(const torch::Tensor &x) { return x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kHalf; }
+
+// `allow_16bit`: the rows-layout kernels also take bf16 / fp16 storage (an addition: the reference
+// raises for them like for any other non-floating type).
+void check_dtype(const torch::Tensor &x, const char *op, bool allow_16bit = false) {
+    if (allow_16bit && is_16bit(x)) return;
     // Same wording as the dispatch macro the reference relies on.
     if (x.scalar_type() != torch::kFloat32 && x.scalar_type() != torch::kFloat64) {
         TORCH_CHECK_NOT_IMPLEMENTED(false, "\"", op, "\" not implemented for '", toString(x.scalar_type()), "'");
@@ -52,7 +57,9 @@ const void *opt_ptr(const c10::optional<torch::Tensor> &t, const torch::Tensor &
     if (!t.has_value() || !t->defined()) return nullptr;
     check_tensor(*t, name);
     TORCH_CHECK(t->numel() == rows, name, " must have one element per row");
-    TORCH_CHECK(t->scalar_type() == like.scalar_type() && t->device() == like.device(), name, " dtype/device mismatch");
+    // carries of 16-bit tensors are fp32
+    const auto want = is_16bit(like) ? torch::kFloat32 : like.scalar_type();
+    TORCH_CHECK(t->scalar_type() == want && t->device() == like.device(), name, " dtype/device mismatch");
     return t->data_ptr();
 }
 
@@ -63,12 +70,16 @@ void scan_forward_impl(const torch::Tensor &gate, const torch::Tensor &value, to
     TORCH_CHECK(gate.dim() == 2, "gate must be 2-D [rows, T]");
     check_same(gate, value, "value");
     check_same(gate, output, "output");
-    check_dtype(gate, op);
+    check_dtype(gate, op, true);
     const int64_t rows = gate.size(0), T = gate.size(1);
     c10::cuda::CUDAGuard guard(gate.device());
     const void *hin = opt_ptr(h_in, gate, rows, "h_in");
     int rc;
-    if (gate.scalar_type() == torch::kFloat32) {
+    if (is_16bit(gate)) {
+        TORCH_CHECK(variant == SSB_VARIANT_AUTO, op, ": 16-bit tensors have no selectable kernel family");
+        auto fn = gate.scalar_type() == torch::kBFloat16 ? ssb_scan_fwd_bf16 : ssb_scan_fwd_f16;
+        rc = fn(gate.data_ptr(), value.data_ptr(), output.data_ptr(), rows, T, static_cast<const float *>(hin), current_stream());
+    } else if (gate.scalar_type() == torch::kFloat32) {
         if (variant == SSB_VARIANT_AUTO)
             variant = ssb_scan_recommend(rows, T, 0, aligned16(gate) && aligned16(value) && aligned16(output), 1);
         const size_t ws_bytes = ssb_scan_workspace_bytes(rows, T, (int)variant);
@@ -93,13 +104,18 @@ void scan_backward_impl(const torch::Tensor &gate, const torch::Tensor &output, 
     check_same(gate, out_grad, "outGrad");
     check_same(gate, gate_grad, "gateGradOut");
     check_same(gate, value_grad, "valueGradOut");
-    check_dtype(gate, op);
+    check_dtype(gate, op, true);
     const int64_t rows = gate.size(0), T = gate.size(1);
     c10::cuda::CUDAGuard guard(gate.device());
     const void *cin = opt_ptr(c_in, gate, rows, "c_in");
     const void *hp = opt_ptr(h_prev, gate, rows, "h_prev");
     int rc;
-    if (gate.scalar_type() == torch::kFloat32) {
+    if (is_16bit(gate)) {
+        TORCH_CHECK(variant == SSB_VARIANT_AUTO, op, ": 16-bit tensors have no selectable kernel family");
+        auto fn = gate.scalar_type() == torch::kBFloat16 ? ssb_scan_bwd_bf16 : ssb_scan_bwd_f16;
+        rc = fn(gate.data_ptr(), output.data_ptr(), out_grad.data_ptr(), gate_grad.data_ptr(), value_grad.data_ptr(), rows, T,
+                static_cast<const float *>(cin), static_cast<const float *>(hp), current_stream());
+    } else if (gate.scalar_type() == torch::kFloat32) {
         if (variant == SSB_VARIANT_AUTO)
             variant = ssb_scan_recommend(rows, T, 1,
                                          aligned16(gate) && aligned16(output) && aligned16(out_grad) &&

@@ -2,6 +2,8 @@
 
     python -m scanscam_b200.tune cfg2,cfg5,1024x262144 [--iters 30] [--families warp,flat,tma]
     python -m scanscam_b200.tune cl:8x4096x512,cl:4x65536x256         (channels-last [N,T,C])
+    python -m scanscam_b200.tune fused:16384x4096                     (gate logits in; recompute backward)
+    python -m scanscam_b200.tune h16:16384x4096                       (bf16 / fp16 storage beside fp32)
 
 For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
 ``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
@@ -145,6 +147,38 @@ def time_fused_sigmoid(lib, rows, T, iters):
     ]
 
 
+def time_16bit(lib, rows, T, iters):
+    """Kernel times of the bf16 / fp16 storage entry points beside fp32 on the same shape."""
+    out = []
+    st = torch.cuda.current_stream().cuda_stream
+    for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16), ("f16", torch.float16)):
+        a = (torch.rand(rows, T, device="cuda") * 0.2 + 0.8).to(dtype)
+        b, g = torch.randn_like(a), torch.randn_like(a)
+        h, ga, gb = (torch.empty_like(a) for _ in range(3))
+        fwd, bwd = getattr(lib, f"ssb_scan_fwd_{name}"), getattr(lib, f"ssb_scan_bwd_{name}")
+        p = [t.data_ptr() for t in (a, b, g, h, ga, gb)]
+        size = a.element_size()
+
+        def run(fn):
+            for _ in range(3):
+                _native.check(fn())
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters
+
+        tf = run(lambda: fwd(p[0], p[1], p[3], rows, T, None, st))
+        tb = run(lambda: bwd(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))
+        n = rows * T
+        out.append((name, 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+        del a, b, g, h, ga, gb
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("shapes")
@@ -161,6 +195,14 @@ def main():
             for label, ms in time_fused_sigmoid(lib, rows, T, args.iters):
                 results[f"{name}/{label}"] = {"ms": ms}
                 print(f"{label:36s} {ms:8.4f} ms", flush=True)
+            continue
+        if name.startswith("h16:"):  # 16-bit storage beside fp32: h16:ROWSxT
+            rows, T = (int(v) for v in name[4:].lower().split("x"))
+            print(f"# storage types, rows={rows} T={T} ({rows * T / 1e6:.0f} M elements per tensor)")
+            print(f"{'storage':8s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
+            for label, fg, tf, bg, tb, ge in time_16bit(lib, rows, T, args.iters):
+                results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
+                print(f"{label:8s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
             continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))

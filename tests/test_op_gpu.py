@@ -103,8 +103,13 @@ def test_error_behaviour_matches_the_reference():
         scanscam_b200.scan(x, torch.rand(4, 9, device="cuda"))
     with pytest.raises(AssertionError):
         scanscam_b200.scan(torch.rand(8, device="cuda"), torch.rand(8, device="cuda"))
+    with pytest.raises(NotImplementedError, match="not implemented for 'Int'"):
+        scanscam_b200.scan(x.int(), x.int())
+    # 16-bit floating types are an addition in the rows layout only; channels-last raises as the
+    # reference does for every half-precision input
+    xt = torch.rand(2, 8, 4, device="cuda").half().mT
     with pytest.raises(NotImplementedError, match="not implemented for 'Half'"):
-        scanscam_b200.scan(x.half(), x.half())
+        scanscam_b200.scan(xt, xt)
     import scanscam_ext
 
     with pytest.raises(RuntimeError, match="contiguous"):
@@ -241,3 +246,24 @@ def test_scan_recompute_matches_scan(shape, dtype, permute):
     h_ref, ga_ref, gb_ref = _gpu.oracle_all(*(x.reshape(-1, T) for x in (a, b, g)))
     assert _gpu.max_norm_err(a2.grad.contiguous().reshape(-1, T), ga_ref) < 1e-4
     assert _gpu.max_norm_err(b2.grad.contiguous().reshape(-1, T), gb_ref) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(4, 16, 4096), (3, 5, 1000), (6, 33)])
+def test_scan_with_16bit_tensors(dtype, shape):
+    """scan() on bf16 / fp16 tensors: fp32 arithmetic inside, outputs and gradients rounded once.
+    Checked against the oracle run in fp32 on the same (already rounded) inputs."""
+    a, b, g = (x.to(dtype) for x in make_inputs("sigmoid2", shape, seed=97))
+    T = shape[-1]
+    h_ref = oracle.scan_forward(a.float().reshape(-1, T).numpy(), b.float().reshape(-1, T).numpy())
+    da, db = a.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
+    h = scanscam_b200.scan(da, db)
+    assert h.dtype == dtype
+    h.backward(g.cuda())
+    # the backward reads the h the forward stored, i.e. the rounded one
+    ga_ref, gb_ref = oracle.scan_backward(a.float().reshape(-1, T).numpy(), h.detach().float().cpu().reshape(-1, T).numpy(),
+                                          g.float().reshape(-1, T).numpy())
+    half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    for x, ref in ((h, h_ref), (da.grad, ga_ref), (db.grad, gb_ref)):
+        assert x.dtype == dtype
+        assert _gpu.max_norm_err(x.detach().float().reshape(-1, T), ref) < 1.01 * half_ulp

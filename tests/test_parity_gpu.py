@@ -526,3 +526,43 @@ def test_recompute_backward_matches_oracle(gates, shape):
     assert _gpu.max_norm_err(ga, ga_ref) < TOL and _gpu.max_norm_err(gb, gb_ref) < TOL
     if gates != "randn":  # gates above 1 in magnitude grow the values beyond an absolute tolerance
         assert _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
+
+
+H16 = {"bf16": (torch.bfloat16, 2.0 ** -8), "f16": (torch.float16, 2.0 ** -11)}
+
+
+@pytest.mark.parametrize("name", ["bf16", "f16"])
+@pytest.mark.parametrize("gates,shape", [("sigmoid2", (40, 4096)), ("resets", (130, 2048)), ("sigmoid0", (77, 256)),
+                                         ("sigmoid2", (300, 64)), ("sigmoid2", (5, 8192)), ("nearunit", (3, 70000)),
+                                         ("sigmoid2", (9, 8000)), ("resets", (50, 24)), ("sigmoid2", (7, 1001)),
+                                         ("sigmoid0", (33, 30))])
+def test_16bit_storage_matches_oracle(name, gates, shape):
+    """ssb_scan_{fwd,bwd}_{bf16,f16}: 16-bit tensors, fp32 arithmetic and fp32 carries.  The oracle
+    runs in fp32 on the same rounded inputs; every kernel output must be that result rounded once:
+    within half a unit in the last place of the storage type (plus the fp32 reassociation noise,
+    which can flip a rounding on a few elements, so one full unit is allowed on those)."""
+    dtype, half_ulp = H16[name]
+    rows, T = shape
+    a, b, g = (x.to(dtype) for x in make_inputs(gates, shape, seed=101))
+    carry = torch.randn(rows)
+    an, bn, gn, cn = a.float().numpy(), b.float().numpy(), g.float().numpy(), carry.numpy()
+    h_ref = oracle.scan_forward(an, bn, h_in=cn)
+    h16 = torch.from_numpy(h_ref).to(dtype)  # what a forward in this storage type hands to the backward
+    ga_ref, gb_ref = oracle.scan_backward(an, h16.float().numpy(), gn, gb_in=cn, h_prev=cn)
+    lib = _native.load()
+    fwd_fn, bwd_fn = getattr(lib, f"ssb_scan_fwd_{name}"), getattr(lib, f"ssb_scan_bwd_{name}")
+    da, db, dg, dh, dc = a.cuda(), b.cuda(), g.cuda(), h16.cuda(), carry.cuda()
+    h, ga, gb = torch.empty_like(da), torch.empty_like(da), torch.empty_like(da)
+    st = _native.stream_of(da)
+    _native.check(fwd_fn(da.data_ptr(), db.data_ptr(), h.data_ptr(), rows, T, dc.data_ptr(), st))
+    _native.check(bwd_fn(da.data_ptr(), dh.data_ptr(), dg.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
+                         dc.data_ptr(), dc.data_ptr(), st))
+    _gpu.device_ok()
+    for x, ref in ((h, h_ref), (ga, ga_ref), (gb, gb_ref)):
+        got = x.float().cpu().numpy().astype(np.float64)
+        err = np.abs(got - ref)
+        unit = 2.0 * half_ulp * np.maximum(np.abs(ref), 1e-30)  # >= one unit in the last place of the result
+        assert _gpu.max_norm_err(x.float(), ref) < 1.01 * half_ulp
+        assert (err <= 1.001 * unit + 1e-6 * np.abs(ref).max()).all()
+        exact = torch.from_numpy(ref).to(dtype).float().numpy()
+        assert (got != exact).mean() < 1e-2  # all but a few rounding flips are the oracle's value rounded once
