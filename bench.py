@@ -56,6 +56,8 @@ def parse_args():
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
     p.add_argument("--variant", type=int, default=0, help="kernel family/tuning id passed to the C-ABI (0 = auto)")
     p.add_argument("--variant-bwd", type=int, default=0, help="as --variant, for the backward only (0 = same as --variant)")
+    p.add_argument("--storage", default="f32", choices=["f32", "bf16", "f16"],
+                   help="element type of the tensors in HBM (arithmetic is fp32 either way); the headline metric is f32")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--e2e-steps", type=int, default=5)
@@ -262,7 +264,11 @@ def run_gpu_arm(args, workload):
     else:
         T_local = T
         a_cpu, b_cpu, g_cpu = (x.reshape(rows, T) for x in workloads.workload_inputs(workload.name, seed=rank))
-    a, b, g = a_cpu.cuda(), b_cpu.cuda(), g_cpu.cuda()
+    storage = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.storage]
+    elem = torch.empty((), dtype=storage).element_size()
+    if args.storage != "f32" and t_sharded:
+        raise SystemExit("bench.py: --storage bf16/f16 is measured on the row-sharded workloads only")
+    a, b, g = (x.cuda().to(storage) for x in (a_cpu, b_cpu, g_cpu))
     h = torch.empty_like(a)
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     stream = torch.cuda.current_stream()
@@ -287,13 +293,24 @@ def run_gpu_arm(args, workload):
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device="cuda")
         ws_ptr = ws.data_ptr() if ws_bytes else None
 
-        def fwd():
-            _native.check(lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local, None,
-                                                  v_fwd, ws_ptr, ws_bytes, st))
+        if args.storage == "f32":
+            def fwd(s=st):
+                _native.check(lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local, None,
+                                                      v_fwd, ws_ptr, ws_bytes, s))
 
-        def bwd():
-            _native.check(lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
-                                                  gb.data_ptr(), rows, T_local, None, None, v_bwd, ws_ptr, ws_bytes, st))
+            def bwd(s=st):
+                _native.check(lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
+                                                      gb.data_ptr(), rows, T_local, None, None, v_bwd, ws_ptr, ws_bytes, s))
+        else:  # 16-bit storage, fp32 arithmetic: the library picks the kernel, no workspace
+            fwd16, bwd16 = getattr(lib, f"ssb_scan_fwd_{args.storage}"), getattr(lib, f"ssb_scan_bwd_{args.storage}")
+            v_fwd = v_bwd = ws_bytes = 0
+
+            def fwd(s=st):
+                _native.check(fwd16(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local, None, s))
+
+            def bwd(s=st):
+                _native.check(bwd16(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T_local,
+                                    None, None, s))
 
         def step():
             fwd()
@@ -325,11 +342,8 @@ def run_gpu_arm(args, workload):
                 with torch.cuda.graph(graph, stream=side):
                     cap = torch.cuda.current_stream().cuda_stream
                     for _ in range(args.steps):
-                        _native.check(lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T_local,
-                                                              None, v_fwd, ws_ptr, ws_bytes, cap))
-                        _native.check(lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
-                                                              gb.data_ptr(), rows, T_local, None, None, v_bwd, ws_ptr,
-                                                              ws_bytes, cap))
+                        fwd(cap)
+                        bwd(cap)
             stream.wait_stream(side)
             graph.replay()  # one untimed replay: instantiation and upload happen here
             torch.cuda.synchronize()
@@ -387,7 +401,7 @@ def run_gpu_arm(args, workload):
 
     # ---- end to end through the public operator, host buffers -------------------------------
     e2e = None
-    if not args.no_e2e and not t_sharded:
+    if not args.no_e2e and not t_sharded and args.storage == "f32":
         from scanscam_b200.host import HostScanPipeline
 
         pin = [x.pin_memory() for x in (a_cpu, b_cpu, g_cpu)]
@@ -433,11 +447,12 @@ def run_gpu_arm(args, workload):
         "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if t_sharded else "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32" if args.storage == "f32" else f"f32 arithmetic on {args.storage} tensors",
+        "data": "synthetic",
         "config": {
             "workload": (f"{workload.name} {list(workload.shape)} fp32 fwd+bwd, one sequence set split along T over all ranks"
                          if t_sharded else
-                         f"{workload.name} {list(workload.shape)} fp32 fwd+bwd per GPU, gates {workload.gates}, seed = rank"),
+                         f"{workload.name} {list(workload.shape)} {args.storage} fwd+bwd per GPU, gates {workload.gates}, seed = rank"),
             "sharding": ("T split across ranks, NCCL all-gather of per-shard carries" if t_sharded
                          else "rows (batch x channel) per rank, no collective"),
             "l2": "no flush: each pass streams 0.8-1.3 GB, far more than the 126 MB L2",
@@ -449,11 +464,12 @@ def run_gpu_arm(args, workload):
         "clocks": sampler.summary(sampler_how),
     }
     if not t_sharded:
+        BYTES_FWD, BYTES_BWD = 3 * elem, 5 * elem  # per element: read a, b + write h | read a, h, g + write both gradients
         achieved = BYTES_BWD * n_local / bwd_avg_s / 1e9
         line["roofline"] = {
             "bound": "hbm", "kernel": "fused backward (reads a, h, g; writes grad_a, grad_b)",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-            "traffic": (NCU_BWD_TRAFFIC_BYTES_PER_ELEM * n_local if NCU_BWD_TRAFFIC_BYTES_PER_ELEM else None),
+            "traffic": (NCU_BWD_TRAFFIC_BYTES_PER_ELEM * n_local if NCU_BWD_TRAFFIC_BYTES_PER_ELEM and elem == 4 else None),
             "algorithmic_bytes_per_launch": BYTES_BWD * n_local, "avg_launch_ms": bwd_avg_s * 1e3,
             "forward": {"achieved": BYTES_FWD * n_local / fwd_avg_s / 1e9,
                         "frac": BYTES_FWD * n_local / fwd_avg_s / 1e9 / peak, "avg_launch_ms": fwd_avg_s * 1e3},
@@ -463,7 +479,7 @@ def run_gpu_arm(args, workload):
         }
     if e2e is not None:
         line["e2e"] = e2e
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.storage == "f32":
         sample_rows = rows if rows * T_local <= (1 << 26) else max(1, (1 << 26) // T_local)
         v, kind = time_cpu_single(a_cpu[:sample_rows], b_cpu[:sample_rows], g_cpu[:sample_rows])
         line["cpu_baseline"] = {"value": v, "unit": "Gelem/s", "cores": 1, "kind": kind,

@@ -88,12 +88,12 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     const __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&v);
 }
-template <typename io_t>
-__device__ __forceinline__ float io_to_float(io_t x) { return static_cast<float>(x); }
-template <>
-__device__ __forceinline__ float io_to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
-template <>
-__device__ __forceinline__ float io_to_float<__half>(__half x) { return __half2float(x); }
+// One stored element as the arithmetic type (`real` itself, or a 16-bit type widened to float).
+template <typename real, typename io_t>
+__device__ __forceinline__ real widen(io_t x) {
+    if constexpr (sizeof(io_t) == sizeof(real)) return x;
+    else if constexpr (sizeof(io_t) == 2 && sizeof(real) == 4) { float lo, hi; unpack2<io_t>((uint32_t)*reinterpret_cast<const uint16_t *>(&x), lo, hi); return lo; }
+}
 
 // Loads VEC elements stored as io_t into a pack of `real`; io_t == real is the plain load above.
 // For a 16-bit io_t, VEC is 1 (scalar) or 8 (one 16-byte load).
@@ -105,7 +105,7 @@ __device__ __forceinline__ Pack<real, VEC> load_stream_io(const io_t *p) {
         static_assert(sizeof(io_t) == 2 && sizeof(real) == 4 && (VEC == 1 || VEC == 8), "16-bit storage, fp32 arithmetic");
         Pack<real, VEC> r;
         if constexpr (VEC == 1) {
-            r.v[0] = io_to_float<io_t>(*p);
+            r.v[0] = widen<real, io_t>(*p);
         } else {
             const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p));
             unpack2<io_t>(t.x, r.v[0], r.v[1]);

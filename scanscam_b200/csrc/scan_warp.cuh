@@ -121,7 +121,7 @@ warp_rows_bwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ hou
             Pack<real, VEC> a[U], g[U], h[U];
             real edge = real(0);  // h just left of this chunk
             if constexpr (!REDUCE) {
-                if (t0 > 0) edge = io_to_float<io_t>(hh_[t0 - 1]);
+                if (t0 > 0) edge = widen<real, io_t>(hh_[t0 - 1]);
                 else if (h_prev != nullptr) edge = h_prev[row];
             }
 #pragma unroll

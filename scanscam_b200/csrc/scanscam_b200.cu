@@ -903,8 +903,10 @@ int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
     if (al16 && encode_fn() != nullptr) {
+        // configurations from a sweep on [16384,4096], [65536,2048], [524288,512] and [262144,64]
         if (tmaflat_eligible(rows, T, 64, 2))
-            return launch_tmaflat<64, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+            return T > 2048 ? launch_tmaflat<64, 2, 1, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st)
+                            : launch_tmaflat<64, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         if (tmaflat_eligible(rows, T, 128, 2))
             return launch_tmaflat<128, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
     }
@@ -933,12 +935,10 @@ int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *gga
     const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) && aligned_to(ggate, 16) &&
                       aligned_to(gvalue, 16);
     if (al16 && encode_fn() != nullptr) {
-        if (tmaflat_eligible(rows, T, 32, 2))
-            return launch_tmaflat<32, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         if (tmaflat_eligible(rows, T, 64, 2))
-            return launch_tmaflat<64, 3, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+            return launch_tmaflat<64, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         if (tmaflat_eligible(rows, T, 128, 2))
-            return launch_tmaflat<128, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+            return launch_tmaflat<128, 3, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
     }
     const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
     if (al16 && T % 8 == 0)
