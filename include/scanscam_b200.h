@@ -220,10 +220,15 @@ int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout,
  * which those are faster (few channels per row, or enough channel groups to fill the GPU but too
  * few to keep look-back chains short). */
 size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C);
-/* Tuning knob for sweeps: selects the tile shape (warps x steps) the calling host thread's next
- * ssb_scan_cl_*_ex calls use; 0 = default choice (tile shape and plain-vs-look-back), any other id
- * forces the look-back kernels with that tile shape.  Returns the previous id.  Results do not
- * depend on it. */
+/* Tuning knob for sweeps, per calling host thread.  0 = default choice: shapes with at least 96
+ * (batch element, 32-channel block) pairs, T >= 128, C % 4 == 0 and 16-byte aligned tensors run
+ * the streaming kernels (a CTA walks all of T for its channel block,
+ * tiles staged by bulk tensor copies, no scratch -- from the plain entry points too); other shapes
+ * the look-back kernels when scratch is given and they are faster, else the plain kernels.
+ * 0x200 forces the plain kernels in every channels-last fp32 entry point.  Any other id applies to
+ * the next ssb_scan_cl_*_ex calls: 1..31 look-back kernels with that tile shape, 32..63 look-back
+ * on TMA-staged tiles, 64.. streaming kernels with that tile shape.  Returns the previous id.
+ * Results do not depend on it beyond fp32 reassociation. */
 int ssb_scan_cl_set_tuning(int tuning);
 int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T,
                            int64_t C, void *workspace, size_t workspace_bytes, void *stream);

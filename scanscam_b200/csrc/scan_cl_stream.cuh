@@ -1,0 +1,215 @@
+// Channels-last streaming kernels: dense fp32 [N, T, C] (C % 4 == 0, 16-byte aligned base), scan
+// over T, for problems with enough independent (batch element, channel block) pairs to fill the
+// GPU without splitting T.  Replaces the reference's transposed kernels
+// (src/scanscam_cuda.cu:471-723) on such shapes.
+//
+//   * A unit of work is one batch element and CC adjacent channels; a CTA owns a unit and walks
+//     its T steps in tiles of TT steps, forward kernels from step 0 up, backward kernels from the
+//     last step down.  The carry from tile to tile is a float4 in registers: no workspace, no
+//     handshake between CTAs.
+//   * The tensor is described to the TMA as {C, T, N}; one `cp.async.bulk.tensor.3d` box
+//     {CC, TT, 1} per input brings a tile into a ring of shared-memory stages (mbarrier
+//     completion), STAGES tiles ahead of the arithmetic and across unit boundaries.  Steps past
+//     T and channels past C arrive as zeros and are clipped on the way out.  The backward fetches
+//     h with a box that starts one step earlier (h_{t-1}; step -1 reads the fill value 0).
+//   * Thread (seg, cg) owns 4 adjacent channels (one float4 per step) and the seg-th run of
+//     TS = TT/SEG steps.  It folds its run sequentially, the runs of a warp are composed with
+//     shuffles, the warps' totals cross through shared memory (one barrier), and the thread
+//     replays its run from its now-known starting value: ~5 instructions per element.
+//     The 8 (or 16) threads of a quarter warp read one contiguous 128-byte row: no bank conflicts.
+//   * Results go to a staging tile and leave through one bulk tensor store per tile.
+//
+// Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
+#pragma once
+
+#include <cuda.h>
+
+#include "scan_common.cuh"
+#include "scan_tma.cuh"
+
+namespace ssb {
+namespace cls {
+
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+struct Config {
+    static constexpr int CG = CC / 4;            // float4 channel groups per tile row
+    static constexpr int THREADS = CG * SEG;
+    static constexpr int TS = TT / SEG;          // steps per thread
+    static constexpr int SPW = 32 / CG;          // segments per warp
+    static constexpr int NW = THREADS / 32;
+    static constexpr int N_IN = BWD ? 3 : 2;
+    static constexpr int N_OUT = BWD ? 2 : 1;
+    static constexpr int TILE = TT * CC * 4;
+    static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 128;
+    static_assert(CC == 32 || CC == 64 || CC == 128, "a tile row is 8, 16 or 32 float4s: whole quarter warps");
+    static_assert(TT % SEG == 0 && THREADS % 32 == 0 && THREADS <= 1024 && TT <= 256, "tile shape");
+    static_assert(STAGES >= 1 && OUTBUF >= 1, "ring sizes");
+};
+
+struct Map4 {  // four affine maps x -> A*x + B, one per channel of a float4
+    float4 A, B;
+};
+
+__device__ __forceinline__ float4 fma4(float4 a, float4 x, float4 b) {
+    return make_float4(fmaf(a.x, x.x, b.x), fmaf(a.y, x.y, b.y), fmaf(a.z, x.z, b.z), fmaf(a.w, x.w, b.w));
+}
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 shfl4(float4 v, int delta, bool up) {
+    float4 r;
+    if (up) {
+        r.x = __shfl_up_sync(kFullMask, v.x, delta); r.y = __shfl_up_sync(kFullMask, v.y, delta);
+        r.z = __shfl_up_sync(kFullMask, v.z, delta); r.w = __shfl_up_sync(kFullMask, v.w, delta);
+    } else {
+        r.x = __shfl_down_sync(kFullMask, v.x, delta); r.y = __shfl_down_sync(kFullMask, v.y, delta);
+        r.z = __shfl_down_sync(kFullMask, v.z, delta); r.w = __shfl_down_sync(kFullMask, v.w, delta);
+    }
+    return r;
+}
+
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+__global__ void __launch_bounds__(CC / 4 * SEG)
+cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
+                 const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
+                 const __grid_constant__ CUtensorMap map_out2, int64_t n_units, int cblocks, int pieces) {
+    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD>;
+    constexpr int CG = Cfg::CG, TS = Cfg::TS, SPW = Cfg::SPW, NW = Cfg::NW, N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT,
+                  TILE = Cfg::TILE;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ float4 s_tot[2][NW][CG][2];  // per warp and channel group: the warp's composed map (A, B)
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cg = tid % CG, seg = tid / CG;       // seg = warp * SPW + (lane / CG)
+    const int seg_in_warp = lane / CG;
+    const uint32_t smem0 = (tma::smem_u32(smem_raw) + 127u) & ~127u;
+    const uint32_t out_base = smem0 + STAGES * N_IN * TILE;
+    const uint32_t bar0 = tma::smem_u32(&full_bar[0]);
+    const int64_t my_units = (int64_t)blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t n_items = my_units * pieces;
+    // byte offset of this thread's float4 at its first step inside a tile
+    const uint32_t my_off = (uint32_t)((seg * TS * CC + cg * 4) * 4);
+
+    auto coords = [&](int64_t i, int &c0, int &t0, int &n) {
+        const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
+        const int piece = (int)(i % pieces);
+        n = (int)(unit / cblocks);
+        c0 = (int)(unit % cblocks) * CC;
+        t0 = (BWD ? pieces - 1 - piece : piece) * TT;
+    };
+    auto issue = [&](int64_t i) {  // thread 0: loads of this CTA's i-th tile into stage i % STAGES
+        const int stage = (int)(i % STAGES);
+        int c0, t0, n;
+        coords(i, c0, t0, n);
+        const uint32_t bar = bar0 + 8 * stage, dst = smem0 + stage * N_IN * TILE;
+        tma::mbar_expect_tx(bar, N_IN * TILE);
+        tma::load_box(dst, &map_gate, c0, t0, n, bar);
+        tma::load_box(dst + TILE, &map_in1, c0, BWD ? t0 - 1 : t0, n, bar);  // backward: h one step earlier
+        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, c0, t0, n, bar);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) tma::mbar_init(bar0 + 8 * s, 1);
+        tma::fence_mbar_init();
+        for (int64_t i = 0; i < STAGES && i < n_items; i++) issue(i);
+    }
+    __syncthreads();
+
+    bool timed_out = false;
+    unsigned phase_bits = 0u;
+    int out_slot = 0, buf = 0;
+    float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);  // state entering the tile, for this thread's 4 channels
+    const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int64_t i = 0; i < n_items; i++) {
+        const int stage = (int)(i % STAGES);
+        const uint32_t in0 = smem0 + stage * N_IN * TILE + my_off;
+        if (i % pieces == 0) carry = zero4;  // a new unit starts
+        if (!tma::mbar_wait_bounded(bar0 + 8 * stage, (phase_bits >> stage) & 1u)) timed_out = true;
+        phase_bits ^= 1u << stage;
+
+        float4 a[TS], x[TS], y[TS];  // x: value | h one step earlier ; y: unused | gout
+#pragma unroll
+        for (int k = 0; k < TS; k++) {
+            a[k] = tma::lds128(in0 + k * CC * 4);
+            x[k] = tma::lds128(in0 + TILE + k * CC * 4);
+            if (BWD) y[k] = tma::lds128(in0 + 2 * TILE + k * CC * 4);
+        }
+        // This thread's run as one map, then the runs of the warp composed (forward: left to
+        // right, lower segments first; backward: right to left).
+        Map4 m;
+        if (!BWD) {
+            m.A = a[0]; m.B = x[0];
+#pragma unroll
+            for (int k = 1; k < TS; k++) { m.B = fma4(a[k], m.B, x[k]); m.A = mul4(m.A, a[k]); }
+        } else {
+            m.A = one4; m.B = zero4;
+#pragma unroll
+            for (int k = TS - 1; k >= 0; k--) { m.B = mul4(a[k], add4(y[k], m.B)); m.A = mul4(m.A, a[k]); }
+        }
+#pragma unroll
+        for (int d = 1; d < SPW; d <<= 1) {
+            const float4 pA = shfl4(m.A, d * CG, !BWD), pB = shfl4(m.B, d * CG, !BWD);
+            const bool has = BWD ? (seg_in_warp + d < SPW) : (seg_in_warp >= d);
+            if (has) { m.B = fma4(m.A, pB, m.B); m.A = mul4(m.A, pA); }
+        }
+        if (seg_in_warp == (BWD ? 0 : SPW - 1)) {
+            s_tot[buf][warp][cg][0] = m.A;
+            s_tot[buf][warp][cg][1] = m.B;
+        }
+        if (tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
+        __syncthreads();
+        // Every thread holds its tile data in registers: this very stage can be refilled now.
+        if (tid == 0 && i + STAGES < n_items) issue(i + STAGES);
+
+        // State entering this warp's runs, and the state leaving the tile (the next carry).
+        float4 s = carry, run = carry;
+#pragma unroll
+        for (int q = 0; q < NW; q++) {
+            const int w = BWD ? NW - 1 - q : q;
+            const float4 tA = s_tot[buf][w][cg][0], tB = s_tot[buf][w][cg][1];
+            if (w == warp) s = run;
+            run = fma4(tA, run, tB);
+        }
+        carry = run;
+        // ... and this thread's own run: the exclusive prefix inside the warp
+        {
+            float4 eA = shfl4(m.A, CG, !BWD), eB = shfl4(m.B, CG, !BWD);
+            if (seg_in_warp == (BWD ? SPW - 1 : 0)) { eA = one4; eB = zero4; }
+            s = fma4(eA, s, eB);
+        }
+
+        const uint32_t ob = out_base + out_slot * N_OUT * TILE + my_off;
+        if (!BWD) {
+#pragma unroll
+            for (int k = 0; k < TS; k++) {
+                s = fma4(a[k], s, x[k]);
+                tma::sts128(ob + k * CC * 4, s);
+            }
+        } else {
+#pragma unroll
+            for (int k = TS - 1; k >= 0; k--) {
+                const float4 gb = add4(y[k], s);
+                s = mul4(a[k], gb);
+                tma::sts128(ob + k * CC * 4, mul4(gb, x[k]));   // grad of gate = gb_t * h_{t-1}
+                tma::sts128(ob + TILE + k * CC * 4, gb);        // grad of value
+            }
+        }
+        tma::fence_async_smem();
+        __syncthreads();
+        if (tid == 0) {
+            int c0, t0, n;
+            coords(i, c0, t0, n);
+            tma::store_box(&map_out1, c0, t0, n, ob - my_off);
+            if (BWD) tma::store_box(&map_out2, c0, t0, n, ob - my_off + TILE);
+            tma::store_commit();
+        }
+        out_slot = (out_slot + 1 == OUTBUF) ? 0 : out_slot + 1;
+        buf ^= 1;
+    }
+    if (tid == 0) tma::store_wait_read<0>();
+    if (timed_out && lane == 0) report_device_wait(7);
+}
+
+}  // namespace cls
+}  // namespace ssb

@@ -214,7 +214,8 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         if (lane == (BWD ? 0 : 31)) s_tot[buf][warp] = make_float2(A, B);
         if (tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
         __syncthreads();
-        // Every thread holds its span data in registers: the stage can be refilled now.
+        // Every thread holds its span data in registers: the stage can be refilled now.  (Refilling
+        // the stage just read instead, one span deeper, measured 1-2 % slower.)
         if (tid == 0 && i + STAGES - 1 < my_spans) issue(i + STAGES - 1);
 
         // Start value of this warp (maps of the warps processed before it) and of this lane.

@@ -15,6 +15,7 @@
 
 #include "scan_cl.cuh"
 #include "scan_cl_lookback.cuh"
+#include "scan_cl_stream.cuh"
 #include "scan_cl_tma.cuh"
 #include "scan_common.cuh"
 #include "scan_flat.cuh"
@@ -1046,6 +1047,48 @@ int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_
     return SSB_OK;
 }
 
+// Channels-last streaming kernels (one CTA walks all of T for a block of channels, tiles through a
+// TMA ring, no workspace).  Tuning ids 64 + k -> (CC, TT, segments, stages, out buffers) forward | backward.
+// Ids 0 and 1 are the defaults for 32- and 64-channel blocks, picked from a sweep of 73 forward and
+// 37 backward tile shapes on [8,4096,512], [64,4096,512], [16,2048,1024], [1,16384,8192] and
+// [32,1024,2048]: large tiles win (the per-tile barriers and store hand-off are the fixed cost).
+#define SSB_CLS_CONFIGS(X)                                                                   \
+    X(0, 32, 256, 16, 2, 2, 32, 128, 16, 2, 1) X(1, 64, 256, 16, 1, 1, 64, 128, 8, 1, 1)     \
+    X(2, 32, 128, 16, 2, 2, 32, 256, 16, 1, 1) X(3, 64, 128, 8, 2, 2, 64, 64, 8, 2, 1)       \
+    X(4, 32, 64, 8, 2, 2, 32, 64, 16, 2, 1) X(5, 64, 64, 8, 2, 1, 64, 64, 4, 2, 1)           \
+    X(6, 128, 32, 8, 3, 2, 128, 32, 8, 2, 1) X(7, 32, 128, 32, 2, 1, 32, 128, 32, 2, 1)
+
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+int launch_cls(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+               int64_t C, cudaStream_t st) {
+    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD>;
+    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD>;
+    const int64_t cblocks = (C + CC - 1) / CC, pieces = (T + TT - 1) / TT;
+    if (pieces > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
+    CUtensorMap mg, m1, m2, mo1, mo2;
+    int rc;
+    if ((rc = make_cl_map(&mg, gate, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m1, in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m2, BWD ? in2 : in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo1, out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo2, BWD ? out2 : out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(cl_stream_kernel)");
+    static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
+    int occ = cached_occ.load(std::memory_order_relaxed);
+    if (occ == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::THREADS, Cfg::SMEM_BYTES) != cudaSuccess || occ <= 0) {
+            (void)cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ.store(occ, std::memory_order_relaxed);
+    }
+    const int64_t units = N * cblocks, cap = (int64_t)sm_count() * occ;
+    const int grid = (int)(units < cap ? units : cap);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces);
+    return check_launch("cl_stream_kernel");
+}
+
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
 int launch_cl3(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
                int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
@@ -1127,9 +1170,39 @@ int cl_bwd(const real *gate, const real *h, const real *gout, real *ggate, real 
 }
 }  // namespace
 
+namespace {
+constexpr int kClForcePlain = 0x200;  // ssb_scan_cl_set_tuning: the plain kernels, whatever the shape
+
+// Channel-block width of the streaming kernels for this shape, or 0 when they do not apply: they
+// need a TMA-describable tensor, rows long enough to fill their 128-256 step tiles, and enough
+// (batch element, channel block) pairs to occupy the GPU without splitting T (measured on B200:
+// 128 pairs of 64 channels when rows have at least 1024 steps and C fills 64-channel blocks, else
+// 96 pairs of 32 channels; below that the look-back kernels win).
+int cl_stream_block(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
+    if (!all_aligned16 || !cl3_eligible(N, T, C) || T < 128 || encode_fn() == nullptr) return 0;
+    if (T >= 1024 && (C % 64 == 0 || C >= 512) && N * ((C + 63) / 64) >= 128) return 64;
+    if (N * ((C + 31) / 32) >= 96) return 32;
+    return 0;
+}
+
+int cl_stream_fwd(int block, const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, cudaStream_t st) {
+    return block == 64 ? launch_cls<64, 256, 16, 1, 1, false>(gate, value, nullptr, out, nullptr, N, T, C, st)
+                       : launch_cls<32, 256, 16, 2, 2, false>(gate, value, nullptr, out, nullptr, N, T, C, st);
+}
+int cl_stream_bwd(int block, const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
+                  int64_t T, int64_t C, cudaStream_t st) {
+    return block == 64 ? launch_cls<64, 128, 8, 1, 1, true>(gate, h, gout, ggate, gvalue, N, T, C, st)
+                       : launch_cls<32, 128, 16, 2, 1, true>(gate, h, gout, ggate, gvalue, N, T, C, st);
+}
+}  // namespace
+
 extern "C" {
 
 int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, void *stream) {
+    if (t_cl_tuning != kClForcePlain && N > 0 && T > 0 && C > 0 && gate && value && out) {
+        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16));
+        if (block) return cl_stream_fwd(block, gate, value, out, N, T, C, static_cast<cudaStream_t>(stream));
+    }
     return cl_fwd<float>(gate, value, out, N, T, C, stream);
 }
 
@@ -1178,6 +1251,11 @@ int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, in
     int rc = check_cl(N, T, C, &n);
     if (rc != SSB_OK) return rc;
     if (n == 0) return SSB_OK;
+    if (t_cl_tuning == kClForcePlain) return cl_fwd<float>(gate, value, out, N, T, C, stream);
+    if (t_cl_tuning == 0 && gate && value && out) {
+        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16));
+        if (block) return cl_stream_fwd(block, gate, value, out, N, T, C, static_cast<cudaStream_t>(stream));
+    }
     if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
         (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
         return cl_fwd<float>(gate, value, out, N, T, C, stream);
@@ -1187,6 +1265,16 @@ int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, in
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16) &&
                      !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) >= 64) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        switch ((t_cl_tuning & 0xff) - 64) {
+#define X(ID, FC, FT, FG, FS, FO, BC, BT, BG, BS, BO) case ID: return launch_cls<FC, FT, FG, FS, FO, false>(gate, value, nullptr, out, nullptr, N, T, C, st);
+            SSB_CLS_CONFIGS(X)
+#undef X
+            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last streaming tuning id %d", t_cl_tuning);
+        }
+    }
     if ((t_cl_tuning & 0xff) >= 32) {
         if (!vec || !cl3_eligible(N, T, C))
             return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
@@ -1212,6 +1300,12 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
     int rc = check_cl(N, T, C, &n);
     if (rc != SSB_OK) return rc;
     if (n == 0) return SSB_OK;
+    if (t_cl_tuning == kClForcePlain) return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
+    if (t_cl_tuning == 0 && gate && h && gout && ggate && gvalue) {
+        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
+                                                       aligned_to(ggate, 16) && aligned_to(gvalue, 16));
+        if (block) return cl_stream_bwd(block, gate, h, gout, ggate, gvalue, N, T, C, static_cast<cudaStream_t>(stream));
+    }
     if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
         (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
         return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
@@ -1221,6 +1315,16 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                      aligned_to(ggate, 16) && aligned_to(gvalue, 16) && !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) >= 64) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        switch ((t_cl_tuning & 0xff) - 64) {
+#define X(ID, FC, FT, FG, FS, FO, BC, BT, BG, BS, BO) case ID: return launch_cls<BC, BT, BG, BS, BO, true>(gate, h, gout, ggate, gvalue, N, T, C, st);
+            SSB_CLS_CONFIGS(X)
+#undef X
+            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last streaming tuning id %d", t_cl_tuning);
+        }
+    }
     if ((t_cl_tuning & 0xff) >= 32) {
         if (!vec || !cl3_eligible(N, T, C))
             return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
@@ -1244,6 +1348,11 @@ int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, in
 }
 int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
                         int64_t T, int64_t C, void *stream) {
+    if (t_cl_tuning != kClForcePlain && N > 0 && T > 0 && C > 0 && gate && h && gout && ggate && gvalue) {
+        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
+                                                       aligned_to(ggate, 16) && aligned_to(gvalue, 16));
+        if (block) return cl_stream_bwd(block, gate, h, gout, ggate, gvalue, N, T, C, static_cast<cudaStream_t>(stream));
+    }
     return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
 }
 int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate, double *gvalue,

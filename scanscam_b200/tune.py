@@ -102,7 +102,10 @@ def time_channels_last(lib, N, T, C, iters):
         return best
 
     rows = []
-    for label, tuning, use_ws in (("plain", 0, False), ("lookback", 1, True), ("auto", 0, True)):
+    modes = [("plain", 0x200, False), ("lookback", 1, True), ("auto", 0, True)]
+    if C % 4 == 0:  # streaming kernels (a CTA walks all of T through a TMA ring), every tile shape
+        modes += [(f"stream{k}", 64 + k, True) for k in range(8)]
+    for label, tuning, use_ws in modes:
         lib.ssb_scan_cl_set_tuning(tuning)
         p, nb = (ws.data_ptr(), need) if use_ws else (None, 0)
         tf = run(lambda: lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, p, nb, st))

@@ -73,6 +73,12 @@ def cl_fwd(a, b, scratch=False):
     lib = _native.load()
     out = torch.empty_like(a)
     N, T, C = a.shape
+    if scratch == "plain":  # the plain kernels, whatever the library would pick
+        lib.ssb_scan_cl_set_tuning(0x200)
+        rc = lib.ssb_scan_cl_fwd_f32(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, _native.stream_of(a))
+        lib.ssb_scan_cl_set_tuning(0)
+        _native.check(rc)
+        return out
     if scratch:
         ws, need = cl_workspace(a)
         lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)  # always look-back
@@ -89,6 +95,13 @@ def cl_bwd(a, h, g, scratch=False):
     lib = _native.load()
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     N, T, C = a.shape
+    if scratch == "plain":
+        lib.ssb_scan_cl_set_tuning(0x200)
+        rc = lib.ssb_scan_cl_bwd_f32(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C,
+                                     _native.stream_of(a))
+        lib.ssb_scan_cl_set_tuning(0)
+        _native.check(rc)
+        return ga, gb
     if scratch:
         ws, need = cl_workspace(a)
         lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)

@@ -68,7 +68,9 @@ def test_golden_vectors(name):
 def test_golden_vectors_channels_last(name):
     c = {k: GOLDEN[f"{name}/{k}"] for k in ("a", "b", "g", "h", "ga", "gb")}
     a, b, g, h_ref = (dev(c[k]) for k in ("a", "b", "g", "h"))
-    for scratch in ([False, True] if a.dtype == torch.float32 else [False]):
+    for scratch in ([False, True, "plain", 64, 65] if a.dtype == torch.float32 else [False]):
+        if isinstance(scratch, int) and scratch >= 64 and a.shape[2] % 4:
+            continue
         h = _gpu.cl_fwd(a, b, scratch=scratch)
         ga, gb = _gpu.cl_bwd(a, h_ref, g, scratch=scratch)
         for got, key in ((h, "h"), (ga, "ga"), (gb, "gb")):
@@ -79,7 +81,7 @@ def test_golden_vectors_channels_last(name):
 # [N, T, C]: wide, narrow, odd C (scalar path), C % 4 == 0 but not a multiple of 128, one long
 # sequence with few channels (many tiles chained by look-back), T below one tile, unaligned base
 @pytest.mark.parametrize("shape", [(2, 300, 512), (3, 107, 197), (5, 613, 107), (2, 1000, 36), (1, 20000, 8),
-                                   (1, 70000, 128), (4, 5, 64), (2, 64, 4), (16, 257, 256)])
+                                   (1, 70000, 128), (4, 5, 64), (2, 64, 4), (16, 257, 256), (32, 300, 256), (3, 700, 1100)])
 @pytest.mark.parametrize("gates", ["randn", "nearunit"])
 def test_channels_last_with_scratch(shape, gates):
     a, b, g = make_inputs(gates, shape, seed=29)
@@ -87,9 +89,12 @@ def test_channels_last_with_scratch(shape, gates):
     h_ref = oracle.scan_forward_channels_last(an, bn)
     ga_ref, gb_ref = oracle.scan_backward_channels_last(an, h_ref, gn)
     da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
-    modes = [True, 12, 7, False]  # look-back: default tile and two other tile shapes; plain kernels
+    modes = [True, 12, 7, False]  # look-back: default tile and two other tile shapes; the library's own choice
+    if a.dtype == torch.float32:
+        modes.append("plain")
     if shape[2] % 4 == 0:
         modes += [32, 33, 34, 35, 36, 37]  # TMA-staged tiles, every tile shape of the table
+        modes += list(range(64, 72))  # streaming kernels (a CTA walks all of T), every tile shape
     for scratch in modes:
         h = _gpu.cl_fwd(da, db, scratch=scratch)
         ga, gb = _gpu.cl_bwd(da, dh, dg, scratch=scratch)
