@@ -164,6 +164,26 @@ int ssb_scan_fwd_f16(const void *gate, const void *value, void *out, int64_t row
                      const float *h_in, void *stream);
 int ssb_scan_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue,
                      int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream);
+/* The fused forms on 16-bit tensors: gate logits in (as ssb_scan_sigmoid_*_f32) and the backward
+ * that recomputes h from (gate, value) (as ssb_scan_bwd_recompute_f32, no workspace).  Rows of
+ * T = 64 * 2^k <= 8192 and 16-byte aligned tensors only; SSB_ERR_UNSUPPORTED otherwise (compose
+ * them from the plain entry points).  The recomputed h is the fp32 one, not its 16-bit rounding. */
+int ssb_scan_sigmoid_fwd_bf16(const void *gate_logits, const void *value, void *out, int64_t rows,
+                              int64_t T, const float *h_in, void *stream);
+int ssb_scan_sigmoid_bwd_bf16(const void *gate_logits, const void *h, const void *gout, void *glogits,
+                              void *gvalue, int64_t rows, int64_t T, const float *c_in,
+                              const float *h_prev, void *stream);
+int ssb_scan_sigmoid_fwd_f16(const void *gate_logits, const void *value, void *out, int64_t rows,
+                             int64_t T, const float *h_in, void *stream);
+int ssb_scan_sigmoid_bwd_f16(const void *gate_logits, const void *h, const void *gout, void *glogits,
+                             void *gvalue, int64_t rows, int64_t T, const float *c_in,
+                             const float *h_prev, void *stream);
+int ssb_scan_bwd_recompute_bf16(const void *gate, const void *value, const void *gout, void *ggate,
+                                void *gvalue, int64_t rows, int64_t T, const float *h_in,
+                                const float *c_in, void *stream);
+int ssb_scan_bwd_recompute_f16(const void *gate, const void *value, const void *gout, void *ggate,
+                               void *gvalue, int64_t rows, int64_t T, const float *h_in,
+                               const float *c_in, void *stream);
 
 /* ------------------------------------------------------------------------------------
  * Backward that recomputes h (no counterpart in the reference, whose op.Scan.forward saves both

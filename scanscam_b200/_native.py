@@ -34,6 +34,12 @@ SIGNATURES = {
     "ssb_scan_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
     "ssb_scan_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
     "ssb_scan_bwd_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_sigmoid_fwd_bf16": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
+    "ssb_scan_sigmoid_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_sigmoid_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
+    "ssb_scan_sigmoid_bwd_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_bwd_recompute_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
+    "ssb_scan_bwd_recompute_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
     "ssb_scan_bwd_recompute_workspace_bytes": (_sz, [_i64, _i64]),
     "ssb_scan_bwd_recompute_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p, _sz, _p]),
     "ssb_scan_workspace_bytes": (_sz, [_i64, _i64, _int]),

@@ -889,7 +889,9 @@ int ssb_scan_bwd_f64(const double *gate, const double *h, const double *gout, do
 // ---- 16-bit storage (bf16 / fp16 in memory, fp32 arithmetic and carries) --------------------
 namespace {
 
-template <typename IO>
+// SIGMOID / RECOMPUTE as in the fp32 entry points; those forms exist on the bulk-tensor sweep only
+// (rows of T = 64 * 2^k <= 8192, 16-byte aligned), other shapes return SSB_ERR_UNSUPPORTED.
+template <typename IO, bool SIGMOID = false>
 int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows, int64_t T, const float *h_in,
                  void *stream, const char *who) {
     int64_t n;
@@ -906,11 +908,13 @@ int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows
     if (al16 && encode_fn() != nullptr) {
         // configurations from a sweep on [16384,4096], [65536,2048], [524288,512] and [262144,64]
         if (tmaflat_eligible(rows, T, 64, 2))
-            return T > 2048 ? launch_tmaflat<64, 2, 1, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st)
-                            : launch_tmaflat<64, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+            return T > 2048 ? launch_tmaflat<64, 2, 1, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st)
+                            : launch_tmaflat<64, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         if (tmaflat_eligible(rows, T, 128, 2))
-            return launch_tmaflat<128, 2, 2, false, false, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+            return launch_tmaflat<128, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
     }
+    if (SIGMOID)
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 and 16-byte aligned tensors (T=%lld)", who, (long long)T);
     const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
     if (al16 && T % 8 == 0)
         ssb::warp_rows_fwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, nullptr);
@@ -919,7 +923,7 @@ int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows
     return check_launch("warp_rows_fwd_kernel<16-bit>");
 }
 
-template <typename IO>
+template <typename IO, bool SIGMOID = false, bool RECOMPUTE = false>
 int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *ggate_, void *gvalue_, int64_t rows, int64_t T,
                  const float *c_in, const float *h_prev, void *stream, const char *who) {
     int64_t n;
@@ -937,10 +941,12 @@ int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *gga
                       aligned_to(gvalue, 16);
     if (al16 && encode_fn() != nullptr) {
         if (tmaflat_eligible(rows, T, 64, 2))
-            return launch_tmaflat<64, 2, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+            return launch_tmaflat<64, 2, 1, true, SIGMOID, RECOMPUTE, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         if (tmaflat_eligible(rows, T, 128, 2))
-            return launch_tmaflat<128, 3, 1, true, false, false, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+            return launch_tmaflat<128, 3, 1, true, SIGMOID, RECOMPUTE, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
     }
+    if (SIGMOID || RECOMPUTE)
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 and 16-byte aligned tensors (T=%lld)", who, (long long)T);
     const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
     if (al16 && T % 8 == 0)
         ssb::warp_rows_bwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr);
@@ -966,6 +972,34 @@ int ssb_scan_bwd_bf16(const void *gate, const void *h, const void *gout, void *g
 int ssb_scan_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t rows, int64_t T,
                      const float *c_in, const float *h_prev, void *stream) {
     return scan_bwd_h16<__half>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, stream, "ssb_scan_bwd_f16");
+}
+int ssb_scan_sigmoid_fwd_bf16(const void *gate_logits, const void *value, void *out, int64_t rows, int64_t T, const float *h_in,
+                              void *stream) {
+    return scan_fwd_h16<__nv_bfloat16, true>(gate_logits, value, out, rows, T, h_in, stream, "ssb_scan_sigmoid_fwd_bf16");
+}
+int ssb_scan_sigmoid_bwd_bf16(const void *gate_logits, const void *h, const void *gout, void *glogits, void *gvalue,
+                              int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream) {
+    return scan_bwd_h16<__nv_bfloat16, true>(gate_logits, h, gout, glogits, gvalue, rows, T, c_in, h_prev, stream,
+                                             "ssb_scan_sigmoid_bwd_bf16");
+}
+int ssb_scan_sigmoid_fwd_f16(const void *gate_logits, const void *value, void *out, int64_t rows, int64_t T, const float *h_in,
+                             void *stream) {
+    return scan_fwd_h16<__half, true>(gate_logits, value, out, rows, T, h_in, stream, "ssb_scan_sigmoid_fwd_f16");
+}
+int ssb_scan_sigmoid_bwd_f16(const void *gate_logits, const void *h, const void *gout, void *glogits, void *gvalue,
+                             int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream) {
+    return scan_bwd_h16<__half, true>(gate_logits, h, gout, glogits, gvalue, rows, T, c_in, h_prev, stream,
+                                      "ssb_scan_sigmoid_bwd_f16");
+}
+int ssb_scan_bwd_recompute_bf16(const void *gate, const void *value, const void *gout, void *ggate, void *gvalue, int64_t rows,
+                                int64_t T, const float *h_in, const float *c_in, void *stream) {
+    return scan_bwd_h16<__nv_bfloat16, false, true>(gate, value, gout, ggate, gvalue, rows, T, c_in, h_in, stream,
+                                                    "ssb_scan_bwd_recompute_bf16");
+}
+int ssb_scan_bwd_recompute_f16(const void *gate, const void *value, const void *gout, void *ggate, void *gvalue, int64_t rows,
+                               int64_t T, const float *h_in, const float *c_in, void *stream) {
+    return scan_bwd_h16<__half, false, true>(gate, value, gout, ggate, gvalue, rows, T, c_in, h_in, stream,
+                                             "ssb_scan_bwd_recompute_f16");
 }
 
 }  // extern "C"

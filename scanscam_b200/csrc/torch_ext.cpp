@@ -172,10 +172,18 @@ void scan_backward_ex(torch::Tensor gate, torch::Tensor output, torch::Tensor ou
 // ---- gate logits in, sigmoid fused (not in the reference) --------------------------------
 void scan_sigmoid_forward(torch::Tensor logits, torch::Tensor value, torch::Tensor output) {
     check_tensor(logits, "gate_logits");
-    TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kFloat32, "gate_logits must be 2-D float32");
+    TORCH_CHECK(logits.dim() == 2 && (logits.scalar_type() == torch::kFloat32 || is_16bit(logits)),
+                "gate_logits must be 2-D float32, bfloat16 or float16");
     check_same(logits, value, "value");
     check_same(logits, output, "output");
     c10::cuda::CUDAGuard guard(logits.device());
+    if (is_16bit(logits)) {
+        auto fn = logits.scalar_type() == torch::kBFloat16 ? ssb_scan_sigmoid_fwd_bf16 : ssb_scan_sigmoid_fwd_f16;
+        raise_on(fn(logits.data_ptr(), value.data_ptr(), output.data_ptr(), logits.size(0), logits.size(1), nullptr,
+                    current_stream()),
+                 "scan_sigmoid_forward");
+        return;
+    }
     raise_on(ssb_scan_sigmoid_fwd_f32(logits.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(),
                                       logits.size(0), logits.size(1), nullptr, current_stream()),
              "scan_sigmoid_forward");
@@ -184,12 +192,20 @@ void scan_sigmoid_forward(torch::Tensor logits, torch::Tensor value, torch::Tens
 void scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output, torch::Tensor outGrad, torch::Tensor logitsGradOut,
                            torch::Tensor valueGradOut) {
     check_tensor(logits, "gate_logits");
-    TORCH_CHECK(logits.dim() == 2 && logits.scalar_type() == torch::kFloat32, "gate_logits must be 2-D float32");
+    TORCH_CHECK(logits.dim() == 2 && (logits.scalar_type() == torch::kFloat32 || is_16bit(logits)),
+                "gate_logits must be 2-D float32, bfloat16 or float16");
     check_same(logits, output, "output");
     check_same(logits, outGrad, "outGrad");
     check_same(logits, logitsGradOut, "logitsGradOut");
     check_same(logits, valueGradOut, "valueGradOut");
     c10::cuda::CUDAGuard guard(logits.device());
+    if (is_16bit(logits)) {
+        auto fn = logits.scalar_type() == torch::kBFloat16 ? ssb_scan_sigmoid_bwd_bf16 : ssb_scan_sigmoid_bwd_f16;
+        raise_on(fn(logits.data_ptr(), output.data_ptr(), outGrad.data_ptr(), logitsGradOut.data_ptr(),
+                    valueGradOut.data_ptr(), logits.size(0), logits.size(1), nullptr, nullptr, current_stream()),
+                 "scan_sigmoid_backward");
+        return;
+    }
     raise_on(ssb_scan_sigmoid_bwd_f32(logits.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
                                       logitsGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), logits.size(0),
                                       logits.size(1), nullptr, nullptr, current_stream()),
@@ -200,12 +216,20 @@ void scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output, torch::Te
 void scan_backward_recompute(torch::Tensor gate, torch::Tensor value, torch::Tensor outGrad, torch::Tensor gateGradOut,
                              torch::Tensor valueGradOut) {
     check_tensor(gate, "gate");
-    TORCH_CHECK(gate.dim() == 2 && gate.scalar_type() == torch::kFloat32, "gate must be 2-D float32");
+    TORCH_CHECK(gate.dim() == 2 && (gate.scalar_type() == torch::kFloat32 || is_16bit(gate)),
+                "gate must be 2-D float32, bfloat16 or float16");
     check_same(gate, value, "value");
     check_same(gate, outGrad, "outGrad");
     check_same(gate, gateGradOut, "gateGradOut");
     check_same(gate, valueGradOut, "valueGradOut");
     c10::cuda::CUDAGuard guard(gate.device());
+    if (is_16bit(gate)) {
+        auto fn = gate.scalar_type() == torch::kBFloat16 ? ssb_scan_bwd_recompute_bf16 : ssb_scan_bwd_recompute_f16;
+        raise_on(fn(gate.data_ptr(), value.data_ptr(), outGrad.data_ptr(), gateGradOut.data_ptr(), valueGradOut.data_ptr(),
+                    gate.size(0), gate.size(1), nullptr, nullptr, current_stream()),
+                 "scan_backward_recompute");
+        return;
+    }
     const size_t ws_bytes = ssb_scan_bwd_recompute_workspace_bytes(gate.size(0), gate.size(1));
     torch::Tensor ws;
     if (ws_bytes > 0) ws = scratch(ws_bytes, gate);

@@ -4,8 +4,9 @@ The reference operator takes ready-made gates (scanscam/op.py:13-21); its users 
 ``gate = sigmoid(logits)`` in a separate elementwise pass before it and multiply by
 ``gate * (1 - gate)`` after its backward.  Taking the logits directly removes one read and one
 write of a full tensor from each direction (20 -> 12 bytes per element forward, 32 -> 20
-backward).  The fused kernels cover float32 tensors whose last axis is a multiple of 4; other
-inputs are served by ``scan(torch.sigmoid(logits), value)``, i.e. the same operator unfused.
+backward).  The fused kernels cover float32 tensors whose last axis is a multiple of 4 and
+bfloat16 / float16 tensors whose last axis is 64 * 2^k <= 8192; other inputs are served by
+``scan(torch.sigmoid(logits), value)``, i.e. the same operator unfused.
 """
 from __future__ import annotations
 
@@ -17,10 +18,18 @@ from . import cuda
 from .op import scan
 
 
+def sweep_row_16bit(steps: int) -> bool:
+    """Row lengths the fused 16-bit kernels take: 64 * 2^k up to 8192."""
+    return steps % 64 == 0 and steps <= 8192 and (steps // 64) & (steps // 64 - 1) == 0
+
+
 def _fusable(*tensors: torch.Tensor) -> bool:
     t0 = tensors[0]
-    return (t0.device.type == "cuda" and t0.dtype == torch.float32 and t0.dim() >= 2 and t0.shape[-1] % 4 == 0
-            and all(t.data_ptr() % 16 == 0 for t in tensors))
+    if t0.device.type != "cuda" or t0.dim() < 2 or any(t.data_ptr() % 16 for t in tensors):
+        return False
+    if t0.dtype == torch.float32:
+        return t0.shape[-1] % 4 == 0
+    return t0.dtype in (torch.bfloat16, torch.float16) and sweep_row_16bit(t0.shape[-1])
 
 
 class ScanSigmoidGate(torch.autograd.Function):

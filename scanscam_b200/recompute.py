@@ -15,13 +15,15 @@ from typing import Any, Tuple
 import torch
 
 from . import cuda
+from .fused import sweep_row_16bit
 from .op import _CHANNELS_PER_BLOCK, _require_cuda, is_transpose_contig
 
 
 def _in_kernel(*tensors: torch.Tensor) -> bool:
     t0 = tensors[0]
-    return (t0.dtype == torch.float32 and t0.dim() >= 2 and all(t.is_contiguous() for t in tensors)
-            and all(t.data_ptr() % 16 == 0 for t in tensors))
+    if t0.dim() < 2 or not all(t.is_contiguous() and t.data_ptr() % 16 == 0 for t in tensors):
+        return False
+    return t0.dtype == torch.float32 or (t0.dtype in (torch.bfloat16, torch.float16) and sweep_row_16bit(t0.shape[-1]))
 
 
 class ScanRecompute(torch.autograd.Function):

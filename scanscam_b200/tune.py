@@ -178,6 +178,11 @@ def time_16bit(lib, rows, T, iters):
         tb = run(lambda: bwd(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))
         n = rows * T
         out.append((name, 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+        if name != "f32" and lib.ssb_scan_sigmoid_fwd_bf16(p[0], p[1], p[3], rows, T, None, st) == _native.OK:
+            sf, sb = getattr(lib, f"ssb_scan_sigmoid_fwd_{name}"), getattr(lib, f"ssb_scan_sigmoid_bwd_{name}")
+            tf = run(lambda: sf(p[0], p[1], p[3], rows, T, None, st))
+            tb = run(lambda: sb(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))
+            out.append((name + " fused sigmoid", 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
         del a, b, g, h, ga, gb
     return out
 
@@ -202,10 +207,10 @@ def main():
         if name.startswith("h16:"):  # 16-bit storage beside fp32: h16:ROWSxT
             rows, T = (int(v) for v in name[4:].lower().split("x"))
             print(f"# storage types, rows={rows} T={T} ({rows * T / 1e6:.0f} M elements per tensor)")
-            print(f"{'storage':8s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
+            print(f"{'storage':18s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
             for label, fg, tf, bg, tb, ge in time_16bit(lib, rows, T, args.iters):
                 results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
-                print(f"{label:8s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
+                print(f"{label:18s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
             continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))

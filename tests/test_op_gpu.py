@@ -212,7 +212,7 @@ def test_fused_sigmoid_gate_matches_unfused_oracle(shape):
     dz2, db2 = z.cuda().requires_grad_(True), b.cuda().requires_grad_(True)
     h2 = scanscam_b200.scan(torch.sigmoid(dz2), db2)
     h2.backward(g.cuda())
-    assert float((h - h2).abs().max() / h2.abs().max()) < 1e-5
+    assert float((h - h2).detach().abs().max() / h2.detach().abs().max()) < 1e-5
     assert float((dz.grad - dz2.grad).abs().max() / dz2.grad.abs().max()) < 1e-5
 
 
@@ -267,3 +267,34 @@ def test_scan_with_16bit_tensors(dtype, shape):
     for x, ref in ((h, h_ref), (da.grad, ga_ref), (db.grad, gb_ref)):
         assert x.dtype == dtype
         assert _gpu.max_norm_err(x.detach().float().reshape(-1, T), ref) < 1.01 * half_ulp
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(4, 16, 4096), (3, 5, 1000)])
+def test_fused_operators_with_16bit_tensors(dtype, shape):
+    """scan_sigmoid_gate and scan_recompute on bf16 / fp16 tensors against the plain operator run in
+    fp32 on the same inputs (the second shape takes the unfused / forward-again fallbacks)."""
+    z, b, g = make_inputs("randn", shape, seed=113)
+    z, b, g = (z + 1).to(dtype).cuda(), b.to(dtype).cuda(), g.to(dtype).cuda()
+    half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+
+    def close(x, ref, slack=3.0):
+        assert x.dtype == dtype
+        return float((x.detach().float() - ref).abs().max() / ref.abs().max()) < slack * half_ulp
+
+    zf, bf = z.float().requires_grad_(True), b.float().requires_grad_(True)
+    ref = scanscam_b200.scan(torch.sigmoid(zf), bf)
+    ref.backward(g.float())
+    z1, b1 = z.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    h = scanscam_b200.scan_sigmoid_gate(z1, b1)
+    h.backward(g)
+    assert close(h, ref.detach()) and close(z1.grad, zf.grad) and close(b1.grad, bf.grad)
+
+    a = torch.sigmoid(z.float()).to(dtype)
+    af, bf2 = a.float().requires_grad_(True), b.float().requires_grad_(True)
+    ref2 = scanscam_b200.scan(af, bf2)
+    ref2.backward(g.float())
+    a2, b2 = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    h2 = scanscam_b200.scan_recompute(a2, b2)
+    h2.backward(g)
+    assert close(h2, ref2.detach()) and close(a2.grad, af.grad) and close(b2.grad, bf2.grad)

@@ -571,3 +571,46 @@ def test_16bit_storage_matches_oracle(name, gates, shape):
         assert (err <= 1.001 * unit + 1e-6 * np.abs(ref).max()).all()
         exact = torch.from_numpy(ref).to(dtype).float().numpy()
         assert (got != exact).mean() < 1e-2  # all but a few rounding flips are the oracle's value rounded once
+
+
+@pytest.mark.parametrize("name", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(40, 4096), (130, 2048), (300, 64), (5, 8192)])
+def test_16bit_fused_entry_points(name, shape):
+    """Gate logits in and the h-recomputing backward on 16-bit tensors, with carries, against the
+    fp32 oracle on the rounded inputs; shapes outside the bulk-tensor sweep are refused."""
+    dtype, half_ulp = H16[name]
+    rows, T = shape
+    z, b, g = make_inputs("randn", shape, seed=111)
+    z, b, g = (z * 2 + 1).to(dtype), b.to(dtype), g.to(dtype)
+    a = torch.sigmoid(z.float())
+    carry = torch.randn(rows)
+    an, bn, gn, cn = a.numpy(), b.float().numpy(), g.float().numpy(), carry.numpy()
+    h_ref = oracle.scan_forward(an, bn, h_in=cn)
+    h16 = torch.from_numpy(h_ref).to(dtype)
+    ga_ref, gb_ref = oracle.scan_backward(an, h16.float().numpy(), gn, gb_in=cn, h_prev=cn)
+    gz_ref = ga_ref * (a * (1 - a)).numpy()
+    ga_exact, gb_exact = oracle.scan_backward(an, h_ref, gn, gb_in=cn, h_prev=cn)  # what a recomputed fp32 h gives
+    lib = _native.load()
+    dz, db, dg, dh, dc = z.cuda(), b.cuda(), g.cuda(), h16.cuda(), carry.cuda()
+    da = a.to(dtype).cuda()
+    h, gz, gb = torch.empty_like(dz), torch.empty_like(dz), torch.empty_like(dz)
+    st = _native.stream_of(dz)
+    _native.check(getattr(lib, f"ssb_scan_sigmoid_fwd_{name}")(dz.data_ptr(), db.data_ptr(), h.data_ptr(), rows, T,
+                                                                dc.data_ptr(), st))
+    _native.check(getattr(lib, f"ssb_scan_sigmoid_bwd_{name}")(dz.data_ptr(), dh.data_ptr(), dg.data_ptr(), gz.data_ptr(),
+                                                                gb.data_ptr(), rows, T, dc.data_ptr(), dc.data_ptr(), st))
+    for x, ref in ((h, h_ref), (gz, gz_ref), (gb, gb_ref)):
+        assert _gpu.max_norm_err(x.float(), ref) < 1.05 * half_ulp
+    # recompute: gates given (already rounded to the storage type), h rebuilt in fp32
+    a16 = da.float().cpu().numpy()
+    h_ref2 = oracle.scan_forward(a16, bn, h_in=cn)
+    ga_ref2, gb_ref2 = oracle.scan_backward(a16, h_ref2, gn, gb_in=cn, h_prev=cn)
+    ga2, gb2 = torch.empty_like(dz), torch.empty_like(dz)
+    _native.check(getattr(lib, f"ssb_scan_bwd_recompute_{name}")(da.data_ptr(), db.data_ptr(), dg.data_ptr(), ga2.data_ptr(),
+                                                                  gb2.data_ptr(), rows, T, dc.data_ptr(), dc.data_ptr(), st))
+    _gpu.device_ok()
+    assert _gpu.max_norm_err(ga2.float(), ga_ref2) < 1.05 * half_ulp
+    assert _gpu.max_norm_err(gb2.float(), gb_ref2) < 1.05 * half_ulp
+    # a row length the sweep does not take
+    rc = getattr(lib, f"ssb_scan_sigmoid_fwd_{name}")(dz.data_ptr(), db.data_ptr(), h.data_ptr(), rows * T // 96, 96, None, st)
+    assert rc == _native.ERR_UNSUPPORTED
