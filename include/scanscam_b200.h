@@ -233,21 +233,22 @@ int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, fl
 int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate,
                         double *gvalue, int64_t N, int64_t T, int64_t C, void *stream);
 
-/* Channels-last with scratch: the time axis is split across CTAs (decoupled look-back), so the
- * whole GPU is busy even when N*C is small.  `workspace` of ssb_scan_cl_workspace_bytes(N,T,C)
- * bytes, 256-byte aligned, contents irrelevant; NULL / 0 falls back to the kernels of the plain
- * entry points above (one CTA walks the whole time axis of 32 channels), and so do shapes for
- * which those are faster (few channels per row, or enough channel groups to fill the GPU but too
- * few to keep look-back chains short). */
+/* Channels-last with scratch: with scratch the time axis can be split across CTAs (two-pass
+ * chunked streaming, or decoupled look-back), so the whole GPU is busy even when N*C is small.
+ * `workspace` of ssb_scan_cl_workspace_bytes(N,T,C) bytes, 256-byte aligned, contents irrelevant;
+ * NULL / 0 behaves like the plain entry points above, and so do shapes that have enough channel
+ * blocks to fill the GPU without splitting T (see the default choice below). */
 size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C);
 /* Tuning knob for sweeps, per calling host thread.  0 = default choice: shapes with at least 96
  * (batch element, 32-channel block) pairs, T >= 128, C % 4 == 0 and 16-byte aligned tensors run
  * the streaming kernels (a CTA walks all of T for its channel block,
- * tiles staged by bulk tensor copies, no scratch -- from the plain entry points too); other shapes
- * the look-back kernels when scratch is given and they are faster, else the plain kernels.
+ * tiles staged by bulk tensor copies, no scratch -- from the plain entry points too); with fewer
+ * pairs, T >= 2048 and scratch the same kernels run over chunks of T in two passes (chunk maps,
+ * then the scan from each chunk's entering state); other shapes the look-back kernels when
+ * scratch is given and they are faster, else the plain kernels.
  * 0x200 forces the plain kernels in every channels-last fp32 entry point.  Any other id applies to
  * the next ssb_scan_cl_*_ex calls: 1..31 look-back kernels with that tile shape, 32..63 look-back
- * on TMA-staged tiles, 64.. streaming kernels with that tile shape.  Returns the previous id.
+ * on TMA-staged tiles, 64..71 streaming kernels with that tile shape, 96 the two-pass chunked form.  Returns the previous id.
  * Results do not depend on it beyond fp32 reassociation. */
 int ssb_scan_cl_set_tuning(int tuning);
 int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T,

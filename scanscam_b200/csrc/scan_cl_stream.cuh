@@ -18,6 +18,11 @@
 //     replays its run from its now-known starting value: ~5 instructions per element.
 //     The 8 (or 16) threads of a quarter warp read one contiguous 128-byte row: no bank conflicts.
 //   * Results go to a staging tile and leave through one bulk tensor store per tile.
+//   * With few (batch element, channel block) pairs the time axis is cut into `chunks` pieces that
+//     run as units of their own, in two passes: the REDUCE instantiation only composes each chunk's
+//     map (reads gate and value / gate and gout, 8 bytes per element, writes 2*CC floats per
+//     chunk), cl_chunk_carry_kernel folds those maps into the state entering every chunk, and the
+//     ordinary instantiation starts each chunk from that state (`carry_in`).
 //
 // Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
 #pragma once
@@ -30,15 +35,15 @@
 namespace ssb {
 namespace cls {
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
 struct Config {
     static constexpr int CG = CC / 4;            // float4 channel groups per tile row
     static constexpr int THREADS = CG * SEG;
     static constexpr int TS = TT / SEG;          // steps per thread
     static constexpr int SPW = 32 / CG;          // segments per warp
     static constexpr int NW = THREADS / 32;
-    static constexpr int N_IN = BWD ? 3 : 2;
-    static constexpr int N_OUT = BWD ? 2 : 1;
+    static constexpr int N_IN = (BWD && !REDUCE) ? 3 : 2;
+    static constexpr int N_OUT = REDUCE ? 0 : (BWD ? 2 : 1);
     static constexpr int TILE = TT * CC * 4;
     static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 128;
     static_assert(CC == 32 || CC == 64 || CC == 128, "a tile row is 8, 16 or 32 float4s: whole quarter warps");
@@ -67,12 +72,17 @@ __device__ __forceinline__ float4 shfl4(float4 v, int delta, bool up) {
     return r;
 }
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+// n_units = N * cblocks * chunks; unit u is chunk u % chunks of (batch element, channel block)
+// u / chunks and covers `pieces` tiles.  carry_in (may be NULL): [n_units][CC] states entering the
+// units.  REDUCE: maps [n_units][2][CC] receives each unit's composed map (A, B) and nothing else
+// is written; the value / h tensor is not read by the backward REDUCE.
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
 __global__ void __launch_bounds__(CC / 4 * SEG)
 cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                  const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
-                 const __grid_constant__ CUtensorMap map_out2, int64_t n_units, int cblocks, int pieces) {
-    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD>;
+                 const __grid_constant__ CUtensorMap map_out2, int64_t n_units, int cblocks, int pieces, int chunks,
+                 const float *__restrict__ carry_in, float *__restrict__ maps) {
+    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
     constexpr int CG = Cfg::CG, TS = Cfg::TS, SPW = Cfg::SPW, NW = Cfg::NW, N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT,
                   TILE = Cfg::TILE;
     extern __shared__ uint8_t smem_raw[];
@@ -92,10 +102,11 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
 
     auto coords = [&](int64_t i, int &c0, int &t0, int &n) {
         const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
-        const int piece = (int)(i % pieces);
-        n = (int)(unit / cblocks);
-        c0 = (int)(unit % cblocks) * CC;
-        t0 = (BWD ? pieces - 1 - piece : piece) * TT;
+        const int piece = (int)(i % pieces), chunk = (int)(unit % chunks);
+        const int64_t pair = unit / chunks;
+        n = (int)(pair / cblocks);
+        c0 = (int)(pair % cblocks) * CC;
+        t0 = (chunk * pieces + (BWD ? pieces - 1 - piece : piece)) * TT;
     };
     auto issue = [&](int64_t i) {  // thread 0: loads of this CTA's i-th tile into stage i % STAGES
         const int stage = (int)(i % STAGES);
@@ -104,8 +115,12 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         const uint32_t bar = bar0 + 8 * stage, dst = smem0 + stage * N_IN * TILE;
         tma::mbar_expect_tx(bar, N_IN * TILE);
         tma::load_box(dst, &map_gate, c0, t0, n, bar);
-        tma::load_box(dst + TILE, &map_in1, c0, BWD ? t0 - 1 : t0, n, bar);  // backward: h one step earlier
-        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, c0, t0, n, bar);
+        if (BWD && REDUCE) {
+            tma::load_box(dst + TILE, &map_in2, c0, t0, n, bar);
+        } else {
+            tma::load_box(dst + TILE, &map_in1, c0, BWD ? t0 - 1 : t0, n, bar);  // backward: h one step earlier
+            if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, c0, t0, n, bar);
+        }
     };
 
     if (tid == 0) {
@@ -120,11 +135,19 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     int out_slot = 0, buf = 0;
     float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);  // state entering the tile, for this thread's 4 channels
     const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 unit_A = one4;  // REDUCE: the gate product of the unit so far (carry holds its B)
 
     for (int64_t i = 0; i < n_items; i++) {
         const int stage = (int)(i % STAGES);
         const uint32_t in0 = smem0 + stage * N_IN * TILE + my_off;
-        if (i % pieces == 0) carry = zero4;  // a new unit starts
+        if (i % pieces == 0) {  // a new unit starts
+            carry = zero4;
+            unit_A = one4;
+            if (!REDUCE && carry_in != nullptr) {
+                const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
+                carry = *reinterpret_cast<const float4 *>(carry_in + unit * CC + cg * 4);
+            }
+        }
         if (!tma::mbar_wait_bounded(bar0 + 8 * stage, (phase_bits >> stage) & 1u)) timed_out = true;
         phase_bits ^= 1u << stage;
 
@@ -132,8 +155,12 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
 #pragma unroll
         for (int k = 0; k < TS; k++) {
             a[k] = tma::lds128(in0 + k * CC * 4);
-            x[k] = tma::lds128(in0 + TILE + k * CC * 4);
-            if (BWD) y[k] = tma::lds128(in0 + 2 * TILE + k * CC * 4);
+            if (BWD && REDUCE) {
+                y[k] = tma::lds128(in0 + TILE + k * CC * 4);
+            } else {
+                x[k] = tma::lds128(in0 + TILE + k * CC * 4);
+                if (BWD) y[k] = tma::lds128(in0 + 2 * TILE + k * CC * 4);
+            }
         }
         // This thread's run as one map, then the runs of the warp composed (forward: left to
         // right, lower segments first; backward: right to left).
@@ -157,7 +184,7 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             s_tot[buf][warp][cg][0] = m.A;
             s_tot[buf][warp][cg][1] = m.B;
         }
-        if (tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
+        if (!REDUCE && tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
         __syncthreads();
         // Every thread holds its tile data in registers: this very stage can be refilled now.
         if (tid == 0 && i + STAGES < n_items) issue(i + STAGES);
@@ -170,8 +197,18 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             const float4 tA = s_tot[buf][w][cg][0], tB = s_tot[buf][w][cg][1];
             if (w == warp) s = run;
             run = fma4(tA, run, tB);
+            if (REDUCE) unit_A = mul4(unit_A, tA);
         }
         carry = run;
+        if (REDUCE) {  // nothing to replay or store; the unit's map leaves after its last tile
+            if (i % pieces == pieces - 1 && seg == 0) {
+                const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
+                *reinterpret_cast<float4 *>(maps + (unit * 2) * CC + cg * 4) = unit_A;
+                *reinterpret_cast<float4 *>(maps + (unit * 2 + 1) * CC + cg * 4) = carry;
+            }
+            buf ^= 1;
+            continue;
+        }
         // ... and this thread's own run: the exclusive prefix inside the warp
         {
             float4 eA = shfl4(m.A, CG, !BWD), eB = shfl4(m.B, CG, !BWD);
@@ -209,6 +246,24 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     }
     if (tid == 0) tma::store_wait_read<0>();
     if (timed_out && lane == 0) report_device_wait(7);
+}
+
+// Folds the chunk maps of each (batch element, channel block) pair into the state entering every
+// chunk: forward left to right, backward right to left.  One thread per pair and channel.
+template <bool BWD>
+__global__ void cl_chunk_carry_kernel(const float *__restrict__ maps, float *__restrict__ carry, int64_t pairs, int chunks,
+                                      int cc) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pairs * cc) return;
+    const int64_t pair = idx / cc;
+    const int c = (int)(idx % cc);
+    float x = 0.f;
+    for (int q = 0; q < chunks; q++) {
+        const int k = BWD ? chunks - 1 - q : q;
+        const int64_t unit = pair * chunks + k;
+        carry[unit * cc + c] = x;
+        x = fmaf(maps[(unit * 2) * cc + c], x, maps[(unit * 2 + 1) * cc + c]);
+    }
 }
 
 }  // namespace cls

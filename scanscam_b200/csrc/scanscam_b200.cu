@@ -1092,20 +1092,29 @@ int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_
     X(4, 32, 64, 8, 2, 2, 32, 64, 16, 2, 1) X(5, 64, 64, 8, 2, 1, 64, 64, 4, 2, 1)           \
     X(6, 128, 32, 8, 3, 2, 128, 32, 8, 2, 1) X(7, 32, 128, 32, 2, 1, 32, 128, 32, 2, 1)
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD>
+// `chunk_steps` = 0: a unit is all of T.  Otherwise (a multiple of TT) T is cut into chunks of that
+// many steps, each a unit of its own that starts from carry_in[unit][CC] (or, REDUCE, only writes
+// its map to maps[unit][2][CC]).  Tensors a REDUCE launch does not touch may be NULL.
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
 int launch_cls(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
-               int64_t C, cudaStream_t st) {
-    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD>;
-    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD>;
-    const int64_t cblocks = (C + CC - 1) / CC, pieces = (T + TT - 1) / TT;
-    if (pieces > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
+               int64_t C, cudaStream_t st, int64_t chunk_steps = 0, const float *carry_in = nullptr, float *maps = nullptr) {
+    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
+    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
+    const int64_t cblocks = (C + CC - 1) / CC, tiles = (T + TT - 1) / TT;
+    if (tiles > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
+    if (chunk_steps % TT != 0) return fail(SSB_ERR_BAD_ARG, "channels-last streaming kernels: chunk of %lld steps, tiles of %d", (long long)chunk_steps, TT);
+    const int64_t pieces = chunk_steps > 0 ? chunk_steps / TT : tiles;
+    const int64_t chunks = (tiles + pieces - 1) / pieces;
+    // tensors this launch does not touch still need a valid descriptor: describe the gate instead
+    const float *p_in1 = (BWD && REDUCE) ? gate : in1, *p_in2 = BWD ? in2 : p_in1;
+    float *p_out1 = REDUCE ? const_cast<float *>(gate) : out1, *p_out2 = (BWD && !REDUCE) ? out2 : p_out1;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_cl_map(&mg, gate, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&m1, in1, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&m2, BWD ? in2 : in1, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&mo1, out1, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&mo2, BWD ? out2 : out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m1, p_in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m2, p_in2, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo1, p_out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo2, p_out2, N, T, C, CC, TT)) != SSB_OK) return rc;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(cl_stream_kernel)");
     static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
@@ -1117,10 +1126,43 @@ int launch_cls(const float *gate, const float *in1, const float *in2, float *out
         }
         cached_occ.store(occ, std::memory_order_relaxed);
     }
-    const int64_t units = N * cblocks, cap = (int64_t)sm_count() * occ;
+    const int64_t units = N * cblocks * chunks, cap = (int64_t)sm_count() * occ;
     const int grid = (int)(units < cap ? units : cap);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces, (int)chunks,
+                                                      carry_in, maps);
     return check_launch("cl_stream_kernel");
+}
+
+// Two-pass form for shapes with few (batch element, channel block) pairs: chunk maps, carries, scan.
+constexpr int kClsChunkTile = 256;   // chunk lengths are multiples of this (every tile height divides it)
+constexpr int kClsChunkUnits = 384;  // aim for about this many units (2.6 per SM)
+
+int64_t cls_chunk_steps(int64_t N, int64_t T, int64_t C) {
+    const int64_t pairs = N * ((C + 31) / 32), tiles = (T + kClsChunkTile - 1) / kClsChunkTile;
+    int64_t chunks = (kClsChunkUnits + pairs - 1) / pairs;
+    if (chunks > tiles) chunks = tiles;
+    return ((tiles + chunks - 1) / chunks) * kClsChunkTile;
+}
+size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C) {
+    const int64_t steps = cls_chunk_steps(N, T, C), chunks = (T + steps - 1) / steps;
+    return (size_t)(N * ((C + 31) / 32) * chunks) * 3 * 32 * sizeof(float);
+}
+
+template <bool BWD>
+int launch_cls_chunked(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+                       int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int64_t steps = cls_chunk_steps(N, T, C), chunks = (T + steps - 1) / steps, pairs = N * ((C + 31) / 32);
+    if (workspace == nullptr || workspace_bytes < cls_chunk_workspace_bytes(N, T, C))
+        return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
+                    cls_chunk_workspace_bytes(N, T, C), workspace_bytes);
+    float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * 32;
+    int rc = launch_cls<32, 256, 16, 2, 1, BWD, true>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
+    if (rc != SSB_OK) return rc;
+    const int64_t threads = pairs * 32;
+    ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, 32);
+    if ((rc = check_launch("cl_chunk_carry_kernel")) != SSB_OK) return rc;
+    if (!BWD) return launch_cls<32, 256, 16, 2, 2, false>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
+    return launch_cls<32, 128, 16, 2, 1, true>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
@@ -1205,6 +1247,7 @@ int cl_bwd(const real *gate, const real *h, const real *gout, real *ggate, real 
 }  // namespace
 
 namespace {
+constexpr int kClChunkedId = 96;      // ssb_scan_cl_set_tuning: the two-pass chunked streaming kernels
 constexpr int kClForcePlain = 0x200;  // ssb_scan_cl_set_tuning: the plain kernels, whatever the shape
 
 // Channel-block width of the streaming kernels for this shape, or 0 when they do not apply: they
@@ -1217,6 +1260,13 @@ int cl_stream_block(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
     if (T >= 1024 && (C % 64 == 0 || C >= 512) && N * ((C + 63) / 64) >= 128) return 64;
     if (N * ((C + 31) / 32) >= 96) return 32;
     return 0;
+}
+
+// Too few pairs for the above but long rows and scratch at hand: the same kernels over chunks of T
+// in two passes (measured 1.3-4x the look-back kernels from 2048 steps up).
+bool cl_chunked_applies(int64_t N, int64_t T, int64_t C, bool all_aligned16, const void *workspace, size_t workspace_bytes) {
+    return all_aligned16 && cl3_eligible(N, T, C) && T >= 2048 && encode_fn() != nullptr && workspace != nullptr &&
+           aligned_to(workspace, 256) && workspace_bytes >= cls_chunk_workspace_bytes(N, T, C);
 }
 
 int cl_stream_fwd(int block, const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, cudaStream_t st) {
@@ -1270,6 +1320,10 @@ size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C) {
         const size_t b = ssb::cl2::workspace_bytes(tiles, vec);
         need = b > need ? b : need;
     }
+    if (C % 4 == 0) {  // chunked streaming: maps and carries of every chunk
+        const size_t b = cls_chunk_workspace_bytes(N, T, C);
+        need = b > need ? b : need;
+    }
     for (int cc : {32, 64, 128}) {  // TMA-staged tiles: at least kCl3MinTileElems elements each
         const int tt = kCl3MinTileElems / cc;
         const int64_t tiles = N * ((C + cc - 1) / cc) * ((T + tt - 1) / tt);
@@ -1289,6 +1343,9 @@ int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, in
     if (t_cl_tuning == 0 && gate && value && out) {
         const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16));
         if (block) return cl_stream_fwd(block, gate, value, out, N, T, C, static_cast<cudaStream_t>(stream));
+        if (cl_chunked_applies(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16), workspace, workspace_bytes))
+            return launch_cls_chunked<false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes,
+                                             static_cast<cudaStream_t>(stream));
     }
     if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
         (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
@@ -1299,6 +1356,11 @@ int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, in
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16) &&
                      !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) == kClChunkedId) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        return launch_cls_chunked<false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
+    }
     if ((t_cl_tuning & 0xff) >= 64) {
         if (!vec || !cl3_eligible(N, T, C))
             return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
@@ -1339,6 +1401,10 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
         const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                                                        aligned_to(ggate, 16) && aligned_to(gvalue, 16));
         if (block) return cl_stream_bwd(block, gate, h, gout, ggate, gvalue, N, T, C, static_cast<cudaStream_t>(stream));
+        if (cl_chunked_applies(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) && aligned_to(ggate, 16) &&
+                                            aligned_to(gvalue, 16), workspace, workspace_bytes))
+            return launch_cls_chunked<true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes,
+                                            static_cast<cudaStream_t>(stream));
     }
     if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
         (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
@@ -1349,6 +1415,11 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
     const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                      aligned_to(ggate, 16) && aligned_to(gvalue, 16) && !(t_cl_tuning & 0x100);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((t_cl_tuning & 0xff) == kClChunkedId) {
+        if (!vec || !cl3_eligible(N, T, C))
+            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
+        return launch_cls_chunked<true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
+    }
     if ((t_cl_tuning & 0xff) >= 64) {
         if (!vec || !cl3_eligible(N, T, C))
             return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");

@@ -104,6 +104,7 @@ def time_channels_last(lib, N, T, C, iters):
     rows = []
     modes = [("plain", 0x200, False), ("lookback", 1, True), ("auto", 0, True)]
     if C % 4 == 0:  # streaming kernels (a CTA walks all of T through a TMA ring), every tile shape
+        modes += [("chunked", 96, True)]  # the same kernels over chunks of T, two passes
         modes += [(f"stream{k}", 64 + k, True) for k in range(8)]
     for label, tuning, use_ws in modes:
         lib.ssb_scan_cl_set_tuning(tuning)

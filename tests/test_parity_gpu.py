@@ -94,6 +94,7 @@ def test_channels_last_with_scratch(shape, gates):
         modes.append("plain")
     if shape[2] % 4 == 0:
         modes += [32, 33, 34, 35, 36, 37]  # TMA-staged tiles, every tile shape of the table
+        modes += [96]  # streaming kernels over chunks of T: chunk maps, carries, scan
         modes += list(range(64, 72))  # streaming kernels (a CTA walks all of T), every tile shape
     for scratch in modes:
         h = _gpu.cl_fwd(da, db, scratch=scratch)
