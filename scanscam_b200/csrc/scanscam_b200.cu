@@ -1063,8 +1063,10 @@ int launch_cl2(const float *gate, const float *in1, const float *in2, float *out
     X(3, 64, 128, 2, 1, 64, 64, 2, 2) X(4, 32, 64, 4, 2, 32, 64, 3, 2) X(5, 128, 64, 2, 1, 128, 32, 2, 2)
 constexpr int kCl3MinTileElems = 32 * 64;  // smallest CC*TT of the table (bounds the workspace)
 
+// What cuTensorMapEncodeTiled and the kernels' 32-bit box coordinates accept for a {C, T, N} view:
+// pitches that are multiples of 16 bytes and below 2^40, extents below 2^31 with room for one tile.
 bool cl3_eligible(int64_t N, int64_t T, int64_t C) {
-    return C % 4 == 0 && N <= 0x7fffffffLL && T <= 0x7ffffff0LL && C <= 0x7fffffffLL;
+    return C % 4 == 0 && N <= 0x7fffffffLL && T <= 0x7fffff00LL && C <= 0x7fffffffLL && T <= ((1LL << 40) - 1) / 4 / C;
 }
 
 int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_t C, int cc, int tt) {
