@@ -233,6 +233,23 @@ int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, fl
 int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate,
                         double *gvalue, int64_t N, int64_t T, int64_t C, void *stream);
 
+/* Channels-last on 16-bit tensors (bf16 / fp16 storage, fp32 arithmetic; no counterpart in the
+ * reference).  The streaming kernels with 64-channel blocks; C % 8 == 0 and 16-byte aligned
+ * tensors, SSB_ERR_UNSUPPORTED otherwise.  `workspace` (ssb_scan_cl_h16_workspace_bytes, 256-byte
+ * aligned, may be NULL) lets shapes with fewer than 96 (batch element, 64-channel block) pairs and
+ * T >= 2048 run in the two-pass chunked form; without it one CTA walks all of T per pair. */
+size_t ssb_scan_cl_h16_workspace_bytes(int64_t N, int64_t T, int64_t C);
+int ssb_scan_cl_fwd_bf16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C,
+                         void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_bwd_bf16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue,
+                         int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes,
+                         void *stream);
+int ssb_scan_cl_fwd_f16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C,
+                        void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue,
+                        int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes,
+                        void *stream);
+
 /* Channels-last with scratch: with scratch the time axis can be split across CTAs (two-pass
  * chunked streaming, or decoupled look-back), so the whole GPU is busy even when N*C is small.
  * `workspace` of ssb_scan_cl_workspace_bytes(N,T,C) bytes, 256-byte aligned, contents irrelevant;

@@ -49,6 +49,11 @@ SIGNATURES = {
     "ssb_scan_cl_bwd_f64": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "ssb_scan_recommend": (_int, [_i64, _i64, _int, _int, _int]),
     "ssb_scan_cl_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "ssb_scan_cl_h16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "ssb_scan_cl_fwd_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_bwd_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_set_tuning": (_int, [_int]),
     "ssb_scan_cl_fwd_f32_ex": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_bwd_f32_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),

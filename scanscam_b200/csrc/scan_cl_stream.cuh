@@ -24,6 +24,11 @@
 //     chunk), cl_chunk_carry_kernel folds those maps into the state entering every chunk, and the
 //     ordinary instantiation starts each chunk from that state (`carry_in`).
 //
+//   * Storage type IO: float, or bf16 / fp16 with fp32 arithmetic.  A thread still owns 4 adjacent
+//     channels; with 16-bit storage they are 8 bytes (one 64-bit shared-memory access), a tile row
+//     of CC channels is CC*2 bytes, and the 16 threads of a half warp cover a 128-byte row.
+//     Chunk maps and carries stay fp32.
+//
 // Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
 #pragma once
 
@@ -35,8 +40,9 @@
 namespace ssb {
 namespace cls {
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
 struct Config {
+    static constexpr int ROW = CC * (int)sizeof(IO);  // bytes of one tile row
     static constexpr int CG = CC / 4;            // float4 channel groups per tile row
     static constexpr int THREADS = CG * SEG;
     static constexpr int TS = TT / SEG;          // steps per thread
@@ -44,9 +50,10 @@ struct Config {
     static constexpr int NW = THREADS / 32;
     static constexpr int N_IN = (BWD && !REDUCE) ? 3 : 2;
     static constexpr int N_OUT = REDUCE ? 0 : (BWD ? 2 : 1);
-    static constexpr int TILE = TT * CC * 4;
+    static constexpr int TILE = TT * ROW;
     static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 128;
-    static_assert(CC == 32 || CC == 64 || CC == 128, "a tile row is 8, 16 or 32 float4s: whole quarter warps");
+    static_assert(CC == 32 || CC == 64 || CC == 128, "a tile row is 8, 16 or 32 groups of 4 channels");
+    static_assert(ROW % 128 == 0, "a tile row is whole 128-byte lines (conflict-free shared-memory access)");
     static_assert(TT % SEG == 0 && THREADS % 32 == 0 && THREADS <= 1024 && TT <= 256, "tile shape");
     static_assert(STAGES >= 1 && OUTBUF >= 1, "ring sizes");
 };
@@ -76,15 +83,39 @@ __device__ __forceinline__ float4 shfl4(float4 v, int delta, bool up) {
 // u / chunks and covers `pieces` tiles.  carry_in (may be NULL): [n_units][CC] states entering the
 // units.  REDUCE: maps [n_units][2][CC] receives each unit's composed map (A, B) and nothing else
 // is written; the value / h tensor is not read by the backward REDUCE.
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
+// Four adjacent channels of one step, shared memory <-> fp32 registers.
+template <typename IO>
+__device__ __forceinline__ float4 lds_vec4(uint32_t addr) {
+    if constexpr (sizeof(IO) == 4) {
+        return tma::lds128(addr);
+    } else {
+        uint32_t lo, hi;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr));
+        float4 r;
+        unpack2<IO>(lo, r.x, r.y);
+        unpack2<IO>(hi, r.z, r.w);
+        return r;
+    }
+}
+template <typename IO>
+__device__ __forceinline__ void sts_vec4(uint32_t addr, float4 v) {
+    if constexpr (sizeof(IO) == 4) {
+        tma::sts128(addr, v);
+    } else {
+        const uint32_t lo = pack2<IO>(v.x, v.y), hi = pack2<IO>(v.z, v.w);
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
+    }
+}
+
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
 __global__ void __launch_bounds__(CC / 4 * SEG)
 cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                  const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
                  const __grid_constant__ CUtensorMap map_out2, int64_t n_units, int cblocks, int pieces, int chunks,
                  const float *__restrict__ carry_in, float *__restrict__ maps) {
-    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
+    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
     constexpr int CG = Cfg::CG, TS = Cfg::TS, SPW = Cfg::SPW, NW = Cfg::NW, N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT,
-                  TILE = Cfg::TILE;
+                  TILE = Cfg::TILE, ROW = Cfg::ROW;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES];
     __shared__ float4 s_tot[2][NW][CG][2];  // per warp and channel group: the warp's composed map (A, B)
@@ -98,7 +129,7 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     const int64_t my_units = (int64_t)blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const int64_t n_items = my_units * pieces;
     // byte offset of this thread's float4 at its first step inside a tile
-    const uint32_t my_off = (uint32_t)((seg * TS * CC + cg * 4) * 4);
+    const uint32_t my_off = (uint32_t)(seg * TS * ROW + cg * 4 * (int)sizeof(IO));
 
     auto coords = [&](int64_t i, int &c0, int &t0, int &n) {
         const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
@@ -154,12 +185,12 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         float4 a[TS], x[TS], y[TS];  // x: value | h one step earlier ; y: unused | gout
 #pragma unroll
         for (int k = 0; k < TS; k++) {
-            a[k] = tma::lds128(in0 + k * CC * 4);
+            a[k] = lds_vec4<IO>(in0 + k * ROW);
             if (BWD && REDUCE) {
-                y[k] = tma::lds128(in0 + TILE + k * CC * 4);
+                y[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
             } else {
-                x[k] = tma::lds128(in0 + TILE + k * CC * 4);
-                if (BWD) y[k] = tma::lds128(in0 + 2 * TILE + k * CC * 4);
+                x[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
+                if (BWD) y[k] = lds_vec4<IO>(in0 + 2 * TILE + k * ROW);
             }
         }
         // This thread's run as one map, then the runs of the warp composed (forward: left to
@@ -221,15 +252,15 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
 #pragma unroll
             for (int k = 0; k < TS; k++) {
                 s = fma4(a[k], s, x[k]);
-                tma::sts128(ob + k * CC * 4, s);
+                sts_vec4<IO>(ob + k * ROW, s);
             }
         } else {
 #pragma unroll
             for (int k = TS - 1; k >= 0; k--) {
                 const float4 gb = add4(y[k], s);
                 s = mul4(a[k], gb);
-                tma::sts128(ob + k * CC * 4, mul4(gb, x[k]));   // grad of gate = gb_t * h_{t-1}
-                tma::sts128(ob + TILE + k * CC * 4, gb);        // grad of value
+                sts_vec4<IO>(ob + k * ROW, mul4(gb, x[k]));   // grad of gate = gb_t * h_{t-1}
+                sts_vec4<IO>(ob + TILE + k * ROW, gb);        // grad of value
             }
         }
         tma::fence_async_smem();

@@ -1069,14 +1069,15 @@ bool cl3_eligible(int64_t N, int64_t T, int64_t C) {
     return C % 4 == 0 && N <= 0x7fffffffLL && T <= 0x7fffff00LL && C <= 0x7fffffffLL && T <= ((1LL << 40) - 1) / 4 / C;
 }
 
-int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_t C, int cc, int tt) {
+template <typename IO>
+int make_cl_map(CUtensorMap *map, const IO *ptr, int64_t N, int64_t T, int64_t C, int cc, int tt) {
     PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
     if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)T, (cuuint64_t)N};
-    cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)T * (cuuint64_t)C * 4};
+    cuuint64_t strides[2] = {(cuuint64_t)C * sizeof(IO), (cuuint64_t)T * (cuuint64_t)C * sizeof(IO)};
     cuuint32_t box[3] = {(cuuint32_t)cc, (cuuint32_t)tt, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = encode_tiled(enc, map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+    CUresult r = encode_tiled(enc, map, tensor_map_type<IO>(), 3, const_cast<IO *>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled([N,T,C]) failed with CUresult %d", (int)r);
@@ -1097,19 +1098,20 @@ int make_cl_map(CUtensorMap *map, const float *ptr, int64_t N, int64_t T, int64_
 // `chunk_steps` = 0: a unit is all of T.  Otherwise (a multiple of TT) T is cut into chunks of that
 // many steps, each a unit of its own that starts from carry_in[unit][CC] (or, REDUCE, only writes
 // its map to maps[unit][2][CC]).  Tensors a REDUCE launch does not touch may be NULL.
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false>
-int launch_cls(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
+int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typename as_given<IO>::type *in2,
+               typename as_given<IO>::type *out1, typename as_given<IO>::type *out2, int64_t N, int64_t T,
                int64_t C, cudaStream_t st, int64_t chunk_steps = 0, const float *carry_in = nullptr, float *maps = nullptr) {
-    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
-    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE>;
+    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
+    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
     const int64_t cblocks = (C + CC - 1) / CC, tiles = (T + TT - 1) / TT;
     if (tiles > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
     if (chunk_steps % TT != 0) return fail(SSB_ERR_BAD_ARG, "channels-last streaming kernels: chunk of %lld steps, tiles of %d", (long long)chunk_steps, TT);
     const int64_t pieces = chunk_steps > 0 ? chunk_steps / TT : tiles;
     const int64_t chunks = (tiles + pieces - 1) / pieces;
     // tensors this launch does not touch still need a valid descriptor: describe the gate instead
-    const float *p_in1 = (BWD && REDUCE) ? gate : in1, *p_in2 = BWD ? in2 : p_in1;
-    float *p_out1 = REDUCE ? const_cast<float *>(gate) : out1, *p_out2 = (BWD && !REDUCE) ? out2 : p_out1;
+    const IO *p_in1 = (BWD && REDUCE) ? gate : in1, *p_in2 = BWD ? in2 : p_in1;
+    IO *p_out1 = REDUCE ? const_cast<IO *>(gate) : out1, *p_out2 = (BWD && !REDUCE) ? out2 : p_out1;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_cl_map(&mg, gate, N, T, C, CC, TT)) != SSB_OK) return rc;
@@ -1139,32 +1141,35 @@ int launch_cls(const float *gate, const float *in1, const float *in2, float *out
 constexpr int kClsChunkTile = 256;   // chunk lengths are multiples of this (every tile height divides it)
 constexpr int kClsChunkUnits = 384;  // aim for about this many units (2.6 per SM)
 
-int64_t cls_chunk_steps(int64_t N, int64_t T, int64_t C) {
-    const int64_t pairs = N * ((C + 31) / 32), tiles = (T + kClsChunkTile - 1) / kClsChunkTile;
+// `cc`: channels per block (32 for fp32, 64 for 16-bit storage)
+int64_t cls_chunk_steps(int64_t N, int64_t T, int64_t C, int cc = 32) {
+    const int64_t pairs = N * ((C + cc - 1) / cc), tiles = (T + kClsChunkTile - 1) / kClsChunkTile;
     int64_t chunks = (kClsChunkUnits + pairs - 1) / pairs;
     if (chunks > tiles) chunks = tiles;
     return ((tiles + chunks - 1) / chunks) * kClsChunkTile;
 }
-size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C) {
-    const int64_t steps = cls_chunk_steps(N, T, C), chunks = (T + steps - 1) / steps;
-    return (size_t)(N * ((C + 31) / 32) * chunks) * 3 * 32 * sizeof(float);
+size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C, int cc = 32) {
+    const int64_t steps = cls_chunk_steps(N, T, C, cc), chunks = (T + steps - 1) / steps;
+    return (size_t)(N * ((C + cc - 1) / cc) * chunks) * 3 * cc * sizeof(float);
 }
 
-template <bool BWD>
-int launch_cls_chunked(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+template <bool BWD, typename IO = float>
+int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, const typename as_given<IO>::type *in2,
+                       typename as_given<IO>::type *out1, typename as_given<IO>::type *out2, int64_t N, int64_t T,
                        int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
-    const int64_t steps = cls_chunk_steps(N, T, C), chunks = (T + steps - 1) / steps, pairs = N * ((C + 31) / 32);
-    if (workspace == nullptr || workspace_bytes < cls_chunk_workspace_bytes(N, T, C))
+    constexpr int CC = 128 / (int)sizeof(IO);  // 128-byte tile rows
+    const int64_t steps = cls_chunk_steps(N, T, C, CC), chunks = (T + steps - 1) / steps, pairs = N * ((C + CC - 1) / CC);
+    if (workspace == nullptr || workspace_bytes < cls_chunk_workspace_bytes(N, T, C, CC))
         return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
-                    cls_chunk_workspace_bytes(N, T, C), workspace_bytes);
-    float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * 32;
-    int rc = launch_cls<32, 256, 16, 2, 1, BWD, true>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
+                    cls_chunk_workspace_bytes(N, T, C, CC), workspace_bytes);
+    float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * CC;
+    int rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
     if (rc != SSB_OK) return rc;
-    const int64_t threads = pairs * 32;
-    ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, 32);
+    const int64_t threads = pairs * CC;
+    ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
     if ((rc = check_launch("cl_chunk_carry_kernel")) != SSB_OK) return rc;
-    if (!BWD) return launch_cls<32, 256, 16, 2, 2, false>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
-    return launch_cls<32, 128, 16, 2, 1, true>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
+    return launch_cls<CC, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
@@ -1450,6 +1455,64 @@ int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout,
         default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last tuning id %d", t_cl_tuning);
     }
 }
+}  // extern "C"
+
+// ---- channels-last, 16-bit storage (bf16 / fp16 tensors, fp32 arithmetic) ---------------------
+namespace {
+bool cl_h16_eligible(int64_t N, int64_t T, int64_t C) {
+    return C % 8 == 0 && N <= 0x7fffffffLL && T <= 0x7fffff00LL && C <= 0x7fffffffLL && T <= ((1LL << 40) - 1) / 2 / C;
+}
+
+template <typename IO, bool BWD>
+int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, void *out2_, int64_t N, int64_t T, int64_t C,
+           void *workspace, size_t workspace_bytes, void *stream, const char *who) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate_ || !in1_ || (BWD && !in2_) || !out1_ || (BWD && !out2_)) return fail(SSB_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+    const bool al16 = aligned_to(gate_, 16) && aligned_to(in1_, 16) && aligned_to(in2_, 16) && aligned_to(out1_, 16) &&
+                      aligned_to(out2_, 16);
+    if (!al16 || !cl_h16_eligible(N, T, C) || encode_fn() == nullptr)
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs C %% 8 == 0 and 16-byte aligned tensors (C=%lld)", who, (long long)C);
+    const IO *gate = static_cast<const IO *>(gate_), *in1 = static_cast<const IO *>(in1_), *in2 = static_cast<const IO *>(in2_);
+    IO *out1 = static_cast<IO *>(out1_), *out2 = static_cast<IO *>(out2_);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t pairs = N * ((C + 63) / 64);
+    if (pairs < 96 && T >= 2048 && workspace != nullptr && aligned_to(workspace, 256) &&
+        workspace_bytes >= cls_chunk_workspace_bytes(N, T, C, 64))
+        return launch_cls_chunked<BWD, IO>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+    if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+    return launch_cls<64, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st);
+}
+}  // namespace
+
+extern "C" {
+
+size_t ssb_scan_cl_h16_workspace_bytes(int64_t N, int64_t T, int64_t C) {
+    if (N <= 0 || T <= 0 || C <= 0) return 0;
+    return cls_chunk_workspace_bytes(N, T, C, 64);
+}
+int ssb_scan_cl_fwd_bf16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+    return cl_h16<__nv_bfloat16, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, stream,
+                                        "ssb_scan_cl_fwd_bf16");
+}
+int ssb_scan_cl_bwd_bf16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t N, int64_t T,
+                         int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__nv_bfloat16, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, stream,
+                                       "ssb_scan_cl_bwd_bf16");
+}
+int ssb_scan_cl_fwd_f16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C, void *workspace,
+                        size_t workspace_bytes, void *stream) {
+    return cl_h16<__half, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, stream,
+                                 "ssb_scan_cl_fwd_f16");
+}
+int ssb_scan_cl_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t N, int64_t T,
+                        int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__half, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, stream, "ssb_scan_cl_bwd_f16");
+}
+
 int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, int64_t N, int64_t T, int64_t C, void *stream) {
     return cl_fwd<double>(gate, value, out, N, T, C, stream);
 }

@@ -253,11 +253,19 @@ void transposed_linear_scan(torch::Tensor gate, torch::Tensor value, torch::Tens
     TORCH_CHECK(gate.dim() == 3, "gate must be 3-D [N, T, C]");
     check_same(gate, value, "value");
     check_same(gate, output, "output");
-    check_dtype(gate, "transposed_linear_scan");
+    // 16-bit storage is an addition, for channel counts the bulk-tensor kernels can describe
+    check_dtype(gate, "transposed_linear_scan", gate.size(2) % 8 == 0);
     check_cpb(channelsPerBlock);
     c10::cuda::CUDAGuard guard(gate.device());
     int rc;
-    if (gate.scalar_type() == torch::kFloat32) {
+    if (is_16bit(gate)) {
+        const size_t ws_bytes = ssb_scan_cl_h16_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        auto fn = gate.scalar_type() == torch::kBFloat16 ? ssb_scan_cl_fwd_bf16 : ssb_scan_cl_fwd_f16;
+        rc = fn(gate.data_ptr(), value.data_ptr(), output.data_ptr(), gate.size(0), gate.size(1), gate.size(2),
+                ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
+    } else if (gate.scalar_type() == torch::kFloat32) {
         const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
         torch::Tensor ws;
         if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
@@ -279,11 +287,18 @@ void transposed_linear_scan_backward(torch::Tensor gate, torch::Tensor output, t
     check_same(gate, outGrad, "outGrad");
     check_same(gate, gateGradOut, "gateGradOut");
     check_same(gate, valueGradOut, "valueGradOut");
-    check_dtype(gate, "transposed_linear_scan_backward");
+    check_dtype(gate, "transposed_linear_scan_backward", gate.size(2) % 8 == 0);
     check_cpb(channelsPerBlock);
     c10::cuda::CUDAGuard guard(gate.device());
     int rc;
-    if (gate.scalar_type() == torch::kFloat32) {
+    if (is_16bit(gate)) {
+        const size_t ws_bytes = ssb_scan_cl_h16_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        auto fn = gate.scalar_type() == torch::kBFloat16 ? ssb_scan_cl_bwd_bf16 : ssb_scan_cl_bwd_f16;
+        rc = fn(gate.data_ptr(), output.data_ptr(), outGrad.data_ptr(), gateGradOut.data_ptr(), valueGradOut.data_ptr(),
+                gate.size(0), gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
+    } else if (gate.scalar_type() == torch::kFloat32) {
         const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
         torch::Tensor ws;
         if (ws_bytes > 0) ws = scratch(ws_bytes, gate);

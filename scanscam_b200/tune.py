@@ -4,6 +4,7 @@
     python -m scanscam_b200.tune cl:8x4096x512,cl:4x65536x256         (channels-last [N,T,C])
     python -m scanscam_b200.tune fused:16384x4096                     (gate logits in; recompute backward)
     python -m scanscam_b200.tune h16:16384x4096                       (bf16 / fp16 storage beside fp32)
+    python -m scanscam_b200.tune clh16:64x4096x512                    (the same for channels-last)
 
 For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
 ``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
@@ -117,6 +118,43 @@ def time_channels_last(lib, N, T, C, iters):
     return rows
 
 
+def time_channels_last_16bit(lib, N, T, C, iters):
+    """Channels-last entry points on fp32, bf16 and fp16 tensors of one shape (library's own choice)."""
+    out = []
+    st = torch.cuda.current_stream().cuda_stream
+    n = N * T * C
+    for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16), ("f16", torch.float16)):
+        a = (torch.rand(N, T, C, device="cuda") * 0.2 + 0.8).to(dtype)
+        b, g = torch.randn_like(a), torch.randn_like(a)
+        h, ga, gb = (torch.empty_like(a) for _ in range(3))
+        need = (lib.ssb_scan_cl_workspace_bytes if name == "f32" else lib.ssb_scan_cl_h16_workspace_bytes)(N, T, C)
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+        fwd = lib.ssb_scan_cl_fwd_f32_ex if name == "f32" else getattr(lib, f"ssb_scan_cl_fwd_{name}")
+        bwd = lib.ssb_scan_cl_bwd_f32_ex if name == "f32" else getattr(lib, f"ssb_scan_cl_bwd_{name}")
+        size = a.element_size()
+
+        def run(fn):
+            for _ in range(3):
+                _native.check(fn())
+            torch.cuda.synchronize()
+            best = float("inf")
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1) / iters)
+            return best
+
+        tf = run(lambda: fwd(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, ws.data_ptr(), need, st))
+        tb = run(lambda: bwd(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C, ws.data_ptr(), need, st))
+        out.append((name, 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+        del a, b, g, h, ga, gb
+    return out
+
+
 def time_fused_sigmoid(lib, rows, T, iters):
     """Kernel times of the plain scan, the fused-sigmoid scan and the elementwise passes it replaces."""
     z = torch.randn(rows, T, device="cuda")
@@ -212,6 +250,14 @@ def main():
             for label, fg, tf, bg, tb, ge in time_16bit(lib, rows, T, args.iters):
                 results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
                 print(f"{label:18s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
+            continue
+        if name.startswith("clh16:"):  # channels-last, storage types: clh16:NxTxC
+            N, T, C = (int(v) for v in name[6:].lower().split("x"))
+            print(f"# channels-last storage types, [N,T,C] = {N}x{T}x{C} ({N * T * C / 1e6:.0f} M elements per tensor)")
+            print(f"{'storage':8s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
+            for label, fg, tf, bg, tb, ge in time_channels_last_16bit(lib, N, T, C, args.iters):
+                results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
+                print(f"{label:8s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
             continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))

@@ -105,8 +105,8 @@ def test_error_behaviour_matches_the_reference():
         scanscam_b200.scan(torch.rand(8, device="cuda"), torch.rand(8, device="cuda"))
     with pytest.raises(NotImplementedError, match="not implemented for 'Int'"):
         scanscam_b200.scan(x.int(), x.int())
-    # 16-bit floating types are an addition in the rows layout only; channels-last raises as the
-    # reference does for every half-precision input
+    # 16-bit floating types are an addition (rows layout: any shape; channels-last: C % 8 == 0);
+    # other channel counts raise as the reference does for every half-precision input
     xt = torch.rand(2, 8, 4, device="cuda").half().mT
     with pytest.raises(NotImplementedError, match="not implemented for 'Half'"):
         scanscam_b200.scan(xt, xt)
@@ -298,3 +298,22 @@ def test_fused_operators_with_16bit_tensors(dtype, shape):
     h2 = scanscam_b200.scan_recompute(a2, b2)
     h2.backward(g)
     assert close(h2, ref2.detach()) and close(a2.grad, af.grad) and close(b2.grad, bf2.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100)])
+def test_scan_channels_last_with_16bit_tensors(dtype, shape):
+    """scan() on channels-last bf16 / fp16 inputs ([N, C, T] views of dense [N, T, C]) against the
+    fp32 oracle on the rounded inputs."""
+    N, C, T = shape
+    a, b, g = (x.to(dtype) for x in make_inputs("sigmoid2", (N, T, C), seed=121))
+    h_ref = oracle.scan_forward_channels_last(a.float().numpy(), b.float().numpy())
+    da, db = a.cuda().mT.requires_grad_(True), b.cuda().mT.requires_grad_(True)
+    assert op.is_transpose_contig(da)
+    h = scanscam_b200.scan(da, db)
+    assert h.dtype == dtype and op.is_transpose_contig(h)
+    h.backward(g.cuda().mT)
+    ga_ref, gb_ref = oracle.scan_backward_channels_last(a.float().numpy(), h.detach().mT.float().cpu().numpy(), g.float().numpy())
+    half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    for x, ref in ((h.mT, h_ref), (da.grad.mT, ga_ref), (db.grad.mT, gb_ref)):
+        assert _gpu.max_norm_err(x.detach().float().contiguous(), ref) < 1.01 * half_ulp

@@ -615,3 +615,36 @@ def test_16bit_fused_entry_points(name, shape):
     # a row length the sweep does not take
     rc = getattr(lib, f"ssb_scan_sigmoid_fwd_{name}")(dz.data_ptr(), db.data_ptr(), h.data_ptr(), rows * T // 96, 96, None, st)
     assert rc == _native.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("name", ["bf16", "f16"])
+@pytest.mark.parametrize("shape,scratch", [((8, 700, 512), False), ((2, 300, 64), False), ((1, 9000, 64), True),
+                                           ((2, 5000, 200), True), ((3, 100, 8), False), ((1, 4096, 1032), True)])
+def test_channels_last_16bit_storage(name, shape, scratch):
+    """ssb_scan_cl_{fwd,bwd}_{bf16,f16}: [N,T,C] tensors in 16-bit storage; direct streaming and,
+    with scratch on few-block shapes, the two-pass chunked form.  Every output within half a unit
+    in the last place of the fp32 oracle's result on the same rounded inputs."""
+    dtype, half_ulp = H16[name]
+    N, T, C = shape
+    a, b, g = (x.to(dtype) for x in make_inputs("sigmoid2", shape, seed=131))
+    an, bn, gn = a.float().numpy(), b.float().numpy(), g.float().numpy()
+    h_ref = oracle.scan_forward_channels_last(an, bn)
+    h16 = torch.from_numpy(h_ref).to(dtype)
+    ga_ref, gb_ref = oracle.scan_backward_channels_last(an, h16.float().numpy(), gn)
+    lib = _native.load()
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), h16.cuda()
+    h, ga, gb = torch.empty_like(da), torch.empty_like(da), torch.empty_like(da)
+    need = lib.ssb_scan_cl_h16_workspace_bytes(N, T, C) if scratch else 0
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    wp = ws.data_ptr() if scratch else None
+    st = _native.stream_of(da)
+    _native.check(getattr(lib, f"ssb_scan_cl_fwd_{name}")(da.data_ptr(), db.data_ptr(), h.data_ptr(), N, T, C, wp, need, st))
+    _native.check(getattr(lib, f"ssb_scan_cl_bwd_{name}")(da.data_ptr(), dh.data_ptr(), dg.data_ptr(), ga.data_ptr(),
+                                                           gb.data_ptr(), N, T, C, wp, need, st))
+    _gpu.device_ok()
+    for x, ref in ((h, h_ref), (ga, ga_ref), (gb, gb_ref)):
+        assert _gpu.max_norm_err(x.float(), ref) < 1.01 * half_ulp
+        exact = torch.from_numpy(ref).to(dtype).float().numpy()
+        assert (x.float().cpu().numpy() != exact).mean() < 1e-2
+    rc = getattr(lib, f"ssb_scan_cl_fwd_{name}")(da.data_ptr(), db.data_ptr(), h.data_ptr(), 1, N * T * C // 4, 4, None, 0, st)
+    assert rc == _native.ERR_UNSUPPORTED  # C % 8 != 0
