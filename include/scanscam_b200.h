@@ -48,7 +48,9 @@ typedef enum ssb_variant {
     SSB_VARIANT_AUTO = 0,
     SSB_VARIANT_WARP = 1,    /* one warp per row, register-resident, any T / any alignment */
     SSB_VARIANT_TMA = 2,     /* TMA-staged shared-memory tiles; needs T % 32 == 0, 16-B aligned base */
-    SSB_VARIANT_LOOKBACK = 3, /* T split across CTAs with decoupled look-back; needs a workspace */
+    SSB_VARIANT_LOOKBACK = 3, /* T split across CTAs with decoupled look-back; needs a workspace.  Tuning id 16
+                                 (variant | 16 << 8): no look-back but two passes over 4096-step chunks of T
+                                 run as rows of their own (chunk maps, carries, scan) */
     SSB_VARIANT_FLAT = 4,    /* memcpy-like sweep, CTA-wide scan of 16 KB spans; needs T % 4 == 0, 16-B aligned base */
     SSB_VARIANT_FLAT_ANY = 5 /* the same sweep with per-element row boundaries: any T, 16-B aligned base */
 } ssb_variant_t;

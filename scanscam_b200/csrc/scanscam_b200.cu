@@ -332,7 +332,27 @@ bool lookback_eligible(int64_t rows, int64_t T, int tuning) {
     return cap > 0 && flat_eligible(rows, T) && T / 4 > cap;
 }
 
+// Tuning id 16 of the family: no look-back at all but two passes over chunks of T (few, very long
+// rows, where the look-back chain of a row has too few CTAs behind it to hide its latency).
+constexpr int kChunkedId = 16;
+int64_t chunked_len(int64_t T) {  // a power of two that divides T: the chunks are rows of a [rows*K, len] view
+    for (int64_t c = 4096; c >= 256; c >>= 1)
+        if (T % c == 0 && T / c >= 2) return c;
+    return 0;
+}
+size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
+bool chunked_eligible(int64_t rows, int64_t T) {
+    const int64_t len = chunked_len(T);
+    return len > 0 && rows > 0 && T / len <= 0x7fffffffLL / rows;
+}
+size_t chunked_bytes(int64_t rows, int64_t T) {  // maps [rows*K][2], carry [rows*K], h_prev [rows*K]
+    if (!chunked_eligible(rows, T)) return 0;
+    const size_t views = (size_t)rows * (size_t)(T / chunked_len(T));
+    return round256(views * 8) + 2 * round256(views * 4);
+}
+
 size_t lookback_bytes(int64_t rows, int64_t T, int tuning) {
+    if (tuning == kChunkedId) return chunked_bytes(rows, T);
     const int cap = lookback_cap(tuning);
     if (cap == 0 || T % 4 != 0) return 0;
     const int64_t pieces = (T / 4 + cap - 1) / cap;
@@ -365,9 +385,37 @@ int launch_lookback(const float *gate, const float *in1, const float *in2, float
 }
 
 template <bool BWD>
+int launch_chunked(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows, int64_t T,
+                   const float *carry_in, const float *h_prev, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (!chunked_eligible(rows, T))
+        return fail(SSB_ERR_UNSUPPORTED, "the two-pass chunked scan needs T divisible by a power of two >= 256 (T=%lld)", (long long)T);
+    const size_t need = chunked_bytes(rows, T);
+    if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 256))
+        return fail(SSB_ERR_WORKSPACE, "the two-pass chunked scan needs a 256-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+    const int64_t len = chunked_len(T), K = T / len, views = rows * K;
+    char *ws = static_cast<char *>(workspace);
+    float *maps = reinterpret_cast<float *>(ws);
+    float *carry = reinterpret_cast<float *>(ws + round256((size_t)views * 8));
+    float *hprev = reinterpret_cast<float *>(ws + round256((size_t)views * 8) + round256((size_t)views * 4));
+    // pass 1: the map of every chunk (8 bytes per element read)
+    int rc = BWD ? ssb_shard_reduce_bwd_f32(gate, in2, maps, views, len, nullptr, 0, st)
+                 : ssb_shard_reduce_fwd_f32(gate, in1, maps, views, len, nullptr, 0, st);
+    if (rc != SSB_OK) return rc;
+    const int64_t blocks = (rows * 32 + 255) / 256;
+    ssb::lookback::chunk_carry_kernel<BWD><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float2 *>(maps), rows, K, len,
+                                                                         carry_in, carry, in1, h_prev, hprev);
+    if ((rc = check_launch("chunk_carry_kernel")) != SSB_OK) return rc;
+    // pass 2: the chunks as rows of their own, each started from its entering state
+    if (!BWD) return ssb_scan_fwd_f32_ex(gate, in1, out1, views, len, carry, SSB_VARIANT_AUTO, nullptr, 0, st);
+    return ssb_scan_bwd_f32_ex(gate, in1, in2, out1, out2, views, len, carry, hprev, SSB_VARIANT_AUTO, nullptr, 0, st);
+}
+
+template <bool BWD>
 int dispatch_lookback(int tuning, const float *gate, const float *in1, const float *in2, float *out1, float *out2,
                       int64_t rows, int64_t T, const float *carry_in, const float *h_prev, void *workspace,
                       size_t workspace_bytes, cudaStream_t st) {
+    if (tuning == kChunkedId)
+        return launch_chunked<BWD>(gate, in1, in2, out1, out2, rows, T, carry_in, h_prev, workspace, workspace_bytes, st);
     if (!lookback_eligible(rows, T, tuning))
         return fail(SSB_ERR_UNSUPPORTED, "look-back kernels need 16-byte aligned tensors, T %% 4 == 0 and rows longer than one span (T=%lld)", (long long)T);
     const size_t need = lookback_bytes(rows, T, tuning);
@@ -541,6 +589,13 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 //     unaligned views and fp64 -> one warp per row.
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
+    // A few very long rows: a row's look-back chain has too few CTAs behind it to hide its latency, and
+    // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 16 and 64
+    // rows; at 4 rows and below the serial carry pass over the chunks takes the gain back, at 128 rows
+    // and above look-back is at 4-6 TB/s and wins).
+    if (workspace_ok && all_aligned16 && rows >= 8 && rows <= 96 && T >= 65536 && chunked_len(T) == 4096 &&
+        T / 4096 <= 4096 && chunked_eligible(rows, T) && encode_fn() != nullptr)
+        return SSB_VARIANT_LOOKBACK | (kChunkedId << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
     if (all_aligned16 && tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr) {
         // power-of-two rows that fit a span: the TMA-staged sweep (forward 128 lines x 2 stages;

@@ -36,6 +36,7 @@ def variants(families):
         out += [(f"tma{t}", _native.VARIANT_TMA | (t << 8)) for t in TMA_IDS]
     if "lookback" in families:
         out += [(f"lookback{t}", _native.VARIANT_LOOKBACK | (t << 8)) for t in LOOKBACK_IDS]
+        out.append(("chunked", _native.VARIANT_LOOKBACK | (16 << 8)))  # two passes over chunks of T
     return out
 
 

@@ -292,7 +292,7 @@ def test_lookback_long_rows(shape, gates):
     da, db, dg, dh, dc = a.cuda(), b.cuda(), g.cuda(), dev(h_ref), carry.cuda()
     lib = _native.load()
     ran = 0
-    for tuning in range(7):
+    for tuning in list(range(7)) + [16]:  # 16: the two-pass form over chunks of T (no look-back)
         variant = _gpu.lookback_variant(tuning)
         if lib.ssb_scan_workspace_bytes(rows, T, variant) == 0:
             continue
@@ -334,7 +334,9 @@ def test_lookback_workspace_contract():
         _gpu.fwd(short, short, variant=v, workspace=(torch.empty(4096, dtype=torch.uint8, device="cuda"), 4096))
     assert err.value.status == _native.ERR_UNSUPPORTED
     # the recommendation: look-back only for long rows and only when the caller can supply scratch
-    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) & 0xff == LOOKBACK
+    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) == LOOKBACK | (16 << 8)   # few long rows: two-pass chunked form
+    assert lib.ssb_scan_recommend(256, 65536, 0, 1, 1) == LOOKBACK
+    assert lib.ssb_scan_recommend(64, 65540, 0, 1, 1) == LOOKBACK               # T not a multiple of 4096
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
     assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
     assert lib.ssb_scan_recommend(64, 4092, 0, 1, 1) & 0xff == FLAT
