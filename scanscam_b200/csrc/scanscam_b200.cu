@@ -1224,7 +1224,10 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
     ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
     if ((rc = check_launch("cl_chunk_carry_kernel")) != SSB_OK) return rc;
     if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
-    return launch_cls<CC, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+    if constexpr (sizeof(IO) == 2)
+        return launch_cls<CC, 256, 16, 1, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+    else
+        return launch_cls<CC, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
@@ -1538,7 +1541,7 @@ int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, v
         workspace_bytes >= cls_chunk_workspace_bytes(N, T, C, 64))
         return launch_cls_chunked<BWD, IO>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
     if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-    return launch_cls<64, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st);
+    return launch_cls<64, 256, 16, 1, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
 }
 }  // namespace
 
