@@ -507,9 +507,14 @@ int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::t
     int rc;
     if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
     if ((rc = make_span_map(&m1, in1, rows, T, LINES)) != SSB_OK) return rc;
-    if ((rc = make_span_map(&m2, BWD ? in2 : in1, rows, T, LINES)) != SSB_OK) return rc;
     if ((rc = make_span_map(&mo1, out1, rows, T, LINES)) != SSB_OK) return rc;
-    if ((rc = make_span_map(&mo2, BWD ? out2 : out1, rows, T, LINES)) != SSB_OK) return rc;
+    if (BWD) {
+        if ((rc = make_span_map(&m2, in2, rows, T, LINES)) != SSB_OK) return rc;
+        if ((rc = make_span_map(&mo2, out2, rows, T, LINES)) != SSB_OK) return rc;
+    } else {  // the forward never touches them: any valid descriptor will do
+        m2 = m1;
+        mo2 = mo1;
+    }
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(tma_flat_kernel)");
     static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
