@@ -436,38 +436,39 @@ __global__ void fold_maps_kernel(const float2 *__restrict__ maps, int64_t rows, 
 // Two-pass form for a few very long rows: every row is cut into K chunks that are scanned as rows
 // of their own.  Given the chunks' maps ([rows*K][2], forward or reverse recurrence) this kernel
 // writes the state entering every chunk (carry [rows*K]); the caller's per-row carry0 (may be NULL)
-// enters the first chunk processed.  BWD also gathers h just before each chunk (h_prev_view): the
-// element preceding the chunk in memory, or the caller's h_prev0 / 0 at a row start.  One warp per row.
+// enters the first chunk processed.  One warp per row walks the maps 32 at a time, the next 32
+// already in flight while the current ones are composed.
 template <bool BWD>
-__global__ void chunk_carry_kernel(const float2 *__restrict__ maps, int64_t rows, int64_t K, int64_t chunk_len,
-                                   const float *__restrict__ carry0, float *__restrict__ carry,
-                                   const float *__restrict__ h, const float *__restrict__ h_prev0,
-                                   float *__restrict__ h_prev_view) {
+__global__ void chunk_carry_kernel(const float2 *__restrict__ maps, int64_t rows, int64_t K,
+                                   const float *__restrict__ carry0, float *__restrict__ carry) {
     const int lane = threadIdx.x & 31;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (row >= rows) return;
     float run = carry0 != nullptr ? carry0[row] : 0.f;
+    auto fetch = [&](int64_t base) {
+        const int64_t i = base + lane;  // position in processing order; chunk index is K-1-i backward
+        return i < K ? maps[row * K + (BWD ? K - 1 - i : i)] : make_float2(1.f, 0.f);
+    };
+    float2 next = fetch(0);
     for (int64_t base = 0; base < K; base += 32) {
-        const int64_t i = base + lane;              // position in processing order
-        const int64_t k = BWD ? K - 1 - i : i;      // chunk index
-        float A = 1.f, B = 0.f;
-        if (i < K) {
-            const float2 v = maps[row * K + k];
-            A = v.x;
-            B = v.y;
-        }
+        float A = next.x, B = next.y;
+        next = fetch(base + 32);
         warp_scan_forward<float>(A, B, lane);
         float eA = __shfl_up_sync(kFullMask, A, 1), eB = __shfl_up_sync(kFullMask, B, 1);
         if (lane == 0) { eA = 1.f; eB = 0.f; }
-        if (i < K) {
-            carry[row * K + k] = fmaf(eA, run, eB);
-            if (BWD) {
-                const int64_t v = row * K + k;
-                h_prev_view[v] = k > 0 ? h[v * chunk_len - 1] : (h_prev0 != nullptr ? h_prev0[row] : 0.f);
-            }
-        }
+        const int64_t i = base + lane;
+        if (i < K) carry[row * K + (BWD ? K - 1 - i : i)] = fmaf(eA, run, eB);
         run = fmaf(__shfl_sync(kFullMask, A, 31), run, __shfl_sync(kFullMask, B, 31));
     }
+}
+
+// h just before each chunk of the [rows*K, chunk_len] view (the backward's h_prev): the element
+// preceding the chunk in memory, or the caller's h_prev0 / 0 at a row start.  One thread per chunk.
+__global__ void chunk_h_prev_kernel(const float *__restrict__ h, int64_t rows, int64_t K, int64_t chunk_len,
+                                    const float *__restrict__ h_prev0, float *__restrict__ h_prev_view) {
+    const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= rows * K) return;
+    h_prev_view[v] = (v % K) > 0 ? h[v * chunk_len - 1] : (h_prev0 != nullptr ? h_prev0[v / K] : 0.f);
 }
 
 }  // namespace lookback

@@ -402,9 +402,12 @@ int launch_chunked(const float *gate, const float *in1, const float *in2, float 
                  : ssb_shard_reduce_fwd_f32(gate, in1, maps, views, len, nullptr, 0, st);
     if (rc != SSB_OK) return rc;
     const int64_t blocks = (rows * 32 + 255) / 256;
-    ssb::lookback::chunk_carry_kernel<BWD><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float2 *>(maps), rows, K, len,
-                                                                         carry_in, carry, in1, h_prev, hprev);
+    ssb::lookback::chunk_carry_kernel<BWD><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float2 *>(maps), rows, K, carry_in, carry);
     if ((rc = check_launch("chunk_carry_kernel")) != SSB_OK) return rc;
+    if (BWD) {
+        ssb::lookback::chunk_h_prev_kernel<<<(int)((views + 255) / 256), 256, 0, st>>>(in1, rows, K, len, h_prev, hprev);
+        if ((rc = check_launch("chunk_h_prev_kernel")) != SSB_OK) return rc;
+    }
     // pass 2: the chunks as rows of their own, each started from its entering state
     if (!BWD) return ssb_scan_fwd_f32_ex(gate, in1, out1, views, len, carry, SSB_VARIANT_AUTO, nullptr, 0, st);
     return ssb_scan_bwd_f32_ex(gate, in1, in2, out1, out2, views, len, carry, hprev, SSB_VARIANT_AUTO, nullptr, 0, st);
@@ -595,10 +598,10 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     // A few very long rows: a row's look-back chain has too few CTAs behind it to hide its latency, and
-    // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 16 and 64
-    // rows; at 4 rows and below the serial carry pass over the chunks takes the gain back, at 128 rows
-    // and above look-back is at 4-6 TB/s and wins).
-    if (workspace_ok && all_aligned16 && rows >= 8 && rows <= 96 && T >= 65536 && chunked_len(T) == 4096 &&
+    // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 4, 16 and
+    // 64 rows; at 1-2 rows the serial carry pass over the chunks takes the gain back, from 96 rows up
+    // look-back is at 3.5-6 TB/s and wins).
+    if (workspace_ok && all_aligned16 && rows >= 4 && rows <= 80 && T >= 65536 && chunked_len(T) == 4096 &&
         T / 4096 <= 4096 && chunked_eligible(rows, T) && encode_fn() != nullptr)
         return SSB_VARIANT_LOOKBACK | (kChunkedId << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
