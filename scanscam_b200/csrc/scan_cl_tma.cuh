@@ -143,7 +143,7 @@ cl_tma_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constan
         const int64_t rec = group * geo.pieces + seq;
         const int c0 = (int)(cg * CC), t0 = (int)(piece * TT);
 
-        // Early, non-blocking look at the predecessor this segment will read in round 0.
+        // Early, non-blocking look at the predecessor this segment will read on its first look-back pass.
         unsigned early_flag = 0u;
         float early_val = 0.f;
         if (seg < seq) {
