@@ -206,6 +206,19 @@ int ssb_scan_bwd_recompute_f32(const float *gate, const float *value, const floa
                                float *gvalue, int64_t rows, int64_t T, const float *h_in,
                                const float *c_in, void *workspace, size_t workspace_bytes, void *stream);
 
+/* fp64 with scratch (an addition; same results as ssb_scan_fwd_f64 / ssb_scan_bwd_f64 up to fp64
+ * reassociation).  The fp64 kernels give one warp a row, which needs about a thousand rows to fill
+ * the GPU; with fewer than 768 rows of T >= 16384, T % 4096 == 0, and a workspace of
+ * ssb_scan_f64_workspace_bytes(rows, T) bytes (256-byte aligned; 0 = this shape never uses one)
+ * the rows are cut into 4096-step chunks and scanned in two passes.  NULL / too small a workspace
+ * or any other shape behaves exactly like the plain entry points. */
+size_t ssb_scan_f64_workspace_bytes(int64_t rows, int64_t T);
+int ssb_scan_fwd_f64_ex(const double *gate, const double *value, double *out, int64_t rows, int64_t T,
+                        const double *h_in, void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_bwd_f64_ex(const double *gate, const double *h, const double *gout, double *ggate,
+                        double *gvalue, int64_t rows, int64_t T, const double *c_in,
+                        const double *h_prev, void *workspace, size_t workspace_bytes, void *stream);
+
 /* Bytes of scratch the given variant needs for a [rows, T] problem (0 = none).
  * The workspace must be 256-byte aligned; its contents need not be initialised (the entry
  * point clears what it needs on the stream it launches on).  A workspace must not be shared

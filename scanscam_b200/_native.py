@@ -24,6 +24,9 @@ SIGNATURES = {
     "ssb_scan_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
     "ssb_scan_fwd_f64": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
     "ssb_scan_fwd_f32_ex": (_int, [_p, _p, _p, _i64, _i64, _p, _int, _p, _sz, _p]),
+    "ssb_scan_f64_workspace_bytes": (_sz, [_i64, _i64]),
+    "ssb_scan_fwd_f64_ex": (_int, [_p, _p, _p, _i64, _i64, _p, _p, _sz, _p]),
+    "ssb_scan_bwd_f64_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p, _sz, _p]),
     "ssb_scan_fwd_f32_static": (_int, [_p, _p, _p, _i64, _i64, _p, _p]),
     "ssb_scan_bwd_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),
     "ssb_scan_bwd_f64": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _p, _p, _p]),

@@ -438,37 +438,45 @@ __global__ void fold_maps_kernel(const float2 *__restrict__ maps, int64_t rows, 
 // writes the state entering every chunk (carry [rows*K]); the caller's per-row carry0 (may be NULL)
 // enters the first chunk processed.  One warp per row walks the maps 32 at a time, the next 32
 // already in flight while the current ones are composed.
-template <bool BWD>
-__global__ void chunk_carry_kernel(const float2 *__restrict__ maps, int64_t rows, int64_t K,
-                                   const float *__restrict__ carry0, float *__restrict__ carry) {
+template <bool BWD, typename real>
+__global__ void chunk_carry_kernel(const real *__restrict__ maps, int64_t rows, int64_t K,
+                                   const real *__restrict__ carry0, real *__restrict__ carry) {
     const int lane = threadIdx.x & 31;
     const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (row >= rows) return;
-    float run = carry0 != nullptr ? carry0[row] : 0.f;
+    real run = carry0 != nullptr ? carry0[row] : real(0);
+    real nA, nB;
     auto fetch = [&](int64_t base) {
         const int64_t i = base + lane;  // position in processing order; chunk index is K-1-i backward
-        return i < K ? maps[row * K + (BWD ? K - 1 - i : i)] : make_float2(1.f, 0.f);
+        nA = real(1);
+        nB = real(0);
+        if (i < K) {
+            const real *m = maps + 2 * (row * K + (BWD ? K - 1 - i : i));
+            nA = m[0];
+            nB = m[1];
+        }
     };
-    float2 next = fetch(0);
+    fetch(0);
     for (int64_t base = 0; base < K; base += 32) {
-        float A = next.x, B = next.y;
-        next = fetch(base + 32);
-        warp_scan_forward<float>(A, B, lane);
-        float eA = __shfl_up_sync(kFullMask, A, 1), eB = __shfl_up_sync(kFullMask, B, 1);
-        if (lane == 0) { eA = 1.f; eB = 0.f; }
+        real A = nA, B = nB;
+        fetch(base + 32);
+        warp_scan_forward<real>(A, B, lane);
+        real eA = __shfl_up_sync(kFullMask, A, 1), eB = __shfl_up_sync(kFullMask, B, 1);
+        if (lane == 0) { eA = real(1); eB = real(0); }
         const int64_t i = base + lane;
-        if (i < K) carry[row * K + (BWD ? K - 1 - i : i)] = fmaf(eA, run, eB);
-        run = fmaf(__shfl_sync(kFullMask, A, 31), run, __shfl_sync(kFullMask, B, 31));
+        if (i < K) carry[row * K + (BWD ? K - 1 - i : i)] = fma_<real>(eA, run, eB);
+        run = fma_<real>(__shfl_sync(kFullMask, A, 31), run, __shfl_sync(kFullMask, B, 31));
     }
 }
 
 // h just before each chunk of the [rows*K, chunk_len] view (the backward's h_prev): the element
 // preceding the chunk in memory, or the caller's h_prev0 / 0 at a row start.  One thread per chunk.
-__global__ void chunk_h_prev_kernel(const float *__restrict__ h, int64_t rows, int64_t K, int64_t chunk_len,
-                                    const float *__restrict__ h_prev0, float *__restrict__ h_prev_view) {
+template <typename real>
+__global__ void chunk_h_prev_kernel(const real *__restrict__ h, int64_t rows, int64_t K, int64_t chunk_len,
+                                    const real *__restrict__ h_prev0, real *__restrict__ h_prev_view) {
     const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= rows * K) return;
-    h_prev_view[v] = (v % K) > 0 ? h[v * chunk_len - 1] : (h_prev0 != nullptr ? h_prev0[v / K] : 0.f);
+    h_prev_view[v] = (v % K) > 0 ? h[v * chunk_len - 1] : (h_prev0 != nullptr ? h_prev0[v / K] : real(0));
 }
 
 }  // namespace lookback

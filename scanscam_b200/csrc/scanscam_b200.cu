@@ -345,10 +345,10 @@ bool chunked_eligible(int64_t rows, int64_t T) {
     const int64_t len = chunked_len(T);
     return len > 0 && rows > 0 && T / len <= 0x7fffffffLL / rows;
 }
-size_t chunked_bytes(int64_t rows, int64_t T) {  // maps [rows*K][2], carry [rows*K], h_prev [rows*K]
+size_t chunked_bytes(int64_t rows, int64_t T, size_t elem = 4) {  // maps [rows*K][2], carry [rows*K], h_prev [rows*K]
     if (!chunked_eligible(rows, T)) return 0;
     const size_t views = (size_t)rows * (size_t)(T / chunked_len(T));
-    return round256(views * 8) + 2 * round256(views * 4);
+    return round256(views * 2 * elem) + 2 * round256(views * elem);
 }
 
 size_t lookback_bytes(int64_t rows, int64_t T, int tuning) {
@@ -384,33 +384,44 @@ int launch_lookback(const float *gate, const float *in1, const float *in2, float
     return check_launch("lookback_kernel");
 }
 
-template <bool BWD>
-int launch_chunked(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows, int64_t T,
-                   const float *carry_in, const float *h_prev, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+template <bool BWD, typename real = float>
+int launch_chunked(const real *gate, const real *in1, const real *in2, real *out1, real *out2, int64_t rows, int64_t T,
+                   const real *carry_in, const real *h_prev, void *workspace, size_t workspace_bytes, cudaStream_t st) {
     if (!chunked_eligible(rows, T))
         return fail(SSB_ERR_UNSUPPORTED, "the two-pass chunked scan needs T divisible by a power of two >= 256 (T=%lld)", (long long)T);
-    const size_t need = chunked_bytes(rows, T);
+    const size_t need = chunked_bytes(rows, T, sizeof(real));
     if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 256))
         return fail(SSB_ERR_WORKSPACE, "the two-pass chunked scan needs a 256-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
     const int64_t len = chunked_len(T), K = T / len, views = rows * K;
     char *ws = static_cast<char *>(workspace);
-    float *maps = reinterpret_cast<float *>(ws);
-    float *carry = reinterpret_cast<float *>(ws + round256((size_t)views * 8));
-    float *hprev = reinterpret_cast<float *>(ws + round256((size_t)views * 8) + round256((size_t)views * 4));
-    // pass 1: the map of every chunk (8 bytes per element read)
-    int rc = BWD ? ssb_shard_reduce_bwd_f32(gate, in2, maps, views, len, nullptr, 0, st)
+    real *maps = reinterpret_cast<real *>(ws);
+    real *carry = reinterpret_cast<real *>(ws + round256((size_t)views * 2 * sizeof(real)));
+    real *hprev = reinterpret_cast<real *>(ws + round256((size_t)views * 2 * sizeof(real)) + round256((size_t)views * sizeof(real)));
+    // pass 1: the map of every chunk (two of the tensors read once)
+    int rc;
+    if constexpr (sizeof(real) == 4) {
+        rc = BWD ? ssb_shard_reduce_bwd_f32(gate, in2, maps, views, len, nullptr, 0, st)
                  : ssb_shard_reduce_fwd_f32(gate, in1, maps, views, len, nullptr, 0, st);
+    } else {
+        rc = BWD ? launch_warp_bwd<real, true>(gate, nullptr, in2, nullptr, nullptr, views, len, nullptr, nullptr, maps, st)
+                 : launch_warp_fwd<real, true>(gate, in1, nullptr, views, len, nullptr, maps, st);
+    }
     if (rc != SSB_OK) return rc;
     const int64_t blocks = (rows * 32 + 255) / 256;
-    ssb::lookback::chunk_carry_kernel<BWD><<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float2 *>(maps), rows, K, carry_in, carry);
+    ssb::lookback::chunk_carry_kernel<BWD, real><<<(int)blocks, 256, 0, st>>>(maps, rows, K, carry_in, carry);
     if ((rc = check_launch("chunk_carry_kernel")) != SSB_OK) return rc;
     if (BWD) {
-        ssb::lookback::chunk_h_prev_kernel<<<(int)((views + 255) / 256), 256, 0, st>>>(in1, rows, K, len, h_prev, hprev);
+        ssb::lookback::chunk_h_prev_kernel<real><<<(int)((views + 255) / 256), 256, 0, st>>>(in1, rows, K, len, h_prev, hprev);
         if ((rc = check_launch("chunk_h_prev_kernel")) != SSB_OK) return rc;
     }
     // pass 2: the chunks as rows of their own, each started from its entering state
-    if (!BWD) return ssb_scan_fwd_f32_ex(gate, in1, out1, views, len, carry, SSB_VARIANT_AUTO, nullptr, 0, st);
-    return ssb_scan_bwd_f32_ex(gate, in1, in2, out1, out2, views, len, carry, hprev, SSB_VARIANT_AUTO, nullptr, 0, st);
+    if constexpr (sizeof(real) == 4) {
+        if (!BWD) return ssb_scan_fwd_f32_ex(gate, in1, out1, views, len, carry, SSB_VARIANT_AUTO, nullptr, 0, st);
+        return ssb_scan_bwd_f32_ex(gate, in1, in2, out1, out2, views, len, carry, hprev, SSB_VARIANT_AUTO, nullptr, 0, st);
+    } else {
+        if (!BWD) return launch_warp_fwd<real, false>(gate, in1, out1, views, len, carry, nullptr, st);
+        return launch_warp_bwd<real, false>(gate, in1, in2, out1, out2, views, len, carry, hprev, nullptr, st);
+    }
 }
 
 template <bool BWD>
@@ -945,6 +956,49 @@ int ssb_scan_bwd_f64(const double *gate, const double *h, const double *gout, do
         return fail(SSB_ERR_ALIGNMENT, "ssb_scan_bwd_f64: pointers must be 8-byte aligned");
     return launch_warp_bwd<double, false>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr,
                                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ---- fp64 with scratch: a few long rows in two passes ------------------------------------------
+namespace {
+// One warp per row needs about a thousand rows to fill the GPU; below that, rows of whole 4096-step
+// chunks run in the two-pass chunked form (40 / 56 bytes per element moved instead of 24 / 40).
+// Measured: 16 rows x 2^21 steps 11.3 / 14.3 ms -> 0.25 / 0.33 ms, 512 rows 1.6x faster, 1024 rows slower.
+constexpr int64_t kF64ChunkedRows = 768;
+bool f64_chunked_applies(int64_t rows, int64_t T, const void *workspace, size_t workspace_bytes) {
+    return rows < kF64ChunkedRows && T >= 16384 && chunked_len(T) == 4096 && chunked_eligible(rows, T) && workspace != nullptr &&
+           aligned_to(workspace, 256) && workspace_bytes >= chunked_bytes(rows, T, 8);
+}
+}  // namespace
+
+extern "C" {
+
+size_t ssb_scan_f64_workspace_bytes(int64_t rows, int64_t T) {
+    if (rows <= 0 || T <= 0 || rows >= kF64ChunkedRows || T < 16384 || chunked_len(T) != 4096) return 0;
+    return chunked_bytes(rows, T, 8);
+}
+
+int ssb_scan_fwd_f64_ex(const double *gate, const double *value, double *out, int64_t rows, int64_t T, const double *h_in,
+                        void *workspace, size_t workspace_bytes, void *stream) {
+    int64_t n;
+    if (check_shape(rows, T, &n) == SSB_OK && n > 0 && gate && value && out && aligned_to(gate, 8) && aligned_to(value, 8) &&
+        aligned_to(out, 8) && aligned_to(h_in, 8) && f64_chunked_applies(rows, T, workspace, workspace_bytes))
+        return launch_chunked<false, double>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, workspace,
+                                             workspace_bytes, static_cast<cudaStream_t>(stream));
+    return ssb_scan_fwd_f64(gate, value, out, rows, T, h_in, stream);
+}
+
+int ssb_scan_bwd_f64_ex(const double *gate, const double *h, const double *gout, double *ggate, double *gvalue, int64_t rows,
+                        int64_t T, const double *c_in, const double *h_prev, void *workspace, size_t workspace_bytes,
+                        void *stream) {
+    int64_t n;
+    if (check_shape(rows, T, &n) == SSB_OK && n > 0 && gate && h && gout && ggate && gvalue && aligned_to(gate, 8) &&
+        aligned_to(h, 8) && aligned_to(gout, 8) && aligned_to(ggate, 8) && aligned_to(gvalue, 8) && aligned_to(c_in, 8) &&
+        aligned_to(h_prev, 8) && f64_chunked_applies(rows, T, workspace, workspace_bytes))
+        return launch_chunked<true, double>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, workspace, workspace_bytes,
+                                            static_cast<cudaStream_t>(stream));
+    return ssb_scan_bwd_f64(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, stream);
 }
 
 }  // extern "C"

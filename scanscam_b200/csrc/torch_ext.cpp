@@ -89,8 +89,11 @@ void scan_forward_impl(const torch::Tensor &gate, const torch::Tensor &value, to
                                  static_cast<const float *>(hin), (int)variant, ws_bytes ? ws.data_ptr() : nullptr,
                                  ws_bytes, current_stream());
     } else {
-        rc = ssb_scan_fwd_f64(gate.data_ptr<double>(), value.data_ptr<double>(), output.data_ptr<double>(), rows, T,
-                              static_cast<const double *>(hin), current_stream());
+        const size_t ws_bytes = ssb_scan_f64_workspace_bytes(rows, T);
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        rc = ssb_scan_fwd_f64_ex(gate.data_ptr<double>(), value.data_ptr<double>(), output.data_ptr<double>(), rows, T,
+                                 static_cast<const double *>(hin), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     }
     raise_on(rc, op);
 }
@@ -128,9 +131,13 @@ void scan_backward_impl(const torch::Tensor &gate, const torch::Tensor &output, 
                                  static_cast<const float *>(cin), static_cast<const float *>(hp), (int)variant,
                                  ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     } else {
-        rc = ssb_scan_bwd_f64(gate.data_ptr<double>(), output.data_ptr<double>(), out_grad.data_ptr<double>(),
-                              gate_grad.data_ptr<double>(), value_grad.data_ptr<double>(), rows, T,
-                              static_cast<const double *>(cin), static_cast<const double *>(hp), current_stream());
+        const size_t ws_bytes = ssb_scan_f64_workspace_bytes(rows, T);
+        torch::Tensor ws;
+        if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
+        rc = ssb_scan_bwd_f64_ex(gate.data_ptr<double>(), output.data_ptr<double>(), out_grad.data_ptr<double>(),
+                                 gate_grad.data_ptr<double>(), value_grad.data_ptr<double>(), rows, T,
+                                 static_cast<const double *>(cin), static_cast<const double *>(hp),
+                                 ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     }
     raise_on(rc, op);
 }

@@ -650,3 +650,29 @@ def test_channels_last_16bit_storage(name, shape, scratch):
         assert (x.float().cpu().numpy() != exact).mean() < 1e-2
     rc = getattr(lib, f"ssb_scan_cl_fwd_{name}")(da.data_ptr(), db.data_ptr(), h.data_ptr(), 1, N * T * C // 4, 4, None, 0, st)
     assert rc == _native.ERR_UNSUPPORTED  # C % 8 != 0
+
+
+@pytest.mark.parametrize("shape", [(3, 16384), (17, 65536), (1, 262144), (40, 16388)])
+def test_fp64_few_long_rows_with_scratch(shape):
+    """ssb_scan_{fwd,bwd}_f64_ex: with scratch, a few rows of whole 4096-step chunks run in two
+    passes; the last shape (T % 4096 != 0) needs no scratch and takes the plain kernels."""
+    rows, T = shape
+    a, b, g = make_inputs("sigmoid2", shape, seed=141, dtype=torch.float64)
+    carry = torch.randn(rows, dtype=torch.float64)
+    an, bn, gn, cn = a.numpy(), b.numpy(), g.numpy(), carry.numpy()
+    h_ref = oracle.scan_forward(an, bn, h_in=cn)
+    ga_ref, gb_ref = oracle.scan_backward(an, h_ref, gn, gb_in=cn, h_prev=cn)
+    lib = _native.load()
+    need = lib.ssb_scan_f64_workspace_bytes(rows, T)
+    assert (need > 0) == (T % 4096 == 0)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    da, db, dg, dh, dc = a.cuda(), b.cuda(), g.cuda(), dev(h_ref), carry.cuda()
+    st = _native.stream_of(da)
+    for wp, nb in ((ws.data_ptr(), need), (None, 0)):
+        h, ga, gb = torch.empty_like(da), torch.empty_like(da), torch.empty_like(da)
+        _native.check(lib.ssb_scan_fwd_f64_ex(da.data_ptr(), db.data_ptr(), h.data_ptr(), rows, T, dc.data_ptr(), wp, nb, st))
+        _native.check(lib.ssb_scan_bwd_f64_ex(da.data_ptr(), dh.data_ptr(), dg.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
+                                              dc.data_ptr(), dc.data_ptr(), wp, nb, st))
+        for got, ref in ((h, h_ref), (ga, ga_ref), (gb, gb_ref)):
+            assert _gpu.max_norm_err(got, ref) < 1e-12
+    _gpu.device_ok()
