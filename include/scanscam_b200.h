@@ -265,6 +265,28 @@ int ssb_scan_cl_bwd_f16(const void *gate, const void *h, const void *gout, void 
                         int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes,
                         void *stream);
 
+/* Channels-last with gate logits in (sigmoid fused, as ssb_scan_sigmoid_*; no counterpart in the
+ * reference), fp32 (C % 4 == 0) and 16-bit tensors (C % 8 == 0), 16-byte aligned; always the
+ * streaming kernels.  `workspace`: ssb_scan_cl_workspace_bytes (fp32) or
+ * ssb_scan_cl_h16_workspace_bytes (16-bit) bytes, may be NULL (then shapes with few channel blocks
+ * run one CTA per block instead of the two-pass chunked form).  SSB_ERR_UNSUPPORTED for other
+ * channel counts or alignments: apply the sigmoid separately. */
+int ssb_scan_cl_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t N, int64_t T,
+                                int64_t C, void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_sigmoid_bwd_f32(const float *gate_logits, const float *h, const float *gout, float *glogits,
+                                float *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
+                                size_t workspace_bytes, void *stream);
+int ssb_scan_cl_sigmoid_fwd_bf16(const void *gate_logits, const void *value, void *out, int64_t N, int64_t T,
+                                 int64_t C, void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_sigmoid_bwd_bf16(const void *gate_logits, const void *h, const void *gout, void *glogits,
+                                 void *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
+                                 size_t workspace_bytes, void *stream);
+int ssb_scan_cl_sigmoid_fwd_f16(const void *gate_logits, const void *value, void *out, int64_t N, int64_t T,
+                                int64_t C, void *workspace, size_t workspace_bytes, void *stream);
+int ssb_scan_cl_sigmoid_bwd_f16(const void *gate_logits, const void *h, const void *gout, void *glogits,
+                                void *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
+                                size_t workspace_bytes, void *stream);
+
 /* Channels-last with scratch: with scratch the time axis can be split across CTAs (two-pass
  * chunked streaming, or decoupled look-back), so the whole GPU is busy even when N*C is small.
  * `workspace` of ssb_scan_cl_workspace_bytes(N,T,C) bytes, 256-byte aligned, contents irrelevant;

@@ -53,6 +53,12 @@ SIGNATURES = {
     "ssb_scan_recommend": (_int, [_i64, _i64, _int, _int, _int]),
     "ssb_scan_cl_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "ssb_scan_cl_h16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "ssb_scan_cl_sigmoid_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_sigmoid_bwd_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_sigmoid_fwd_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_sigmoid_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_sigmoid_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_sigmoid_bwd_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_fwd_bf16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),

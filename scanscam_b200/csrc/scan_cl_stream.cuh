@@ -28,6 +28,8 @@
 //     channels; with 16-bit storage they are 8 bytes (one 64-bit shared-memory access), a tile row
 //     of CC channels is CC*2 bytes, and the 16 threads of a half warp cover a 128-byte row.
 //     Chunk maps and carries stay fp32.
+//   * SIGMOID: the gate tensor holds logits z; the gate is sigmoid(z) (flat::sigmoidf) and the
+//     backward's first output is the gradient with respect to z.
 //
 // Every mbarrier wait is bounded; a wait that runs out is reported through the status word.
 #pragma once
@@ -35,6 +37,7 @@
 #include <cuda.h>
 
 #include "scan_common.cuh"
+#include "scan_flat.cuh"
 #include "scan_tma.cuh"
 
 namespace ssb {
@@ -107,7 +110,15 @@ __device__ __forceinline__ void sts_vec4(uint32_t addr, float4 v) {
     }
 }
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
+__device__ __forceinline__ float4 sigmoid4(float4 z) {
+    return make_float4(flat::sigmoidf(z.x), flat::sigmoidf(z.y), flat::sigmoidf(z.z), flat::sigmoidf(z.w));
+}
+__device__ __forceinline__ float4 dsigmoid4(float4 a) {  // a (1 - a), the derivative of the sigmoid at its output a
+    return make_float4(a.x * (1.f - a.x), a.y * (1.f - a.y), a.z * (1.f - a.z), a.w * (1.f - a.w));
+}
+
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float,
+          bool SIGMOID = false>
 __global__ void __launch_bounds__(CC / 4 * SEG)
 cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                  const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
@@ -186,6 +197,7 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
 #pragma unroll
         for (int k = 0; k < TS; k++) {
             a[k] = lds_vec4<IO>(in0 + k * ROW);
+            if (SIGMOID) a[k] = sigmoid4(a[k]);
             if (BWD && REDUCE) {
                 y[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
             } else {
@@ -259,7 +271,9 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             for (int k = TS - 1; k >= 0; k--) {
                 const float4 gb = add4(y[k], s);
                 s = mul4(a[k], gb);
-                sts_vec4<IO>(ob + k * ROW, mul4(gb, x[k]));   // grad of gate = gb_t * h_{t-1}
+                float4 dgate = mul4(gb, x[k]);  // grad of gate = gb_t * h_{t-1}
+                if (SIGMOID) dgate = mul4(dgate, dsigmoid4(a[k]));
+                sts_vec4<IO>(ob + k * ROW, dgate);
                 sts_vec4<IO>(ob + TILE + k * ROW, gb);        // grad of value
             }
         }

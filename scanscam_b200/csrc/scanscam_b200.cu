@@ -1215,12 +1215,12 @@ int make_cl_map(CUtensorMap *map, const IO *ptr, int64_t N, int64_t T, int64_t C
 // `chunk_steps` = 0: a unit is all of T.  Otherwise (a multiple of TT) T is cut into chunks of that
 // many steps, each a unit of its own that starts from carry_in[unit][CC] (or, REDUCE, only writes
 // its map to maps[unit][2][CC]).  Tensors a REDUCE launch does not touch may be NULL.
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float, bool SIGMOID = false>
 int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typename as_given<IO>::type *in2,
                typename as_given<IO>::type *out1, typename as_given<IO>::type *out2, int64_t N, int64_t T,
                int64_t C, cudaStream_t st, int64_t chunk_steps = 0, const float *carry_in = nullptr, float *maps = nullptr) {
     using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
-    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
+    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO, SIGMOID>;
     const int64_t cblocks = (C + CC - 1) / CC, tiles = (T + TT - 1) / TT;
     if (tiles > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
     if (chunk_steps % TT != 0) return fail(SSB_ERR_BAD_ARG, "channels-last streaming kernels: chunk of %lld steps, tiles of %d", (long long)chunk_steps, TT);
@@ -1270,7 +1270,7 @@ size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C, int cc = 32) {
     return (size_t)(N * ((C + cc - 1) / cc) * chunks) * 3 * cc * sizeof(float);
 }
 
-template <bool BWD, typename IO = float>
+template <bool BWD, typename IO = float, bool SIGMOID = false>
 int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, const typename as_given<IO>::type *in2,
                        typename as_given<IO>::type *out1, typename as_given<IO>::type *out2, int64_t N, int64_t T,
                        int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
@@ -1280,16 +1280,16 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
         return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
                     cls_chunk_workspace_bytes(N, T, C, CC), workspace_bytes);
     float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * CC;
-    int rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
+    int rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO, SIGMOID>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
     if (rc != SSB_OK) return rc;
     const int64_t threads = pairs * CC;
     ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
     if ((rc = check_launch("cl_chunk_carry_kernel")) != SSB_OK) return rc;
-    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
+    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
     if constexpr (sizeof(IO) == 2)
-        return launch_cls<CC, 256, 16, 1, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+        return launch_cls<CC, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
     else
-        return launch_cls<CC, 128, 16, 2, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+        return launch_cls<CC, 128, 16, 2, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
@@ -1583,7 +1583,7 @@ bool cl_h16_eligible(int64_t N, int64_t T, int64_t C) {
     return C % 8 == 0 && N <= 0x7fffffffLL && T <= 0x7fffff00LL && C <= 0x7fffffffLL && T <= ((1LL << 40) - 1) / 2 / C;
 }
 
-template <typename IO, bool BWD>
+template <typename IO, bool BWD, bool SIGMOID = false>
 int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, void *out2_, int64_t N, int64_t T, int64_t C,
            void *workspace, size_t workspace_bytes, void *stream, const char *who) {
     int64_t n;
@@ -1601,9 +1601,9 @@ int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, v
     const int64_t pairs = N * ((C + 63) / 64);
     if (pairs < 96 && T >= 2048 && workspace != nullptr && aligned_to(workspace, 256) &&
         workspace_bytes >= cls_chunk_workspace_bytes(N, T, C, 64))
-        return launch_cls_chunked<BWD, IO>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
-    if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-    return launch_cls<64, 256, 16, 1, 1, true, false, IO>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
+        return launch_cls_chunked<BWD, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+    if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+    return launch_cls<64, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
 }
 }  // namespace
 
@@ -1631,6 +1631,68 @@ int ssb_scan_cl_fwd_f16(const void *gate, const void *value, void *out, int64_t 
 int ssb_scan_cl_bwd_f16(const void *gate, const void *h, const void *gout, void *ggate, void *gvalue, int64_t N, int64_t T,
                         int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
     return cl_h16<__half, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, stream, "ssb_scan_cl_bwd_f16");
+}
+
+// Gate logits in, channels-last (the sigmoid and its derivative computed in the streaming kernels).
+int ssb_scan_cl_sigmoid_fwd_bf16(const void *gate_logits, const void *value, void *out, int64_t N, int64_t T, int64_t C,
+                                 void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__nv_bfloat16, false, true>(gate_logits, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes,
+                                              stream, "ssb_scan_cl_sigmoid_fwd_bf16");
+}
+int ssb_scan_cl_sigmoid_bwd_bf16(const void *gate_logits, const void *h, const void *gout, void *glogits, void *gvalue,
+                                 int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__nv_bfloat16, true, true>(gate_logits, h, gout, glogits, gvalue, N, T, C, workspace, workspace_bytes, stream,
+                                             "ssb_scan_cl_sigmoid_bwd_bf16");
+}
+int ssb_scan_cl_sigmoid_fwd_f16(const void *gate_logits, const void *value, void *out, int64_t N, int64_t T, int64_t C,
+                                void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__half, false, true>(gate_logits, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, stream,
+                                       "ssb_scan_cl_sigmoid_fwd_f16");
+}
+int ssb_scan_cl_sigmoid_bwd_f16(const void *gate_logits, const void *h, const void *gout, void *glogits, void *gvalue,
+                                int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_h16<__half, true, true>(gate_logits, h, gout, glogits, gvalue, N, T, C, workspace, workspace_bytes, stream,
+                                      "ssb_scan_cl_sigmoid_bwd_f16");
+}
+
+}  // extern "C"
+
+namespace {
+template <bool BWD>
+int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+                   int64_t C, void *workspace, size_t workspace_bytes, void *stream, const char *who) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !in1 || (BWD && !in2) || !out1 || (BWD && !out2)) return fail(SSB_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(in1, 16) && aligned_to(in2, 16) && aligned_to(out1, 16) &&
+                      aligned_to(out2, 16);
+    if (!al16 || !cl3_eligible(N, T, C) || encode_fn() == nullptr)
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs C %% 4 == 0 and 16-byte aligned tensors (C=%lld)", who, (long long)C);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cl_stream_block(N, T, C, true) == 0 && cl_chunked_applies(N, T, C, true, workspace, workspace_bytes))
+        return launch_cls_chunked<BWD, float, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+    if (cl_stream_block(N, T, C, true) == 64) {
+        if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+        return launch_cls<64, 128, 8, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+    }
+    if (!BWD) return launch_cls<32, 256, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+    return launch_cls<32, 128, 16, 2, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+}
+}  // namespace
+
+extern "C" {
+
+int ssb_scan_cl_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t N, int64_t T, int64_t C,
+                                void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_sigmoid_f32<false>(gate_logits, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, stream,
+                                 "ssb_scan_cl_sigmoid_fwd_f32");
+}
+int ssb_scan_cl_sigmoid_bwd_f32(const float *gate_logits, const float *h, const float *gout, float *glogits, float *gvalue,
+                                int64_t N, int64_t T, int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_sigmoid_f32<true>(gate_logits, h, gout, glogits, gvalue, N, T, C, workspace, workspace_bytes, stream,
+                                "ssb_scan_cl_sigmoid_bwd_f32");
 }
 
 int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, int64_t N, int64_t T, int64_t C, void *stream) {

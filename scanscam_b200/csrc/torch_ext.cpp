@@ -321,6 +321,56 @@ void transposed_linear_scan_backward(torch::Tensor gate, torch::Tensor output, t
     raise_on(rc, "transposed_linear_scan_backward");
 }
 
+// ---- channels-last with gate logits in (not in the reference) ------------------------------
+void transposed_scan_sigmoid(torch::Tensor logits, torch::Tensor value, torch::Tensor output) {
+    check_tensor(logits, "gate_logits");
+    TORCH_CHECK(logits.dim() == 3 && (logits.scalar_type() == torch::kFloat32 || is_16bit(logits)),
+                "gate_logits must be 3-D [N, T, C] float32, bfloat16 or float16");
+    check_same(logits, value, "value");
+    check_same(logits, output, "output");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t N = logits.size(0), T = logits.size(1), C = logits.size(2);
+    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_workspace_bytes(N, T, C);
+    torch::Tensor ws;
+    if (ws_bytes > 0) ws = scratch(ws_bytes, logits);
+    void *wp = ws_bytes ? ws.data_ptr() : nullptr;
+    int rc;
+    if (logits.scalar_type() == torch::kFloat32)
+        rc = ssb_scan_cl_sigmoid_fwd_f32(logits.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(), N, T, C, wp,
+                                         ws_bytes, current_stream());
+    else
+        rc = (logits.scalar_type() == torch::kBFloat16 ? ssb_scan_cl_sigmoid_fwd_bf16 : ssb_scan_cl_sigmoid_fwd_f16)(
+            logits.data_ptr(), value.data_ptr(), output.data_ptr(), N, T, C, wp, ws_bytes, current_stream());
+    raise_on(rc, "transposed_scan_sigmoid");
+}
+
+void transposed_scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output, torch::Tensor outGrad,
+                                      torch::Tensor logitsGradOut, torch::Tensor valueGradOut) {
+    check_tensor(logits, "gate_logits");
+    TORCH_CHECK(logits.dim() == 3 && (logits.scalar_type() == torch::kFloat32 || is_16bit(logits)),
+                "gate_logits must be 3-D [N, T, C] float32, bfloat16 or float16");
+    check_same(logits, output, "output");
+    check_same(logits, outGrad, "outGrad");
+    check_same(logits, logitsGradOut, "logitsGradOut");
+    check_same(logits, valueGradOut, "valueGradOut");
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int64_t N = logits.size(0), T = logits.size(1), C = logits.size(2);
+    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_workspace_bytes(N, T, C);
+    torch::Tensor ws;
+    if (ws_bytes > 0) ws = scratch(ws_bytes, logits);
+    void *wp = ws_bytes ? ws.data_ptr() : nullptr;
+    int rc;
+    if (logits.scalar_type() == torch::kFloat32)
+        rc = ssb_scan_cl_sigmoid_bwd_f32(logits.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
+                                         logitsGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), N, T, C, wp, ws_bytes,
+                                         current_stream());
+    else
+        rc = (logits.scalar_type() == torch::kBFloat16 ? ssb_scan_cl_sigmoid_bwd_bf16 : ssb_scan_cl_sigmoid_bwd_f16)(
+            logits.data_ptr(), output.data_ptr(), outGrad.data_ptr(), logitsGradOut.data_ptr(), valueGradOut.data_ptr(), N, T, C,
+            wp, ws_bytes, current_stream());
+    raise_on(rc, "transposed_scan_sigmoid_backward");
+}
+
 // ---- sequence sharding (not in the reference) ------------------------------------------
 void shard_reduce_forward(torch::Tensor gate, torch::Tensor value, torch::Tensor agg) {
     check_tensor(gate, "gate");
@@ -388,6 +438,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("c_in") = py::none(), py::arg("h_prev") = py::none(), py::arg("variant") = 0);
     m.def("scan_sigmoid_forward", &scan_sigmoid_forward, "Forward scan with gate = sigmoid(logits) computed in the kernel");
     m.def("scan_sigmoid_backward", &scan_sigmoid_backward, "Fused backward returning the gradient w.r.t. the gate logits");
+    m.def("transposed_scan_sigmoid", &transposed_scan_sigmoid, "Channels-last forward scan with gate = sigmoid(logits)");
+    m.def("transposed_scan_sigmoid_backward", &transposed_scan_sigmoid_backward,
+          "Channels-last fused backward returning the gradient w.r.t. the gate logits");
     m.def("scan_backward_recompute", &scan_backward_recompute,
           "Fused backward from (gate, value, outGrad): rebuilds the forward's output instead of reading it");
     m.def("shard_reduce_forward", &shard_reduce_forward, "Per-row aggregate map (A, B) of a sequence shard");

@@ -15,7 +15,7 @@ from typing import Any, Tuple
 import torch
 
 from . import cuda
-from .op import scan
+from .op import is_transpose_contig, scan
 
 
 def sweep_row_16bit(steps: int) -> bool:
@@ -54,6 +54,38 @@ class ScanSigmoidGate(torch.autograd.Function):
         return grad_logits.reshape(ctx.full_shape), grad_value.reshape(ctx.full_shape)
 
 
+def _fusable_channels_last(*tensors: torch.Tensor) -> bool:
+    """Inputs viewed as ``[N, C, T]`` but dense in ``[N, T, C]`` order, with a channel count the
+    streaming kernels take (a multiple of 4 for float32, of 8 for the 16-bit types)."""
+    t0 = tensors[0]
+    if t0.device.type != "cuda" or not all(is_transpose_contig(t) and t.data_ptr() % 16 == 0 for t in tensors):
+        return False
+    channels = t0.shape[1]
+    if t0.dtype == torch.float32:
+        return channels % 4 == 0
+    return t0.dtype in (torch.bfloat16, torch.float16) and channels % 8 == 0
+
+
+class ScanSigmoidGateChannelsLast(torch.autograd.Function):
+    """The same operator for channels-last inputs; tensors are handled as dense ``[N, T, C]``."""
+
+    @staticmethod
+    def forward(ctx: Any, gate_logits: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+        z, b = gate_logits.mT, value.mT
+        out = torch.empty_like(z)
+        cuda._ext().transposed_scan_sigmoid(z, b, out)
+        ctx.save_for_backward(z, out)
+        return out.mT
+
+    @staticmethod
+    def backward(ctx: Any, output_grad: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        z, out = ctx.saved_tensors
+        g = output_grad.mT.contiguous()
+        grad_logits, grad_value = torch.empty_like(z), torch.empty_like(z)
+        cuda._ext().transposed_scan_sigmoid_backward(z, out, g, grad_logits, grad_value)
+        return grad_logits.mT, grad_value.mT
+
+
 def scan_sigmoid_gate(gate_logits: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
     """``scan(sigmoid(gate_logits), value)`` over the last axis, differentiable in both arguments.
 
@@ -64,4 +96,6 @@ def scan_sigmoid_gate(gate_logits: torch.Tensor, value: torch.Tensor) -> torch.T
         raise RuntimeError("scanscam_b200.scan_sigmoid_gate needs CUDA tensors; this build has no CPU path")
     if gate_logits.is_contiguous() and value.is_contiguous() and _fusable(gate_logits, value):
         return ScanSigmoidGate.apply(gate_logits, value)
+    if gate_logits.shape == value.shape and _fusable_channels_last(gate_logits, value):
+        return ScanSigmoidGateChannelsLast.apply(gate_logits, value)
     return scan(torch.sigmoid(gate_logits), value)

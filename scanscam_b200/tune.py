@@ -152,6 +152,11 @@ def time_channels_last_16bit(lib, N, T, C, iters):
         tf = run(lambda: fwd(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, ws.data_ptr(), need, st))
         tb = run(lambda: bwd(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C, ws.data_ptr(), need, st))
         out.append((name, 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+        sf, sb = getattr(lib, f"ssb_scan_cl_sigmoid_fwd_{name}"), getattr(lib, f"ssb_scan_cl_sigmoid_bwd_{name}")
+        if sf(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, ws.data_ptr(), need, st) == _native.OK:
+            tf = run(lambda: sf(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, ws.data_ptr(), need, st))
+            tb = run(lambda: sb(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C, ws.data_ptr(), need, st))
+            out.append((name + " fused sigmoid", 3 * size * n / tf / 1e6, tf, 5 * size * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
         del a, b, g, h, ga, gb
     return out
 
@@ -255,10 +260,10 @@ def main():
         if name.startswith("clh16:"):  # channels-last, storage types: clh16:NxTxC
             N, T, C = (int(v) for v in name[6:].lower().split("x"))
             print(f"# channels-last storage types, [N,T,C] = {N}x{T}x{C} ({N * T * C / 1e6:.0f} M elements per tensor)")
-            print(f"{'storage':8s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
+            print(f"{'storage':18s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
             for label, fg, tf, bg, tb, ge in time_channels_last_16bit(lib, N, T, C, args.iters):
                 results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
-                print(f"{label:8s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
+                print(f"{label:18s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
             continue
         if name.startswith("cl:"):  # channels-last: cl:NxTxC
             N, T, C = (int(v) for v in name[3:].lower().split("x"))

@@ -317,3 +317,28 @@ def test_scan_channels_last_with_16bit_tensors(dtype, shape):
     half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
     for x, ref in ((h.mT, h_ref), (da.grad.mT, ga_ref), (db.grad.mT, gb_ref)):
         assert _gpu.max_norm_err(x.detach().float().contiguous(), ref) < 1.01 * half_ulp
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100), (3, 12, 50)])
+def test_fused_sigmoid_gate_channels_last(dtype, shape):
+    """scan_sigmoid_gate on channels-last inputs ([N, C, T] views of dense [N, T, C]): the fused
+    streaming kernels (the last shape's 12 channels fall back to the unfused composition for the
+    16-bit types) against the plain operator run in fp32 on the same inputs."""
+    N, C, T = shape
+    z, b, g = make_inputs("randn", (N, T, C), seed=151)
+    z, b, g = (z + 1).to(dtype).cuda(), b.to(dtype).cuda(), g.to(dtype).cuda()
+    if dtype != torch.float32 and C % 8:
+        with pytest.raises(NotImplementedError):  # neither fused nor unfused: 16-bit channels-last needs C % 8 == 0
+            scanscam_b200.scan_sigmoid_gate(z.mT, b.mT)
+        return
+    tol = {torch.float32: 2e-6, torch.bfloat16: 3 * 2.0 ** -8, torch.float16: 3 * 2.0 ** -11}[dtype]
+    zf, bf = z.float().mT.requires_grad_(True), b.float().mT.requires_grad_(True)
+    ref = scanscam_b200.scan(torch.sigmoid(zf), bf)
+    ref.backward(g.float().mT)
+    z1, b1 = z.mT.requires_grad_(True), b.mT.requires_grad_(True)
+    h = scanscam_b200.scan_sigmoid_gate(z1, b1)
+    assert h.dtype == dtype and op.is_transpose_contig(h)
+    h.backward(g.mT)
+    for x, r in ((h, ref), (z1.grad, zf.grad), (b1.grad, bf.grad)):
+        assert float((x.detach().float() - r.detach()).abs().max() / r.detach().abs().max()) < tol
