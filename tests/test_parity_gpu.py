@@ -676,3 +676,32 @@ def test_fp64_few_long_rows_with_scratch(shape):
         for got, ref in ((h, h_ref), (ga, ga_ref), (gb, gb_ref)):
             assert _gpu.max_norm_err(got, ref) < 1e-12
     _gpu.device_ok()
+
+
+@pytest.mark.parametrize("shape,scratch", [((8, 700, 512), False), ((2, 300, 64), True), ((1, 9000, 64), True),
+                                           ((2, 5000, 200), True), ((3, 100, 8), False), ((1, 4096, 1028), True)])
+def test_channels_last_fused_sigmoid_matches_oracle(shape, scratch):
+    """ssb_scan_cl_sigmoid_{fwd,bwd}_f32 against the oracle fed sigmoid(z) computed on the host;
+    direct streaming and, with scratch on few-block shapes, the two-pass chunked form."""
+    N, T, C = shape
+    z, b, g = make_inputs("randn", shape, seed=161)
+    z = z * 2 + 1
+    a = torch.sigmoid(z)
+    h_ref = oracle.scan_forward_channels_last(a.numpy(), b.numpy())
+    ga_ref, gb_ref = oracle.scan_backward_channels_last(a.numpy(), h_ref, g.numpy())
+    gz_ref = ga_ref * (a * (1 - a)).numpy()
+    lib = _native.load()
+    dz, db, dg, dh = z.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    h, gz, gb = torch.empty_like(dz), torch.empty_like(dz), torch.empty_like(dz)
+    need = lib.ssb_scan_cl_workspace_bytes(N, T, C) if scratch else 0
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    wp = ws.data_ptr() if scratch else None
+    st = _native.stream_of(dz)
+    _native.check(lib.ssb_scan_cl_sigmoid_fwd_f32(dz.data_ptr(), db.data_ptr(), h.data_ptr(), N, T, C, wp, need, st))
+    _native.check(lib.ssb_scan_cl_sigmoid_bwd_f32(dz.data_ptr(), dh.data_ptr(), dg.data_ptr(), gz.data_ptr(), gb.data_ptr(),
+                                                  N, T, C, wp, need, st))
+    _gpu.device_ok()
+    for x, ref in ((h, h_ref), (gz, gz_ref), (gb, gb_ref)):
+        assert _gpu.max_norm_err(x, ref) < TOL
+    rc = lib.ssb_scan_cl_sigmoid_fwd_f32(dz.data_ptr(), db.data_ptr(), h.data_ptr(), 1, N * T * C // 6, 6, None, 0, st)
+    assert rc == _native.ERR_UNSUPPORTED  # C % 4 != 0
