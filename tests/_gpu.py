@@ -125,7 +125,7 @@ def max_norm_err(x, ref):
     """max|x - ref| / max|ref| : the parity metric (elementwise relative error is meaningless
     near zero crossings, where the fp32 oracle itself is several percent from fp64)."""
     x = x.detach().cpu().numpy() if isinstance(x, torch.Tensor) else x
-    return float(np.abs(x.astype(np.float64) - ref.astype(np.float64)).max() / (np.abs(ref).max() + 1e-300))
+    return float(np.abs(x.astype(np.float64) - ref.astype(np.float64)).max() / (float(np.abs(ref).max()) + 1e-300))
 
 
 def allclose_ref(x, ref, atol=1e-4, rtol=1e-5):
