@@ -705,3 +705,46 @@ def test_channels_last_fused_sigmoid_matches_oracle(shape, scratch):
         assert _gpu.max_norm_err(x, ref) < TOL
     rc = lib.ssb_scan_cl_sigmoid_fwd_f32(dz.data_ptr(), db.data_ptr(), h.data_ptr(), 1, N * T * C // 6, 6, None, 0, st)
     assert rc == _native.ERR_UNSUPPORTED  # C % 4 != 0
+
+
+@pytest.mark.skipif(os.environ.get("SCANSCAM_BIG_TESTS") != "1",
+                    reason="holds ~60 GB on the device; set SCANSCAM_BIG_TESTS=1 to run")
+def test_tensors_beyond_2_31_elements():
+    """Index arithmetic past 2^31 elements: the channels-last streaming kernels against the plain
+    kernels and a float64 loop on the tensor's tail, and the 16-bit sweep against the fp32 kernels
+    on its last rows."""
+    def rel(x, y):
+        return float((x - y).abs().max() / y.abs().max())
+
+    N, T, C = 4, 4096, 160000
+    a = torch.rand(N, T, C, device="cuda") * 0.3 + 0.65
+    b, g = torch.randn(N, T, C, device="cuda"), torch.randn(N, T, C, device="cuda")
+    assert a.numel() > 2 ** 31
+    h1, h2 = _gpu.cl_fwd(a, b), _gpu.cl_fwd(a, b, scratch="plain")
+    assert rel(h1, h2) < 1e-5
+    ga1, gb1 = _gpu.cl_bwd(a, h2, g)
+    ga2, gb2 = _gpu.cl_bwd(a, h2, g, scratch="plain")
+    assert rel(ga1, ga2) < 1e-5 and rel(gb1, gb2) < 1e-5
+    sl = (slice(N - 1, N), slice(None), slice(C - 8, C))
+    aa, bb = a[sl].double(), b[sl].double()
+    hh, acc = torch.zeros_like(aa), torch.zeros(1, 8, dtype=torch.float64, device="cuda")
+    for t in range(T):
+        acc = aa[:, t] * acc + bb[:, t]
+        hh[:, t] = acc
+    assert rel(h1[sl].double(), hh) < 1e-5
+    del a, b, g, h1, h2, ga1, gb1, ga2, gb2
+    torch.cuda.empty_cache()
+    rows, T = 700000, 4096
+    a = (torch.rand(rows, T, device="cuda") * 0.3 + 0.65).bfloat16()
+    b, g = torch.randn(rows, T, device="cuda").bfloat16(), torch.randn(rows, T, device="cuda").bfloat16()
+    assert a.numel() > 2 ** 31
+    lib = _native.load()
+    h, ga, gb = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+    st = _native.stream_of(a)
+    _native.check(lib.ssb_scan_fwd_bf16(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, st))
+    _native.check(lib.ssb_scan_bwd_bf16(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T, None, None, st))
+    af, bf = a[-4096:].float(), b[-4096:].float()
+    assert rel(h[-4096:].float(), _gpu.fwd(af, bf)) < 2.0 ** -8
+    gaf, gbf = _gpu.bwd(af, h[-4096:].float(), g[-4096:].float())
+    assert rel(ga[-4096:].float(), gaf) < 2.0 ** -8 and rel(gb[-4096:].float(), gbf) < 2.0 ** -8
+    _gpu.device_ok()
