@@ -623,6 +623,13 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
         return SSB_VARIANT_TMA | ((T > 2048 ? 37 : 36) << 8);
     }
     if (all_aligned16 && flat_eligible(rows, T)) {
+        // The default span holds 4096 elements: whole rows are packed into it, longer rows are walked
+        // in 4096-element pieces.  When that leaves more than a fifth of the span's slots idle
+        // (T = 2200: one row per span; T = 4100: a full piece and a 4-element one) the 2048-element
+        // span of 128 threads x 4 float4s is 3-25 % faster (measured at T = 1500, 2200, 2600, 3000, 4100,
+        // 5000; at T = 6000, two pieces and 73 % used, the large span still wins).
+        const double used = T <= 4096 ? (double)((4096 / T) * T) / 4096.0 : (double)T / (double)(((T + 4095) / 4096) * 4096);
+        if (used < (T <= 4096 ? 0.8 : 0.65)) return SSB_VARIANT_FLAT | (4 << 8);
         if (backward && T > 4096) return SSB_VARIANT_FLAT | (9 << 8);
         return SSB_VARIANT_FLAT | (6 << 8);
     }
