@@ -74,3 +74,16 @@ def test_check_raises_with_the_library_message(native):
 def test_workspace_query(native):
     assert native.ssb_scan_workspace_bytes(1024, 4096, _native.VARIANT_WARP) == 0
     assert native.ssb_scan_workspace_bytes(1024, 4096, _native.VARIANT_TMA) == 0
+
+
+def test_kernel_recommendation_for_row_lengths_that_need_no_device(native):
+    """The part of the default policy that does not depend on a driver being present."""
+    flat = _native.VARIANT_FLAT
+    assert native.ssb_scan_recommend(64, 4092, 0, 1, 0) == flat | (6 << 8)   # fills the 4096-element span
+    assert native.ssb_scan_recommend(64, 3000, 0, 1, 0) == flat | (4 << 8)   # 27 % of it idle: the smaller span
+    assert native.ssb_scan_recommend(64, 2200, 1, 1, 0) == flat | (4 << 8)
+    assert native.ssb_scan_recommend(64, 4100, 0, 1, 0) == flat | (4 << 8)   # a full piece and a 4-element one
+    assert native.ssb_scan_recommend(64, 6000, 0, 1, 0) == flat | (6 << 8)
+    assert native.ssb_scan_recommend(64, 6000, 1, 1, 0) == flat | (9 << 8)
+    assert native.ssb_scan_recommend(64, 1001, 0, 1, 0) == _native.VARIANT_WARP
+    assert native.ssb_scan_recommend(64, 1000, 0, 0, 0) == _native.VARIANT_WARP  # unaligned tensors
