@@ -47,7 +47,9 @@ typedef enum ssb_status {
 typedef enum ssb_variant {
     SSB_VARIANT_AUTO = 0,
     SSB_VARIANT_WARP = 1,    /* one warp per row, register-resident, any T / any alignment */
-    SSB_VARIANT_TMA = 2,     /* TMA-staged shared-memory tiles; needs T % 32 == 0, 16-B aligned base */
+    SSB_VARIANT_TMA = 2,     /* TMA-staged shared-memory tiles; needs T % 32 == 0, 16-B aligned base.  Tuning ids
+                                0..31 per-warp rings, 32..38 the flat sweep for T = 32 * 2^k <= 4096, 48 the flat
+                                sweep over rows that are a multiple (>= 2) of 4096 */
     SSB_VARIANT_LOOKBACK = 3, /* T split across CTAs with decoupled look-back; needs a workspace.  Tuning id 16
                                  (variant | 16 << 8): no look-back but two passes over 4096-step chunks of T
                                  run as rows of their own (chunk maps, carries, scan) */
@@ -154,8 +156,9 @@ int ssb_scan_sigmoid_bwd_f32(const float *gate_logits, const float *h, const flo
  * src/scanscam_cuda.cu:52, and raises for half types).  Halves the bytes the scan moves: forward
  * 6, backward 10 bytes per element.  Same meaning of every argument as ssb_scan_fwd_f32 /
  * ssb_scan_bwd_f32; tensor pointers address 16-bit elements and need 2-byte alignment (16-byte for
- * the fast kernels: rows of T = 64 * 2^k <= 8192 go through the bulk-tensor sweep, T % 8 == 0
- * through 16-byte loads, anything else element by element).  Every output element is the fp32
+ * the fast kernels: rows of T = 64 * 2^k <= 8192, and longer rows that are a multiple of 4096, go
+ * through the bulk-tensor sweep, other T % 8 == 0 through 16-byte loads, anything else element by
+ * element).  Every output element is the fp32
  * result rounded to nearest-even once; the running state h is never rounded between steps.
  * ---------------------------------------------------------------------------------- */
 int ssb_scan_fwd_bf16(const void *gate, const void *value, void *out, int64_t rows, int64_t T,
@@ -168,8 +171,9 @@ int ssb_scan_bwd_f16(const void *gate, const void *h, const void *gout, void *gg
                      int64_t rows, int64_t T, const float *c_in, const float *h_prev, void *stream);
 /* The fused forms on 16-bit tensors: gate logits in (as ssb_scan_sigmoid_*_f32) and the backward
  * that recomputes h from (gate, value) (as ssb_scan_bwd_recompute_f32, no workspace).  Rows of
- * T = 64 * 2^k <= 8192 and 16-byte aligned tensors only; SSB_ERR_UNSUPPORTED otherwise (compose
- * them from the plain entry points).  The recomputed h is the fp32 one, not its 16-bit rounding. */
+ * T = 64 * 2^k <= 8192 (the sigmoid forms also take longer rows that are a multiple of 4096) and
+ * 16-byte aligned tensors only; SSB_ERR_UNSUPPORTED otherwise (compose them from the plain entry
+ * points).  The recomputed h is the fp32 one, not its 16-bit rounding. */
 int ssb_scan_sigmoid_fwd_bf16(const void *gate_logits, const void *value, void *out, int64_t rows,
                               int64_t T, const float *h_in, void *stream);
 int ssb_scan_sigmoid_bwd_bf16(const void *gate_logits, const void *h, const void *gout, void *glogits,

@@ -63,13 +63,21 @@ __device__ __forceinline__ uint32_t unit_chunk_offset(int t, int j) {
 // h; the kernel rebuilds h for the span with a forward scan of (a, b) -- both scans share the one
 // barrier -- so a caller need not keep h between the passes.  carry_b is then the h entering each
 // row (the forward's h_in).
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float>
+// LONG: rows longer than a span (T a multiple of the span's 32*threads elements).  A span is then one
+// piece of one row (the tensor maps' boxes are {line, LINES, 1}); a CTA walks the `pieces` pieces of a
+// row one after the other -- forward from the first, backward from the last -- and hands the state
+// from piece to piece through one float in shared memory, using the row-start / row-end carry
+// mechanism of the short-row case.  The backward's h just before a piece comes from `h_rows`.
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float,
+          bool LONG = false>
 __global__ void __launch_bounds__(LINES * (4 / (int)sizeof(IO)))
 tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                 const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
                 const __grid_constant__ CUtensorMap map_out2, int64_t rows, int lines_per_row,
                 const float *__restrict__ carry_a,   // fwd: h_in | bwd: c_in
-                const float *__restrict__ carry_b) { // bwd: h_prev
+                const float *__restrict__ carry_b,   // bwd: h_prev
+                int pieces,                          // LONG: spans per row (1 otherwise)
+                const IO *__restrict__ h_rows) {     // LONG backward: the h tensor (NULL otherwise)
     using Cfg = Config<LINES, STAGES, OUTBUF, BWD, IO>;
     constexpr int N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT, TILE = Cfg::TILE, NW = Cfg::THREADS / 32;
     constexpr bool F32 = sizeof(IO) == 4;
@@ -79,14 +87,20 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     __shared__ float2 s_tot[2][NW];
     __shared__ float2 s_fwd[RECOMPUTE ? 2 : 1][NW];  // RECOMPUTE: the forward scan's warp totals
     static_assert(BWD || !RECOMPUTE, "only the backward recomputes");
+    static_assert(!(LONG && RECOMPUTE), "recomputing h needs the row inside one span");
+    __shared__ float s_chain;  // LONG: the state handed from one piece of a row to the next
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t smem0 = (tma::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t out_base = smem0 + STAGES * N_IN * TILE;
     const uint32_t bar0 = tma::smem_u32(&full_bar[0]);
-    const int rows_per_span = Cfg::THREADS / lines_per_row;  // lines_per_row: 32-element units per row
-    const int64_t n_spans = (rows + rows_per_span - 1) / rows_per_span;
-    const int64_t my_spans = (int64_t)blockIdx.x < n_spans ? (n_spans - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int rows_per_span = Cfg::THREADS / lines_per_row;  // lines_per_row: 32-element units per row (LONG: per piece)
+    const int64_t n_spans = LONG ? rows : (rows + rows_per_span - 1) / rows_per_span;  // LONG: counted in rows here
+    const int64_t my_spans = ((int64_t)blockIdx.x < n_spans ? (n_spans - blockIdx.x + gridDim.x - 1) / gridDim.x : 0) *
+                             (LONG ? pieces : 1);
+    // LONG: item i of this CTA is piece i % pieces (counted from the end, backward) of row blockIdx.x + (i / pieces) * gridDim.x
+    auto long_row = [&](int64_t i) { return blockIdx.x + (i / pieces) * (int64_t)gridDim.x; };
+    auto long_piece = [&](int64_t i) { return BWD ? pieces - 1 - (int)(i % pieces) : (int)(i % pieces); };
     // line of this thread inside its row, and whether it starts / ends a row
     const int line_in_row = tid & (lines_per_row - 1);  // lines_per_row is a power of two
     const bool row_start = line_in_row == 0, row_end = line_in_row == lines_per_row - 1;
@@ -95,12 +109,13 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     auto issue = [&](int64_t i) {  // thread 0: loads of this CTA's i-th span into stage i % STAGES
         const int stage = (int)(i % STAGES);
         const int64_t span = blockIdx.x + i * (int64_t)gridDim.x;
-        const int row0 = (int)(span * rows_per_span);
+        const int row0 = LONG ? (int)long_row(i) : (int)(span * rows_per_span);
+        const int line0 = LONG ? long_piece(i) * LINES : 0;
         const uint32_t bar = bar0 + 8 * stage, dst = smem0 + stage * N_IN * TILE;
         tma::mbar_expect_tx(bar, N_IN * TILE);
-        tma::load_box(dst, &map_gate, 0, 0, row0, bar);
-        tma::load_box(dst + TILE, &map_in1, 0, 0, row0, bar);
-        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, 0, 0, row0, bar);
+        tma::load_box(dst, &map_gate, 0, line0, row0, bar);
+        tma::load_box(dst + TILE, &map_in1, 0, line0, row0, bar);
+        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, 0, line0, row0, bar);
     };
 
     if (tid == 0) {
@@ -120,8 +135,14 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     for (int64_t i = 0; i < my_spans; i++) {
         const int stage = (int)(i % STAGES);
         const int64_t span = blockIdx.x + i * (int64_t)gridDim.x;
-        const int64_t row = span * rows_per_span + row_in_span;
+        const int64_t row = LONG ? long_row(i) : span * rows_per_span + row_in_span;
+        const int piece = LONG ? long_piece(i) : 0;
+        const bool first_piece = !LONG || i % pieces == 0;  // of the row, in processing order
         const uint32_t in0 = smem0 + stage * N_IN * TILE;
+        // LONG backward: h just before the piece, for thread 0 (issued before the wait to overlap with it)
+        float h_before_piece = 0.f;
+        if (LONG && BWD && tid == 0 && piece > 0)
+            h_before_piece = widen<float, IO>(h_rows[row * ((int64_t)pieces * Cfg::THREADS * 32) + (int64_t)piece * Cfg::THREADS * 32 - 1]);
         if (!tma::mbar_wait_bounded(bar0 + 8 * stage, (phase_bits >> stage) & 1u)) timed_out = true;
         phase_bits ^= 1u << stage;
 
@@ -165,7 +186,8 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         float h_left = 0.f;  // backward: h just before this line's first element
         if (BWD) {
             if (row_start) {
-                if (carry_b != nullptr && row < rows) h_left = carry_b[row];
+                if (LONG && piece > 0) h_left = h_before_piece;
+                else if (carry_b != nullptr && row < rows) h_left = carry_b[row];
             } else if (!RECOMPUTE) {
                 if constexpr (F32) {
                     h_left = tma::lds32(in0 + TILE + chunk_offset(tid - 1, 7) + 12);
@@ -179,13 +201,15 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
         // Row boundaries and caller-supplied carries.
         if (!BWD) {
             if (row_start) {
-                if (carry_a != nullptr && row < rows) x[0] = fmaf(a[0], carry_a[row], x[0]);
+                if (!first_piece) x[0] = fmaf(a[0], s_chain, x[0]);
+                else if (carry_a != nullptr && row < rows) x[0] = fmaf(a[0], carry_a[row], x[0]);
                 a[0] = 0.f;
             }
         } else {
             if (RECOMPUTE && row_start) x[0] = fmaf(a[0], h_left, x[0]);
             if (row_start) a[0] = 0.f;
-            if (row_end && carry_a != nullptr && row < rows) y[31] += carry_a[row];
+            if (row_end && !first_piece) y[31] += s_chain;
+            else if (row_end && carry_a != nullptr && row < rows) y[31] += carry_a[row];
             if (row >= rows) {  // rows past the end arrive as zeros; keep them inert
 #pragma unroll
                 for (int k = 0; k < 32; k++) a[k] = 0.f;
@@ -250,7 +274,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
 #pragma unroll
                 for (int k = 31; k >= 0; k--) {
                     const float gb = y[k] + s, ak = (k == 0) ? a_first : a[k];
-                    s = a[k] * gb;
+                    s = (LONG && k == 0 ? a_first : a[k]) * gb;
                     y[k] = gb;
                     a[k] = gb * (k > 0 ? x[k > 0 ? k - 1 : 0] : h_left);
                     if (SIGMOID) a[k] *= ak * (1.f - ak);
@@ -292,6 +316,7 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
                 gb = y[4 * j + 2] + s; s = a[4 * j + 2] * gb; og.z = gb; oa.z = gb * x[4 * j + 1];
                 gb = y[4 * j + 1] + s; s = a[4 * j + 1] * gb; og.y = gb; oa.y = gb * x[4 * j];
                 gb = y[4 * j] + s; s = a[4 * j] * gb; og.x = gb;
+                if (LONG && j == 0) s = a_first * gb;  // what leaves the piece towards the one before it
                 oa.x = gb * (j > 0 ? x[j > 0 ? 4 * j - 1 : 0] : h_left);
                 if (SIGMOID) {  // d sigmoid(z) / dz = a (1 - a)
                     const float a0 = j > 0 ? a[4 * j] : a_first;
@@ -304,12 +329,14 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
                 tma::sts128(ob + TILE + off[j], og);
             }
         }
+        if (LONG && tid == (BWD ? 0 : Cfg::THREADS - 1)) s_chain = s;  // read by the next piece after the barrier below
         tma::fence_async_smem();
         __syncthreads();
         if (tid == 0) {
-            const int row0 = (int)(span * rows_per_span);
-            tma::store_box(&map_out1, 0, 0, row0, ob);
-            if (BWD) tma::store_box(&map_out2, 0, 0, row0, ob + TILE);
+            const int row0 = LONG ? (int)row : (int)(span * rows_per_span);
+            const int line0 = LONG ? piece * LINES : 0;
+            tma::store_box(&map_out1, 0, line0, row0, ob);
+            if (BWD) tma::store_box(&map_out2, 0, line0, row0, ob + TILE);
             tma::store_commit();
         }
         out_slot = (out_slot + 1 == OUTBUF) ? 0 : out_slot + 1;

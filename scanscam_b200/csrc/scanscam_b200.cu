@@ -476,6 +476,7 @@ int launch_span_maps(const float *gate, const float *in1, float *agg, int64_t ro
     X(4, 128, 2, 1, 64, 2, 1) X(5, 256, 2, 1, 128, 3, 1) X(6, 32, 4, 2, 32, 4, 2)
 
 // `elem_bytes`: 4 (fp32) or 2 (bf16 / fp16 storage); a 128-byte line holds 128 / elem_bytes elements.
+constexpr int kTmaFlatLongId = 48;  // TMA family tuning id: the flat sweep over rows of several 4096-element spans
 bool tmaflat_eligible(int64_t rows, int64_t T, int lines, int elem_bytes = 4) {
     const int per_line = 128 / elem_bytes;
     if (T % per_line != 0 || rows > 0x7fffffffLL) return false;
@@ -507,24 +508,51 @@ int make_span_map(CUtensorMap *map, const IO *ptr, int64_t rows, int64_t T, int 
 
 template <typename T> struct as_given { using type = T; };  // keeps a parameter out of template deduction
 
-template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float>
+// The same view with boxes of `lines` lines of one row (rows longer than a span).
+template <typename IO>
+int make_long_map(CUtensorMap *map, const IO *ptr, int64_t rows, int64_t T, int lines) {
+    PFN_cuTensorMapEncodeTiled_v12000 enc = encode_fn();
+    if (enc == nullptr) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from this driver");
+    constexpr int per_line = 128 / (int)sizeof(IO);
+    cuuint64_t dims[3] = {(cuuint64_t)per_line, (cuuint64_t)(T / per_line), (cuuint64_t)rows};
+    cuuint64_t strides[2] = {128, (cuuint64_t)T * sizeof(IO)};
+    cuuint32_t box[3] = {(cuuint32_t)per_line, (cuuint32_t)lines, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_tiled(enc, map, tensor_map_type<IO>(), 3, const_cast<IO *>(ptr), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SSB_ERR_LAUNCH, "cuTensorMapEncodeTiled(long rows) failed with CUresult %d", (int)r);
+    return SSB_OK;
+}
+
+// LONG: rows of a whole number of spans (T % (LINES * 128 / sizeof(IO)) == 0, more than one span):
+// a CTA walks a row span by span and chains the state through shared memory.
+template <int LINES, int STAGES, int OUTBUF, bool BWD, bool SIGMOID = false, bool RECOMPUTE = false, typename IO = float,
+          bool LONG = false>
 int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::type *in2, IO *out1,
                    typename as_given<IO>::type *out2, int64_t rows,
                    int64_t T, const float *carry_a, const float *carry_b, cudaStream_t st) {
     using Cfg = ssb::tmaflat::Config<LINES, STAGES, OUTBUF, BWD, IO>;
     static_assert(STAGES >= 2, "the ring needs a stage to refill while another is consumed");
     constexpr int per_line = 128 / (int)sizeof(IO);
-    if (!tmaflat_eligible(rows, T, LINES, (int)sizeof(IO)))
+    constexpr int64_t span_elems = (int64_t)LINES * per_line;
+    if (LONG) {
+        if (T % span_elems != 0 || T / span_elems < 2 || T / span_elems > 0x7fffffffLL || rows > 0x7fffffffLL)
+            return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep over long rows needs T to be a multiple (>= 2) of %lld (T=%lld)",
+                        (long long)span_elems, (long long)T);
+    } else if (!tmaflat_eligible(rows, T, LINES, (int)sizeof(IO))) {
         return fail(SSB_ERR_UNSUPPORTED, "the TMA flat sweep needs T = %d * 2^k <= %d (T=%lld)", per_line, LINES * per_line, (long long)T);
-    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID, RECOMPUTE, IO>;
+    }
+    auto kern = ssb::tmaflat::tma_flat_kernel<LINES, STAGES, OUTBUF, BWD, SIGMOID, RECOMPUTE, IO, LONG>;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
-    if ((rc = make_span_map(&mg, gate, rows, T, LINES)) != SSB_OK) return rc;
-    if ((rc = make_span_map(&m1, in1, rows, T, LINES)) != SSB_OK) return rc;
-    if ((rc = make_span_map(&mo1, out1, rows, T, LINES)) != SSB_OK) return rc;
+    auto make = [&](CUtensorMap *m, const IO *p) { return LONG ? make_long_map<IO>(m, p, rows, T, LINES) : make_span_map(m, p, rows, T, LINES); };
+    if ((rc = make(&mg, gate)) != SSB_OK) return rc;
+    if ((rc = make(&m1, in1)) != SSB_OK) return rc;
+    if ((rc = make(&mo1, out1)) != SSB_OK) return rc;
     if (BWD) {
-        if ((rc = make_span_map(&m2, in2, rows, T, LINES)) != SSB_OK) return rc;
-        if ((rc = make_span_map(&mo2, out2, rows, T, LINES)) != SSB_OK) return rc;
+        if ((rc = make(&m2, in2)) != SSB_OK) return rc;
+        if ((rc = make(&mo2, out2)) != SSB_OK) return rc;
     } else {  // the forward never touches them: any valid descriptor will do
         m2 = m1;
         mo2 = mo1;
@@ -540,11 +568,13 @@ int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::t
         }
         cached_occ.store(occ, std::memory_order_relaxed);
     }
-    const int upr = (int)(T / 32);  // 32-element units per row
-    const int64_t spans = (rows + Cfg::THREADS / upr - 1) / (Cfg::THREADS / upr);
+    const int upr = LONG ? Cfg::THREADS : (int)(T / 32);  // 32-element units per row (LONG: per piece)
+    const int64_t spans = LONG ? rows : (rows + Cfg::THREADS / upr - 1) / (Cfg::THREADS / upr);
     const int64_t cap = (int64_t)sm_count() * occ;
     const int grid = (int)(spans < cap ? spans : cap);
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b);
+    const int pieces = LONG ? (int)(T / span_elems) : 1;
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b, pieces,
+                                                      (LONG && BWD) ? in1 : nullptr);
     return check_launch("tma_flat_kernel");
 }
 
@@ -697,6 +727,8 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
         case SSB_VARIANT_TMA:
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA forward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            if (tuning_of(variant) == kTmaFlatLongId)
+                return launch_tmaflat<128, 2, 2, false, false, false, float, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
             if (tuning_of(variant) >= 32) {
                 switch (tuning_of(variant) - 32) {
 #define X(ID, FL, FS, FO, BL, BS, BO) case ID: return launch_tmaflat<FL, FS, FO, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
@@ -831,6 +863,8 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
         case SSB_VARIANT_TMA:
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA backward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+            if (tuning_of(variant) == kTmaFlatLongId)
+                return launch_tmaflat<128, 3, 1, true, false, false, float, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
             if (tuning_of(variant) >= 32) {
                 switch (tuning_of(variant) - 32) {
 #define X(ID, FL, FS, FO, BL, BS, BO) case ID: return launch_tmaflat<BL, BS, BO, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
@@ -1014,7 +1048,8 @@ int ssb_scan_bwd_f64_ex(const double *gate, const double *h, const double *gout,
 namespace {
 
 // SIGMOID / RECOMPUTE as in the fp32 entry points; those forms exist on the bulk-tensor sweep only
-// (rows of T = 64 * 2^k <= 8192, 16-byte aligned), other shapes return SSB_ERR_UNSUPPORTED.
+// (rows of T = 64 * 2^k <= 8192, for SIGMOID also larger multiples of 4096; 16-byte aligned), other
+// shapes return SSB_ERR_UNSUPPORTED.
 template <typename IO, bool SIGMOID = false>
 int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows, int64_t T, const float *h_in,
                  void *stream, const char *who) {
@@ -1036,9 +1071,11 @@ int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows
                             : launch_tmaflat<64, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         if (tmaflat_eligible(rows, T, 128, 2))
             return launch_tmaflat<128, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+        if (T % 4096 == 0 && T > 8192)  // longer rows of whole 4096-element spans: a CTA walks the row
+            return launch_tmaflat<64, 2, 2, false, SIGMOID, false, IO, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
     }
     if (SIGMOID)
-        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 and 16-byte aligned tensors (T=%lld)", who, (long long)T);
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 (or, without recomputation, a larger multiple of 4096) and 16-byte aligned tensors (T=%lld)", who, (long long)T);
     const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
     if (al16 && T % 8 == 0)
         ssb::warp_rows_fwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, value, out, rows, T, h_in, nullptr);
@@ -1068,9 +1105,13 @@ int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *gga
             return launch_tmaflat<64, 2, 1, true, SIGMOID, RECOMPUTE, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         if (tmaflat_eligible(rows, T, 128, 2))
             return launch_tmaflat<128, 3, 1, true, SIGMOID, RECOMPUTE, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        if constexpr (!RECOMPUTE) {
+            if (T % 4096 == 0 && T > 8192)
+                return launch_tmaflat<64, 2, 1, true, SIGMOID, false, IO, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
+        }
     }
     if (SIGMOID || RECOMPUTE)
-        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 and 16-byte aligned tensors (T=%lld)", who, (long long)T);
+        return fail(SSB_ERR_UNSUPPORTED, "%s needs T = 64 * 2^k <= 8192 (or, without recomputation, a larger multiple of 4096) and 16-byte aligned tensors (T=%lld)", who, (long long)T);
     const int grid = warp_grid(rows), block = ssb::kWarpKernelWarps * 32;
     if (al16 && T % 8 == 0)
         ssb::warp_rows_bwd_kernel<float, 8, 2, false, IO><<<grid, block, 0, st>>>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, nullptr);

@@ -5,7 +5,7 @@ The reference operator takes ready-made gates (scanscam/op.py:13-21); its users 
 ``gate * (1 - gate)`` after its backward.  Taking the logits directly removes one read and one
 write of a full tensor from each direction (20 -> 12 bytes per element forward, 32 -> 20
 backward).  The fused kernels cover float32 tensors whose last axis is a multiple of 4 and
-bfloat16 / float16 tensors whose last axis is 64 * 2^k <= 8192; other inputs are served by
+bfloat16 / float16 tensors whose last axis is 64 * 2^k <= 8192 or a larger multiple of 4096; other inputs are served by
 ``scan(torch.sigmoid(logits), value)``, i.e. the same operator unfused.
 """
 from __future__ import annotations
@@ -19,8 +19,13 @@ from .op import is_transpose_contig, scan
 
 
 def sweep_row_16bit(steps: int) -> bool:
-    """Row lengths the fused 16-bit kernels take: 64 * 2^k up to 8192."""
+    """Row lengths the 16-bit kernels take with the row inside one span: 64 * 2^k up to 8192."""
     return steps % 64 == 0 and steps <= 8192 and (steps // 64) & (steps // 64 - 1) == 0
+
+
+def fused_row_16bit(steps: int) -> bool:
+    """Row lengths the fused-sigmoid 16-bit kernels take: the above, or whole 4096-step spans."""
+    return sweep_row_16bit(steps) or (steps > 8192 and steps % 4096 == 0)
 
 
 def _fusable(*tensors: torch.Tensor) -> bool:
@@ -29,7 +34,7 @@ def _fusable(*tensors: torch.Tensor) -> bool:
         return False
     if t0.dtype == torch.float32:
         return t0.shape[-1] % 4 == 0
-    return t0.dtype in (torch.bfloat16, torch.float16) and sweep_row_16bit(t0.shape[-1])
+    return t0.dtype in (torch.bfloat16, torch.float16) and fused_row_16bit(t0.shape[-1])
 
 
 class ScanSigmoidGate(torch.autograd.Function):

@@ -22,7 +22,7 @@ from . import _native
 from .workloads import WORKLOADS
 
 FLAT_IDS = range(14)                 # SSB_FLAT_CONFIGS in csrc/scanscam_b200.cu
-TMA_IDS = (0, 1, 5, 6, 8, 10)
+TMA_IDS = (0, 1, 5, 6, 8, 10, 32, 33, 36, 37, 48)  # per-warp ring ids; 32.. flat sweep; 48 flat sweep over long rows
 LOOKBACK_IDS = range(7)              # SSB_LOOKBACK_CONFIGS
 
 
