@@ -637,6 +637,13 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 //   * odd T on aligned tensors -> the per-element flat sweep or one warp per row, by length;
 //     unaligned views and fp64 -> one warp per row.
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
+    // Many long rows of whole 4096-element spans: the flat sweep that walks a row span by span wins the
+    // backward at every measured shape from 1024 x 65536 to 16384 x 16384 (+1-7 % over look-back, +0.5-4 %
+    // over the per-warp ring) and the forward from 2048 rows up; at 1024 rows the per-warp ring is the
+    // faster forward.  Neither needs scratch.
+    if (all_aligned16 && rows >= 1024 && T >= 16384 && T % 4096 == 0 && T / 4096 <= 0x7fffffffLL && rows <= 0x7fffffffLL &&
+        encode_fn() != nullptr)
+        return SSB_VARIANT_TMA | ((backward || rows >= 2048 ? kTmaFlatLongId : 1) << 8);
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     // A few very long rows: a row's look-back chain has too few CTAs behind it to hide its latency, and
     // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 4, 16 and
