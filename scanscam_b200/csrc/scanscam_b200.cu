@@ -571,7 +571,11 @@ int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::t
     const int upr = LONG ? Cfg::THREADS : (int)(T / 32);  // 32-element units per row (LONG: per piece)
     const int64_t spans = LONG ? rows : (rows + Cfg::THREADS / upr - 1) / (Cfg::THREADS / upr);
     const int64_t cap = (int64_t)sm_count() * occ;
-    const int grid = (int)(spans < cap ? spans : cap);
+    int grid = (int)(spans < cap ? spans : cap);
+    if (LONG && spans > cap) {  // whole rows per CTA: as few CTAs as give every CTA the same number of rows (+-1)
+        const int64_t per_cta = (spans + cap - 1) / cap;
+        grid = (int)((spans + per_cta - 1) / per_cta);
+    }
     const int pieces = LONG ? (int)(T / span_elems) : 1;
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b, pieces,
                                                       (LONG && BWD) ? in1 : nullptr);
@@ -639,11 +643,11 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, bool workspace_ok = false) {
     // Many long rows of whole 4096-element spans: the flat sweep that walks a row span by span wins the
     // backward at every measured shape from 1024 x 65536 to 16384 x 16384 (+1-7 % over look-back, +0.5-4 %
-    // over the per-warp ring) and the forward from 2048 rows up; at 1024 rows the per-warp ring is the
-    // faster forward.  Neither needs scratch.
-    if (all_aligned16 && rows >= 1024 && T >= 16384 && T % 4096 == 0 && T / 4096 <= 0x7fffffffLL && rows <= 0x7fffffffLL &&
-        encode_fn() != nullptr)
-        return SSB_VARIANT_TMA | ((backward || rows >= 2048 ? kTmaFlatLongId : 1) << 8);
+    // over the per-warp ring) and the forward from 2048 rows up; below that the forward is left to the
+    // rules that follow (per-warp ring for very long rows, look-back otherwise).  It needs no scratch.
+    if (all_aligned16 && rows >= (backward ? 1024 : 2048) && T >= 16384 && T % 4096 == 0 && T / 4096 <= 0x7fffffffLL &&
+        rows <= 0x7fffffffLL && encode_fn() != nullptr)
+        return SSB_VARIANT_TMA | (kTmaFlatLongId << 8);
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     // A few very long rows: a row's look-back chain has too few CTAs behind it to hide its latency, and
     // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 4, 16 and
