@@ -314,6 +314,12 @@ def test_lookback_long_rows(shape, gates):
         if gates != "randn":  # randn gates swing over many orders of magnitude; max-norm is the fair metric there
             assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(gb, gb_ref)
     assert ran >= 3
+    if T % 4096 == 0 and T >= 8192:  # the flat sweep that walks a row span by span, same carries
+        variant = _gpu.tma_variant(48)
+        h = _gpu.fwd(da, db, h_in=dc, variant=variant)
+        ga, gb = _gpu.bwd(da, dh, dg, c_in=dc, h_prev=dc, variant=variant)
+        for got, ref, name in ((h, h_ref, "h"), (gb, gb_ref, "gb"), (ga, ga_ref, "ga")):
+            assert _gpu.max_norm_err(got, ref) < TOL, (shape, gates, "tma48", name)
     _gpu.device_ok()
 
 
