@@ -738,8 +738,8 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
         case SSB_VARIANT_TMA:
             if (!al16 || !tma_eligible(rows, T))
                 return fail(SSB_ERR_UNSUPPORTED, "TMA forward needs T %% 32 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
-            if (tuning_of(variant) == kTmaFlatLongId)
-                return launch_tmaflat<128, 2, 2, false, false, false, float, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+            if (tuning_of(variant) == kTmaFlatLongId)  // four stages, one CTA per SM: every SM carries the same number of rows
+                return launch_tmaflat<128, 4, 2, false, false, false, float, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
             if (tuning_of(variant) >= 32) {
                 switch (tuning_of(variant) - 32) {
 #define X(ID, FL, FS, FO, BL, BS, BO) case ID: return launch_tmaflat<FL, FS, FO, false>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
@@ -1082,7 +1082,12 @@ int scan_fwd_h16(const void *gate_, const void *value_, void *out_, int64_t rows
                             : launch_tmaflat<64, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
         if (tmaflat_eligible(rows, T, 128, 2))
             return launch_tmaflat<128, 2, 2, false, SIGMOID, false, IO>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
-        if (T % 4096 == 0 && T > 8192)  // longer rows of whole 4096-element spans: a CTA walks the row
+        // longer rows of whole spans: a CTA walks the row (8192-element spans, one CTA per SM with a deep
+        // ring, measured 5-25 % ahead of 4096-element spans at four CTAs per SM where both apply)
+        // (not with the sigmoid fused: that needs the four CTAs per SM to hide its arithmetic)
+        if (!SIGMOID && T % 8192 == 0 && T > 8192)
+            return launch_tmaflat<128, 4, 2, false, SIGMOID, false, IO, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
+        if (T % 4096 == 0 && T > 8192)
             return launch_tmaflat<64, 2, 2, false, SIGMOID, false, IO, true>(gate, value, nullptr, out, nullptr, rows, T, h_in, nullptr, st);
     }
     if (SIGMOID)
@@ -1117,6 +1122,8 @@ int scan_bwd_h16(const void *gate_, const void *h_, const void *gout_, void *gga
         if (tmaflat_eligible(rows, T, 128, 2))
             return launch_tmaflat<128, 3, 1, true, SIGMOID, RECOMPUTE, IO>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         if constexpr (!RECOMPUTE) {
+            if (!SIGMOID && T % 8192 == 0 && T > 8192)
+                return launch_tmaflat<128, 3, 1, true, SIGMOID, false, IO, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
             if (T % 4096 == 0 && T > 8192)
                 return launch_tmaflat<64, 2, 1, true, SIGMOID, false, IO, true>(gate, h, gout, ggate, gvalue, rows, T, c_in, h_prev, st);
         }
