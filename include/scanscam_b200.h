@@ -341,6 +341,26 @@ size_t ssb_shard_reduce_workspace_bytes(int64_t rows, int64_t T);
 int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse, int64_t rows,
                         float *carry, void *stream);
 
+/* The same two maps, computed by walking each row from the end that the map depends on most --
+ * the forward map from the shard's last step towards its first, the reverse map from the first
+ * step towards the last -- and stopping as soon as the product of the gates walked so far has
+ * dropped to |A| <= cut.  What was not walked could change B (or D) by at most cut times the
+ * state entering the walked part, i.e. by at most `cut` relative to the largest value of the scan.
+ *   cut = 0 : stop only when the product is exactly zero (a zero gate, or underflow); the result
+ *             equals ssb_shard_reduce_* up to reassociation.
+ *   cut > 0 : e.g. 2^-40; gates in (0, 1) then cost a few thousand steps per row instead of the
+ *             whole shard (8 bytes per element of the walked part only).
+ *   cut < 0 : never stop early.
+ * Rows whose product stays above the cut are walked in full, so the result is within the stated
+ * bound for any gates.  `walked` (optional, device memory, 8-byte aligned) is incremented by the
+ * number of elements read per tensor, for callers that account for the traffic.  No scratch.
+ * T % 4 == 0 and 16-byte aligned tensors run one CTA per row; other shapes fall back to the full
+ * reduction of ssb_shard_reduce_* without scratch. */
+int ssb_shard_map_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows, int64_t T,
+                          float cut, unsigned long long *walked, void *stream);
+int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T,
+                          float cut, unsigned long long *walked, void *stream);
+
 /* Self-test of the bounded-wait machinery: launches one warp that looks back at a record which
  * is never published.  The kernel returns by itself after the poll's time limit (about one
  * second); afterwards ssb_device_status() reports SSB_ERR_DEVICE_WAIT once and the context

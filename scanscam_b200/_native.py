@@ -70,6 +70,8 @@ SIGNATURES = {
     "ssb_shard_reduce_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p, _sz, _p]),
     "ssb_shard_reduce_workspace_bytes": (_sz, [_i64, _i64]),
     "ssb_shard_carry_f32": (_int, [_p, _int, _int, _int, _i64, _p, _p]),
+    "ssb_shard_map_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
+    "ssb_shard_map_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_selftest_wait_timeout": (_int, [_p, _sz, _p]),
     "ssb_device_status": (_int, [ctypes.POINTER(_int)]),
 }

@@ -21,6 +21,7 @@
 #include "scan_flat.cuh"
 #include "scan_flat_any.cuh"
 #include "scan_lookback.cuh"
+#include "scan_shard.cuh"
 #include "scan_tma.cuh"
 #include "scan_tma_flat.cuh"
 #include "scan_warp.cuh"
@@ -1822,6 +1823,50 @@ int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse,
     if (grid > 0x7fffffffLL) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_f32: too many rows");
     ssb::shard_carry_kernel<float><<<(int)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(aggs, n_shards, shard, reverse, rows, carry);
     return check_launch("shard_carry_kernel");
+}
+
+}  // extern "C"
+
+namespace {
+constexpr int kTailThreads = 256, kTailU = 2;  // 2048-element chunks: the walk overshoots the cut by half a chunk on average
+
+template <bool BWD>
+int shard_map(const float *gate, const float *in1, float *agg, int64_t rows, int64_t T, float cut,
+              unsigned long long *walked, void *stream, const char *who) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    if (rows == 0) return SSB_OK;
+    if (!agg || (n > 0 && (!gate || !in1))) return fail(SSB_ERR_BAD_ARG, "%s: NULL pointer", who);
+    if (!aligned_to(gate, 4) || !aligned_to(in1, 4) || !aligned_to(agg, 4) || !aligned_to(walked, 8))
+        return fail(SSB_ERR_ALIGNMENT, "%s: tensors must be 4-byte aligned, the counter 8-byte aligned", who);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (T == 0 || T % 4 != 0 || !aligned_to(gate, 16) || !aligned_to(in1, 16)) {  // full reduction, one warp per row
+        if (walked != nullptr && n > 0) {
+            ssb::shard::add_counter_kernel<<<1, 1, 0, st>>>(walked, (unsigned long long)n);
+            if ((rc = check_launch("add_counter_kernel")) != SSB_OK) return rc;
+        }
+        return BWD ? launch_warp_bwd<float, true>(gate, nullptr, in1, nullptr, nullptr, rows, T, nullptr, nullptr, agg, st)
+                   : launch_warp_fwd<float, true>(gate, in1, nullptr, rows, T, nullptr, agg, st);
+    }
+    auto kern = ssb::shard::tail_map_kernel<kTailThreads, kTailU, BWD>;
+    const int grid = persistent_grid<600000 + (BWD ? 1 : 0)>(kern, kTailThreads, rows);
+    kern<<<grid, kTailThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1), rows,
+                                        T / 4, cut, agg, walked);
+    return check_launch("tail_map_kernel");
+}
+}  // namespace
+
+extern "C" {
+
+int ssb_shard_map_fwd_f32(const float *gate, const float *value, float *agg, int64_t rows, int64_t T, float cut,
+                          unsigned long long *walked, void *stream) {
+    return shard_map<false>(gate, value, agg, rows, T, cut, walked, stream, "ssb_shard_map_fwd_f32");
+}
+
+int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T, float cut,
+                          unsigned long long *walked, void *stream) {
+    return shard_map<true>(gate, gout, agg, rows, T, cut, walked, stream, "ssb_shard_map_bwd_f32");
 }
 
 int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream) {

@@ -404,6 +404,37 @@ void shard_reduce_backward(torch::Tensor gate, torch::Tensor outGrad, torch::Ten
              "shard_reduce_backward");
 }
 
+// Row maps with early termination (see ssb_shard_map_*): `walked`, when given, is a one-element
+// int64 CUDA tensor that accumulates the number of elements read per tensor.
+void shard_map_impl(bool backward, const torch::Tensor &gate, const torch::Tensor &other, torch::Tensor &agg, double cut,
+                    const c10::optional<torch::Tensor> &walked, const char *op) {
+    check_tensor(gate, "gate");
+    TORCH_CHECK(gate.dim() == 2 && gate.scalar_type() == torch::kFloat32, "gate must be 2-D float32");
+    check_same(gate, other, backward ? "outGrad" : "value");
+    check_tensor(agg, "agg");
+    TORCH_CHECK(agg.scalar_type() == torch::kFloat32 && agg.numel() == 2 * gate.size(0), "agg must be float32 [rows, 2]");
+    unsigned long long *counter = nullptr;
+    if (walked.has_value() && walked->defined()) {
+        check_tensor(*walked, "walked");
+        TORCH_CHECK(walked->scalar_type() == torch::kInt64 && walked->numel() == 1 && walked->device() == gate.device(),
+                    "walked must be a one-element int64 tensor on the gate's device");
+        counter = reinterpret_cast<unsigned long long *>(walked->data_ptr<int64_t>());
+    }
+    c10::cuda::CUDAGuard guard(gate.device());
+    auto fn = backward ? ssb_shard_map_bwd_f32 : ssb_shard_map_fwd_f32;
+    raise_on(fn(gate.data_ptr<float>(), other.data_ptr<float>(), agg.data_ptr<float>(), gate.size(0), gate.size(1), (float)cut,
+                counter, current_stream()),
+             op);
+}
+void shard_map_forward(torch::Tensor gate, torch::Tensor value, torch::Tensor agg, double cut,
+                       c10::optional<torch::Tensor> walked) {
+    shard_map_impl(false, gate, value, agg, cut, walked, "shard_map_forward");
+}
+void shard_map_backward(torch::Tensor gate, torch::Tensor outGrad, torch::Tensor agg, double cut,
+                        c10::optional<torch::Tensor> walked) {
+    shard_map_impl(true, gate, outGrad, agg, cut, walked, "shard_map_backward");
+}
+
 void shard_carry(torch::Tensor aggs, int64_t shard, bool reverse, torch::Tensor carry) {
     check_tensor(aggs, "aggs");
     check_tensor(carry, "carry");
@@ -445,6 +476,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           "Fused backward from (gate, value, outGrad): rebuilds the forward's output instead of reading it");
     m.def("shard_reduce_forward", &shard_reduce_forward, "Per-row aggregate map (A, B) of a sequence shard");
     m.def("shard_reduce_backward", &shard_reduce_backward, "Per-row aggregate map (A, D) of the reverse recurrence");
+    m.def("shard_map_forward", &shard_map_forward, "Map (A, B) of a sequence shard, walked from its end until |A| <= cut",
+          py::arg("gate"), py::arg("value"), py::arg("agg"), py::arg("cut") = 0.0, py::arg("walked") = py::none());
+    m.def("shard_map_backward", &shard_map_backward, "Map (A, D) of the reverse recurrence, walked from the shard's start until |A| <= cut",
+          py::arg("gate"), py::arg("outGrad"), py::arg("agg"), py::arg("cut") = 0.0, py::arg("walked") = py::none());
     m.def("shard_carry", &shard_carry, "Fold gathered shard aggregates into the carry entering one shard");
     m.def("device_status", &device_status, "Synchronise and return/clear the device-side status code");
 }

@@ -5,14 +5,21 @@ src/scanscam_cuda.cu:154-167); this module is the multi-GPU extension of the sam
 Rank ``s`` of ``G`` holds the contiguous slice ``[..., s*T/G : (s+1)*T/G]`` of gate and value.
 
 Forward, per rank:
-  1. reduce   -- one pass over the local gate/value produces, per row, the shard's affine map
-                 ``(A, B)``: ``h_end = A*h_start + B``                       (8 bytes per row out)
+  1. map      -- per row, the shard's affine map ``(A, B)``: ``h_end = A*h_start + B``.  It is
+                 folded from the shard's LAST step backwards and the walk stops once the product of
+                 the gates walked so far has dropped to ``|A| <= cut`` (what lies further left can
+                 then change ``B`` by at most ``cut`` relative to the largest value of the scan).
+                 Gates in (0, 1) cost a few thousand steps per row; rows whose product does not
+                 vanish are walked in full, so any gates are handled.         (8 bytes per row out)
   2. exchange -- ``all_gather`` of those ``[rows, 2]`` pairs (the only collective; a few KB)
   3. carry    -- fold the maps of the shards to the left into ``h_in`` for this shard
-  4. scan     -- the ordinary forward kernel started from ``h_in``
-Backward mirrors it from the right with the reverse recurrence ``c_t = a_t*(g_t + c_{t+1})``;
-the ``h`` just left of the shard, needed for ``grad_gate`` at the shard's first step, is the
-forward's ``h_in``.
+  4. scan     -- the ordinary forward kernel started from ``h_in``: the prefix fix-up happens
+                 inside the scan kernel, at the first element of each row, not in a pass of its own
+Backward mirrors it from the right with the reverse recurrence ``c_t = a_t*(g_t + c_{t+1})``
+(its map is folded from the shard's FIRST step forwards); the ``h`` just left of the shard, needed
+for ``grad_gate`` at the shard's first step, is the forward's ``h_in``.
+
+Bytes moved per element and direction: the scan's 12 / 20 plus 8 x (walked fraction of the shard).
 
 The numeric work is delegated to an *ops* object so the exchange logic can be exercised on CPU
 process groups (gloo) with stand-in ops supplied by the tests; the default ops call the CUDA
@@ -27,12 +34,32 @@ import torch.distributed as dist
 
 from . import cuda
 
+#: Default early-termination threshold of the shard maps: error at most 2^-40 (9e-13) of the
+#: largest scan value, far below fp32 rounding.  0.0 stops only at an exactly-zero product.
+DEFAULT_CUT = 2.0 ** -40
+
 
 class CudaShardOps:
     """Local kernels of the sharded scan, backed by the CUDA extension (float32, ``[rows, T]``)."""
 
     @staticmethod
+    def map_forward(gate: torch.Tensor, value: torch.Tensor, cut: float = DEFAULT_CUT,
+                    walked: Optional[torch.Tensor] = None) -> torch.Tensor:
+        agg = torch.empty(gate.shape[0], 2, dtype=gate.dtype, device=gate.device)
+        cuda._ext().shard_map_forward(gate, value, agg, cut, walked)
+        return agg
+
+    @staticmethod
+    def map_backward(gate: torch.Tensor, out_grad: torch.Tensor, cut: float = DEFAULT_CUT,
+                     walked: Optional[torch.Tensor] = None) -> torch.Tensor:
+        agg = torch.empty(gate.shape[0], 2, dtype=gate.dtype, device=gate.device)
+        cuda._ext().shard_map_backward(gate, out_grad, agg, cut, walked)
+        return agg
+
+    @staticmethod
     def reduce_forward(gate: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+        """The full fold of the shard (many CTAs per row through scratch): for a few very long
+        rows whose gate products do not vanish."""
         agg = torch.empty(gate.shape[0], 2, dtype=gate.dtype, device=gate.device)
         cuda._ext().shard_reduce_forward(gate, value, agg)
         return agg
@@ -76,26 +103,30 @@ def _rank(group) -> int:
     return dist.get_rank(group) if dist.is_initialized() else 0
 
 
-def sharded_scan_forward(gate: torch.Tensor, value: torch.Tensor, group=None, ops: Any = CudaShardOps
+def sharded_scan_forward(gate: torch.Tensor, value: torch.Tensor, group=None, ops: Any = CudaShardOps,
+                         cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None
                          ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Forward of this rank's T-slice. ``gate``/``value``: ``[rows, T_local]`` contiguous.
 
-    Returns ``(h_local, h_in)`` where ``h_in`` (``[rows]``) is h just before the slice.
+    Returns ``(h_local, h_in)`` where ``h_in`` (``[rows]``) is h just before the slice.  ``cut``:
+    see the module docstring.  ``walked``: optional one-element int64 tensor on the inputs' device
+    that accumulates how many elements per tensor the map pass read.
     """
     assert gate.shape == value.shape and gate.dim() == 2
     gate, value = gate.contiguous(), value.contiguous()
-    maps = _gather_maps(ops.reduce_forward(gate, value), group)
+    maps = _gather_maps(ops.map_forward(gate, value, cut, walked), group)
     h_in = ops.carry(maps, _rank(group), False)
     return ops.scan_forward(gate, value, h_in), h_in
 
 
 def sharded_scan_backward(gate: torch.Tensor, output: torch.Tensor, out_grad: torch.Tensor,
-                          h_in: torch.Tensor, group=None, ops: Any = CudaShardOps
+                          h_in: torch.Tensor, group=None, ops: Any = CudaShardOps,
+                          cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None
                           ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Backward of this rank's T-slice; ``h_in`` is what :func:`sharded_scan_forward` returned."""
     assert gate.shape == output.shape == out_grad.shape and gate.dim() == 2
     gate, output, out_grad = gate.contiguous(), output.contiguous(), out_grad.contiguous()
-    maps = _gather_maps(ops.reduce_backward(gate, out_grad), group)
+    maps = _gather_maps(ops.map_backward(gate, out_grad, cut, walked), group)
     c_in = ops.carry(maps, _rank(group), True)
     return ops.scan_backward(gate, output, out_grad, c_in, h_in)
 
@@ -104,27 +135,27 @@ class ShardedScan(torch.autograd.Function):
     """Autograd Function over the local slice; gradients stay sharded like the inputs."""
 
     @staticmethod
-    def forward(ctx: Any, gate: torch.Tensor, value: torch.Tensor, group, ops) -> torch.Tensor:
+    def forward(ctx: Any, gate: torch.Tensor, value: torch.Tensor, group, ops, cut: float) -> torch.Tensor:
         rows_shape = gate.shape
         g2, v2 = gate.reshape(-1, rows_shape[-1]), value.reshape(-1, rows_shape[-1])
-        out, h_in = sharded_scan_forward(g2, v2, group, ops)
+        out, h_in = sharded_scan_forward(g2, v2, group, ops, cut)
         ctx.save_for_backward(g2, out, h_in)
-        ctx.group, ctx.ops, ctx.rows_shape = group, ops, rows_shape
+        ctx.group, ctx.ops, ctx.rows_shape, ctx.cut = group, ops, rows_shape, cut
         return out.reshape(rows_shape)
 
     @staticmethod
     def backward(ctx: Any, output_grad: torch.Tensor):
         gate, out, h_in = ctx.saved_tensors
-        gg, gv = sharded_scan_backward(gate, out, output_grad.reshape(gate.shape), h_in, ctx.group, ctx.ops)
-        return gg.reshape(ctx.rows_shape), gv.reshape(ctx.rows_shape), None, None
+        gg, gv = sharded_scan_backward(gate, out, output_grad.reshape(gate.shape), h_in, ctx.group, ctx.ops, ctx.cut)
+        return gg.reshape(ctx.rows_shape), gv.reshape(ctx.rows_shape), None, None, None
 
 
 def scan_sequence_parallel(gate: torch.Tensor, value: torch.Tensor, group: Optional[Any] = None,
-                           ops: Any = CudaShardOps) -> torch.Tensor:
+                           ops: Any = CudaShardOps, cut: float = DEFAULT_CUT) -> torch.Tensor:
     """``scan`` for a sequence sharded along its last axis over ``group`` (default: the world).
 
     Every rank passes its own ``[N, ..., T_local]`` slice (slices in rank order form the full
     sequence) and receives the matching slice of the result.
     """
     assert gate.shape == value.shape and gate.dim() >= 2
-    return ShardedScan.apply(gate, value, group, ops)
+    return ShardedScan.apply(gate, value, group, ops, cut)

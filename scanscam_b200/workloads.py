@@ -52,7 +52,8 @@ def make_inputs(gates: str, shape, seed: int = 0, dtype: torch.dtype = torch.flo
 
     gates: ``sigmoid2`` a = sigmoid(N(0,1)+2) (median 0.88) | ``sigmoid0`` a = sigmoid(N(0,1)) |
     ``nearunit`` a ~ U(0.99, 1), value ~ 0.1*N(0,1) | ``resets`` a = U(0,1) with exact zeros
-    w.p. 0.1 | ``randn`` a ~ N(0,1) (the reference's test inputs: negative and >1 gates).
+    w.p. 0.1 | ``randn`` a ~ N(0,1) (the reference's test inputs: negative and >1 gates) |
+    ``ones`` a = 1 (a plain cumulative sum: the gate product never vanishes).
     """
     gen = torch.Generator().manual_seed(seed)
 
@@ -77,6 +78,9 @@ def make_inputs(gates: str, shape, seed: int = 0, dtype: torch.dtype = torch.flo
         b = randn()
     elif gates == "randn":
         a = randn()
+        b = randn()
+    elif gates == "ones":
+        a = torch.ones(shape, dtype=dtype)
         b = randn()
     else:
         raise ValueError(f"unknown gate distribution {gates!r}")

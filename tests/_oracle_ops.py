@@ -31,6 +31,46 @@ class OracleShardOps:
         return torch.from_numpy(np.stack([A, D], axis=1).astype(a.dtype))
 
     @staticmethod
+    def map_forward(gate, value, cut=0.0, walked=None):
+        """(A, B) folded from the shard's last step backwards; a row stops once |A| <= cut."""
+        a, b = gate.numpy(), value.numpy()
+        A = np.ones(a.shape[0], a.dtype)
+        B = np.zeros(a.shape[0], a.dtype)
+        live = np.ones(a.shape[0], bool)
+        steps = 0
+        for t in range(a.shape[1] - 1, -1, -1):
+            if not live.any():
+                break
+            # prepend element t: h_end = A*(a_t*h + b_t) + B
+            B = np.where(live, A * b[:, t] + B, B)
+            A = np.where(live, A * a[:, t], A)
+            steps += int(live.sum())
+            live &= ~(np.abs(A) <= cut)
+        if walked is not None:
+            walked += steps
+        return torch.from_numpy(np.stack([A, B], axis=1).astype(a.dtype))
+
+    @staticmethod
+    def map_backward(gate, out_grad, cut=0.0, walked=None):
+        """(A, D) of c_t = a_t*(g_t + c_{t+1}) folded from the shard's first step forwards."""
+        a, g = gate.numpy(), out_grad.numpy()
+        A = np.ones(a.shape[0], a.dtype)
+        D = np.zeros(a.shape[0], a.dtype)
+        live = np.ones(a.shape[0], bool)
+        steps = 0
+        for t in range(a.shape[1]):
+            if not live.any():
+                break
+            # append element t: c_first = A*(a_t*(g_t + c)) + D
+            D = np.where(live, (A * a[:, t]) * g[:, t] + D, D)
+            A = np.where(live, A * a[:, t], A)
+            steps += int(live.sum())
+            live &= ~(np.abs(A) <= cut)
+        if walked is not None:
+            walked += steps
+        return torch.from_numpy(np.stack([A, D], axis=1).astype(a.dtype))
+
+    @staticmethod
     def carry(aggs, shard, reverse):
         m = aggs.numpy()
         x = np.zeros(m.shape[1], m.dtype)

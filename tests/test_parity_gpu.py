@@ -278,6 +278,111 @@ def test_virtual_t_shards_on_one_gpu(n_shards):
     _gpu.device_ok()
 
 
+@pytest.mark.parametrize("gates", ["nearunit", "sigmoid2", "randn", "ones", "resets"])
+@pytest.mark.parametrize("shape", [(48, 40960), (3, 2048), (200, 6148), (5, 4098)])
+def test_shard_maps_with_early_termination(gates, shape):
+    """ssb_shard_map_*: cut = 0 (and cut < 0) equals the full reduction; cut = 2^-40 stays within
+    the cut's bound, walks only as far as the gate product needs, and walks everything when the
+    product never vanishes.  (5, 4098): T % 4 != 0, the fallback that always reads the whole shard."""
+    lib = _native.load()
+    rows, T = shape
+    a, b, g = make_inputs(gates, shape, seed=31)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    st = _native.stream_of(da)
+    full = torch.empty(2, rows, 2, device="cuda")
+    _native.check(lib.ssb_shard_reduce_fwd_f32(da.data_ptr(), db.data_ptr(), full[0].data_ptr(), rows, T, None, 0, st))
+    _native.check(lib.ssb_shard_reduce_bwd_f32(da.data_ptr(), dg.data_ptr(), full[1].data_ptr(), rows, T, None, 0, st))
+    full = full.cpu().double().numpy()
+    an = a.double().numpy()
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy())
+    _, gb_ref = oracle.scan_backward(a.numpy(), h_ref, g.numpy())
+    finite = np.isfinite(full).all(axis=(0, 2)) & np.isfinite(h_ref).all(axis=1) & np.isfinite(gb_ref).all(axis=1)
+    scale = [max(float(np.abs(h_ref[finite]).max()), 1e-30),
+             max(float(np.abs(gb_ref[finite]).max() * max(np.abs(an).max(), 1.0)), 1e-30)]
+    for cut in (-1.0, 0.0, 2.0 ** -40):
+        got = torch.empty(2, rows, 2, device="cuda")
+        walked = torch.zeros(2, dtype=torch.int64, device="cuda")
+        _native.check(lib.ssb_shard_map_fwd_f32(da.data_ptr(), db.data_ptr(), got[0].data_ptr(), rows, T, cut,
+                                                walked[0:].data_ptr(), st))
+        _native.check(lib.ssb_shard_map_bwd_f32(da.data_ptr(), dg.data_ptr(), got[1].data_ptr(), rows, T, cut,
+                                                walked[1:].data_ptr(), st))
+        got, walked = got.cpu().double().numpy(), walked.cpu().numpy()
+        for d in range(2):
+            err = np.abs(got[d, finite, 1] - full[d, finite, 1]).max(initial=0.0) / scale[d]
+            assert err <= 2 * max(cut, 0.0) + 1e-5, (d, cut, err)
+            assert (np.abs(got[d, finite, 0]) <= np.maximum(np.abs(full[d, finite, 0]) * 1.01 + 1e-37, max(cut, 0.0))).all()
+        assert (walked <= rows * T).all() and (walked > 0).all()
+        if cut < 0 or gates == "ones" or T % 4 != 0:
+            assert (walked == rows * T).all()  # no early stop: the whole shard is read
+        elif gates == "nearunit" and T >= 40960:
+            # 0.995^t reaches 2^-40 after ~5.5 K steps and zero after ~20.6 K (2048-element chunks)
+            limit = 8192 if cut > 0 else 24576
+            assert (walked <= rows * limit).all(), (cut, walked)
+        elif gates in ("sigmoid2", "resets") and T >= 6148:
+            assert (walked <= rows * 4096).all(), (cut, walked)
+    _gpu.device_ok()
+
+
+@pytest.mark.parametrize("gates,n_shards,cut", [("nearunit", 4, 2.0 ** -40), ("nearunit", 2, 0.0), ("randn", 4, 2.0 ** -40),
+                                                ("ones", 2, 2.0 ** -40), ("sigmoid2", 8, 2.0 ** -40)])
+def test_virtual_t_shards_through_the_sharded_module(gates, n_shards, cut):
+    """scanscam_b200.sharded's own steps (map -> gather -> carry -> scan) with the CUDA ops, the
+    gather replaced by stacking the shards' maps on one device; result vs. the unsharded oracle."""
+    from scanscam_b200 import sharded
+
+    ops = sharded.CudaShardOps
+    rows, step = 40, 24576 if gates == "nearunit" else 4096
+    T = step * n_shards
+    a, b, g = make_inputs(gates, (rows, T), seed=5)
+    if gates == "ones":
+        b, g = b * 0.01, g * 0.01  # keep the running sums small against fp32 cancellation
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    parts = [[x[:, s * step:(s + 1) * step].contiguous() for x in (da, db, dg)] for s in range(n_shards)]
+    fmaps = torch.stack([ops.map_forward(pa, pb, cut) for pa, pb, _ in parts])
+    bmaps = torch.stack([ops.map_backward(pa, pg, cut) for pa, _, pg in parts])
+    hs, gas, gbs = [], [], []
+    for s, (pa, pb, pg) in enumerate(parts):
+        h_in, c_in = ops.carry(fmaps, s, False), ops.carry(bmaps, s, True)
+        h = ops.scan_forward(pa, pb, h_in)
+        ga, gb = ops.scan_backward(pa, h, pg, c_in, h_in)
+        hs.append(h), gas.append(ga), gbs.append(gb)
+    assert _gpu.max_norm_err(torch.cat(hs, 1), h_ref) < TOL
+    assert _gpu.max_norm_err(torch.cat(gbs, 1), gb_ref) < TOL
+    assert _gpu.max_norm_err(torch.cat(gas, 1), ga_ref) < TOL
+    _gpu.device_ok()
+
+
+def test_cfg3_full_size_under_auto_sampled():
+    """cfg3 as configured -- [1024, 2^20], near-unit gates, the kernels AUTO picks at that size --
+    at full size on the GPU; a strided sample of 16 rows against the oracle, the backward fed with
+    the oracle's h (isolates it) and with the kernel's own h (end to end)."""
+    w = WORKLOADS["cfg3"]
+    rows, T = w.rows, w.steps
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    da = torch.rand(rows, T, generator=gen, device="cuda").mul_(0.01).add_(0.99)
+    db = torch.randn(rows, T, generator=gen, device="cuda").mul_(0.1)
+    dg = torch.randn(rows, T, generator=gen, device="cuda")
+    lib = _native.load()
+    v_f, v_b = lib.ssb_scan_recommend(rows, T, 0, 1, 1), lib.ssb_scan_recommend(rows, T, 1, 1, 1)
+    h = _gpu.fwd(da, db, variant=v_f)
+    ga, gb = _gpu.bwd(da, h, dg, variant=v_b)
+    idx = torch.arange(5, rows, 64, device="cuda")  # 16 rows
+    assert idx.numel() == 16
+    sa, sb, sg = (x[idx].contiguous() for x in (da, db, dg))
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(sa.cpu(), sb.cpu(), sg.cpu())
+    assert _gpu.max_norm_err(h[idx], h_ref) < TOL
+    assert _gpu.max_norm_err(gb[idx], gb_ref) < TOL and _gpu.max_norm_err(ga[idx], ga_ref) < TOL
+    del ga, gb
+    dh = torch.empty_like(h)
+    dh.copy_(h)
+    dh[idx] = dev(h_ref)  # the sampled rows get the oracle's h
+    del h
+    ga2, gb2 = _gpu.bwd(da, dh, dg, variant=v_b)
+    assert _gpu.max_norm_err(gb2[idx], gb_ref) < TOL and _gpu.max_norm_err(ga2[idx], ga_ref) < TOL
+    _gpu.device_ok()
+
+
 # ---- long rows: spans of one row on different CTAs, carries by decoupled look-back ----------
 LONG_SHAPES = [(3, 8192), (1, 1048576), (5, 40000), (64, 16384), (700, 8196), (2, 4100), (17, 262144)]
 

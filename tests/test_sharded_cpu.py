@@ -25,7 +25,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, gates, rows, steps, out_dir):
+def _worker(rank, world, port, gates, rows, steps, out_dir, cut=sharded.DEFAULT_CUT):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -33,17 +33,21 @@ def _worker(rank, world, port, gates, rows, steps, out_dir):
         lo, hi = rank * steps // world, (rank + 1) * steps // world
         a_l = a[:, lo:hi].contiguous().requires_grad_(True)
         b_l = b[:, lo:hi].contiguous().requires_grad_(True)
-        h_l = sharded.scan_sequence_parallel(a_l, b_l, None, OracleShardOps)
+        h_l = sharded.scan_sequence_parallel(a_l, b_l, None, OracleShardOps, cut)
         h_l.backward(g[:, lo:hi].contiguous())
         torch.save({"h": h_l.detach(), "ga": a_l.grad, "gb": b_l.grad}, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,gates", [(2, "sigmoid2"), (3, "randn"), (2, "resets")])
-def test_sequence_parallel_scan_on_gloo(tmp_path, world, gates):
-    rows, steps = 6, 96
-    mp.spawn(_worker, args=(world, _free_port(), gates, rows, steps, str(tmp_path)), nprocs=world, join=True)
+@pytest.mark.parametrize("world,gates,steps,cut", [(2, "sigmoid2", 96, sharded.DEFAULT_CUT), (3, "randn", 96, 0.0),
+                                                   (2, "resets", 96, 0.0), (2, "ones", 96, sharded.DEFAULT_CUT),
+                                                   (2, "sigmoid2", 1200, sharded.DEFAULT_CUT), (3, "randn", 300, sharded.DEFAULT_CUT)])
+def test_sequence_parallel_scan_on_gloo(tmp_path, world, gates, steps, cut):
+    """Gates whose products vanish inside a shard (sigmoid2 over 600 steps, randn), gates whose
+    products never do (ones), exact zeros (resets); with the default cut and with cut = 0."""
+    rows = 6
+    mp.spawn(_worker, args=(world, _free_port(), gates, rows, steps, str(tmp_path), cut), nprocs=world, join=True)
     parts = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     h = torch.cat([p["h"] for p in parts], dim=1).numpy()
     ga = torch.cat([p["ga"] for p in parts], dim=1).numpy()
@@ -86,3 +90,29 @@ def test_virtual_shards_compose_to_the_unsharded_result(n_shards):
                                               g[:, sl[s]].contiguous(), c_in, h_in)
         np.testing.assert_allclose(gb.numpy(), gb_ref[:, sl[s]], rtol=2e-6, atol=1e-5)
         np.testing.assert_allclose(ga.numpy(), ga_ref[:, sl[s]], rtol=2e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("gates", ["sigmoid2", "nearunit", "randn", "ones", "resets"])
+def test_early_terminated_maps_stay_within_the_cut(gates):
+    """map_* with cut = 0 equals the full fold; with cut > 0 it stops early on vanishing products and
+    differs from the full fold by at most cut x (largest state), and it reads fewer elements."""
+    rows, steps = 5, 3000
+    a, b, g = make_inputs(gates, (rows, steps), seed=7)
+    full_f, full_b = OracleShardOps.reduce_forward(a, b).numpy(), OracleShardOps.reduce_backward(a, g).numpy()
+    for cut in (0.0, 2.0 ** -40, 1e-3):
+        wf, wb = np.zeros(1, np.int64), np.zeros(1, np.int64)
+        mf = OracleShardOps.map_forward(a, b, cut, wf).numpy()
+        mb = OracleShardOps.map_backward(a, g, cut, wb).numpy()
+        h = oracle.scan_forward(a.numpy(), b.numpy())
+        scale_h = np.abs(h).max()
+        ga, gb = oracle.scan_backward(a.numpy(), h, g.numpy())
+        scale_c = max(np.abs(gb).max(), 1.0) * max(np.abs(a.numpy()).max(), 1.0)
+        finite = np.isfinite(full_f).all(axis=1) & np.isfinite(full_b).all(axis=1)  # randn gates can overflow
+        tol = 2 * cut + 2e-6  # the cut's bound plus fp32 reassociation
+        assert (np.abs(mf[finite, 1] - full_f[finite, 1]) <= tol * scale_h + 1e-6 * np.abs(full_f[finite, 1])).all()
+        assert (np.abs(mb[finite, 1] - full_b[finite, 1]) <= tol * scale_c + 1e-6 * np.abs(full_b[finite, 1])).all()
+        assert (np.abs(mf[finite, 0]) <= np.maximum(np.abs(full_f[finite, 0]) * 1.001, cut)).all()
+        if gates in ("sigmoid2", "resets") and cut > 0:
+            assert wf[0] < rows * steps // 4 and wb[0] < rows * steps // 4  # products vanish within a few hundred steps
+        if gates == "ones":
+            assert wf[0] == rows * steps and wb[0] == rows * steps  # never vanishes: the whole shard is walked
