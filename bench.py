@@ -80,6 +80,9 @@ def parse_args():
     p.add_argument("--no-weak", action="store_true", help="N > 1: skip the weak-scaling measurement")
     p.add_argument("--ts-steps", type=int, default=6, help="timed steps of the T-sharded measurement")
     p.add_argument("--cut", type=float, default=None, help="early-termination threshold of the shard maps (default: the library's)")
+    p.add_argument("--sets", type=int, default=0,
+                   help="independent buffer sets the timed steps rotate over (0 = as many as keep the L2 from serving re-reads; "
+                        "1 = one set, i.e. L2-resident when the workload fits)")
     p.add_argument("--pcie-probe", action="store_true")
     return p.parse_args()
 
@@ -666,7 +669,7 @@ def run_gpu_arm(args, workload):
     n_local = rows_local * T
     elem = 4 if args.storage == "f32" else 2
     working_set = 6 * n_local * elem
-    sets = 1 if working_set >= 8 * L2_BYTES else min(8, max(4, math.ceil(8 * L2_BYTES / working_set)))
+    sets = args.sets or (1 if working_set >= 8 * L2_BYTES else min(8, max(4, math.ceil(8 * L2_BYTES / working_set))))
     problem = RowsProblem(lib, _native, torch, *mine_cpu, args.storage, sets, args.variant, args.variant_bwd)
     sampler.start()
     ms_per_step, repeats, launch = measure_rows(args, torch, timer, problem, args.steps, args.min_region_ms,
@@ -680,7 +683,8 @@ def run_gpu_arm(args, workload):
         "per_gpu": {"rows": rows_local, "elements": n_local, "working_set_bytes": working_set, "buffer_sets": sets,
                     "l2": (f"{sets} independent buffer sets in rotation ({sets * working_set >> 20} MiB) so that no step re-reads "
                            "what the previous one left in the 126 MB L2") if sets > 1 else
-                          "one buffer set: every pass streams far more than the 126 MB L2"},
+                          ("one buffer set: every pass streams far more than the 126 MB L2" if working_set > 2 * L2_BYTES else
+                           "one buffer set that fits the 126 MB L2: an L2-resident measurement")},
         "kernels": {"forward": problem.v_fwd, "backward": problem.v_bwd, "workspace_bytes": problem.ws_bytes},
         "gpu_launches": 2 * args.steps * world,
         "clocks": sampler.summary("NVML samples every 20 ms during the timed region" +

@@ -77,8 +77,10 @@ int ssb_scan_fwd_f32(const float *gate, const float *value, float *out, int64_t 
                      const float *h_in, void *stream);
 int ssb_scan_fwd_f64(const double *gate, const double *value, double *out, int64_t rows,
                      int64_t T, const double *h_in, void *stream);
-/* Same, with the kernel family pinned and an optional workspace (only
- * SSB_VARIANT_LOOKBACK needs one). */
+/* Same, with the kernel family pinned and an optional workspace (only SSB_VARIANT_LOOKBACK needs
+ * one).  With SSB_VARIANT_AUTO the entry point makes the choice ssb_scan_recommend reports for
+ * can_provide_workspace = 1 when `workspace` is 256-byte aligned and holds at least
+ * ssb_scan_workspace_bytes() of that choice, and otherwise the choice made without scratch. */
 int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t rows,
                         int64_t T, const float *h_in, int variant, void *workspace,
                         size_t workspace_bytes, void *stream);
@@ -256,7 +258,8 @@ int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout,
  * reference).  The streaming kernels with 64-channel blocks; C % 8 == 0 and 16-byte aligned
  * tensors, SSB_ERR_UNSUPPORTED otherwise.  `workspace` (ssb_scan_cl_h16_workspace_bytes, 256-byte
  * aligned, may be NULL) lets shapes with fewer than 96 (batch element, 64-channel block) pairs and
- * T >= 2048 run in the two-pass chunked form; without it one CTA walks all of T per pair. */
+ * T >= 2048 run in the two-pass chunked form; without it one CTA walks all of T per pair.  The
+ * query returns 0 for shapes that never use scratch. */
 size_t ssb_scan_cl_h16_workspace_bytes(int64_t N, int64_t T, int64_t C);
 int ssb_scan_cl_fwd_bf16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C,
                          void *workspace, size_t workspace_bytes, void *stream);
@@ -271,10 +274,11 @@ int ssb_scan_cl_bwd_f16(const void *gate, const void *h, const void *gout, void 
 
 /* Channels-last with gate logits in (sigmoid fused, as ssb_scan_sigmoid_*; no counterpart in the
  * reference), fp32 (C % 4 == 0) and 16-bit tensors (C % 8 == 0), 16-byte aligned; always the
- * streaming kernels.  `workspace`: ssb_scan_cl_workspace_bytes (fp32) or
- * ssb_scan_cl_h16_workspace_bytes (16-bit) bytes, may be NULL (then shapes with few channel blocks
- * run one CTA per block instead of the two-pass chunked form).  SSB_ERR_UNSUPPORTED for other
- * channel counts or alignments: apply the sigmoid separately. */
+ * streaming kernels.  `workspace`: ssb_scan_cl_sigmoid_workspace_bytes (fp32; 0 for shapes that
+ * never use scratch) or ssb_scan_cl_h16_workspace_bytes (16-bit) bytes, may be NULL (then shapes
+ * with few channel blocks run one CTA per block instead of the two-pass chunked form).
+ * SSB_ERR_UNSUPPORTED for other channel counts or alignments: apply the sigmoid separately. */
+size_t ssb_scan_cl_sigmoid_workspace_bytes(int64_t N, int64_t T, int64_t C);
 int ssb_scan_cl_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t N, int64_t T,
                                 int64_t C, void *workspace, size_t workspace_bytes, void *stream);
 int ssb_scan_cl_sigmoid_bwd_f32(const float *gate_logits, const float *h, const float *gout, float *glogits,
@@ -291,28 +295,44 @@ int ssb_scan_cl_sigmoid_bwd_f16(const void *gate_logits, const void *h, const vo
                                 void *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
                                 size_t workspace_bytes, void *stream);
 
-/* Channels-last with scratch: with scratch the time axis can be split across CTAs (two-pass
- * chunked streaming, or decoupled look-back), so the whole GPU is busy even when N*C is small.
- * `workspace` of ssb_scan_cl_workspace_bytes(N,T,C) bytes, 256-byte aligned, contents irrelevant;
- * NULL / 0 behaves like the plain entry points above, and so do shapes that have enough channel
- * blocks to fill the GPU without splitting T (see the default choice below). */
+/* Channels-last with a selectable kernel family and optional scratch.  With scratch the time axis
+ * can be split across CTAs (two-pass chunked streaming, or decoupled look-back), so the whole GPU
+ * is busy even when N*C is small.  (No counterpart in the reference, whose one kernel per direction
+ * gives a CTA a (batch element, channel block) pair for all of T, src/scanscam_cuda.cu:471-685.)
+ *
+ * `variant` = family | tuning id << 8 | (1 << 16 to force one channel per lane where the family
+ * has a 4-channel form).  SSB_CL_VARIANT_AUTO chooses from the shape and from the scratch it was
+ * given: shapes with at least 96 (batch element, 32-channel block) pairs, T >= 128, C % 4 == 0 and
+ * 16-byte aligned tensors run the streaming kernels, which need no scratch -- the plain entry
+ * points above choose them too; with fewer pairs, T >= 2048 and enough scratch the same kernels run
+ * over chunks of T in two passes; otherwise the look-back kernels when scratch is given and they
+ * are faster, else the plain kernels.  A pinned family that cannot run the shape returns
+ * SSB_ERR_UNSUPPORTED, one that is given too little scratch SSB_ERR_WORKSPACE.  Results do not
+ * depend on the variant beyond fp32 reassociation.  There is no hidden state: every call names its
+ * variant, and concurrent calls need only distinct workspaces. */
+typedef enum ssb_cl_variant {
+    SSB_CL_VARIANT_AUTO = 0,
+    SSB_CL_VARIANT_PLAIN = 1,        /* a CTA walks all of T for 32 channels, lane = channel; any shape, no scratch */
+    SSB_CL_VARIANT_LOOKBACK = 2,     /* tiles of one channel group on different CTAs, decoupled look-back; ids 0..12 */
+    SSB_CL_VARIANT_LOOKBACK_TMA = 3, /* the same on tiles staged by bulk tensor copies; ids 0..5; C % 4 == 0 */
+    SSB_CL_VARIANT_STREAM = 4,       /* a CTA walks all of T, tiles through a bulk-tensor ring; ids 0..7; no scratch */
+    SSB_CL_VARIANT_CHUNKED = 5       /* the streaming kernels over chunks of T in two passes (maps, then scan) */
+} ssb_cl_variant_t;
+
+/* What SSB_CL_VARIANT_AUTO would run for this fp32 problem (`can_provide_workspace` != 0: assume
+ * the caller can supply whatever ssb_scan_cl_variant_workspace_bytes asks for). */
+int ssb_scan_cl_recommend(int64_t N, int64_t T, int64_t C, int backward, int aligned16, int can_provide_workspace);
+/* Scratch that `variant` needs for this problem and direction: 0 for the plain and streaming
+ * kernels, the chunk maps and carries for the chunked form, one record per tile for look-back.
+ * 256-byte aligned; contents need not be initialised. */
+size_t ssb_scan_cl_variant_workspace_bytes(int64_t N, int64_t T, int64_t C, int variant, int backward);
+/* An upper bound of the above over every variant and both directions, for callers that would
+ * rather size one buffer once (it can be a third of a tensor; prefer the per-variant query). */
 size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C);
-/* Tuning knob for sweeps, per calling host thread.  0 = default choice: shapes with at least 96
- * (batch element, 32-channel block) pairs, T >= 128, C % 4 == 0 and 16-byte aligned tensors run
- * the streaming kernels (a CTA walks all of T for its channel block,
- * tiles staged by bulk tensor copies, no scratch -- from the plain entry points too); with fewer
- * pairs, T >= 2048 and scratch the same kernels run over chunks of T in two passes (chunk maps,
- * then the scan from each chunk's entering state); other shapes the look-back kernels when
- * scratch is given and they are faster, else the plain kernels.
- * 0x200 forces the plain kernels in every channels-last fp32 entry point.  Any other id applies to
- * the next ssb_scan_cl_*_ex calls: 1..31 look-back kernels with that tile shape, 32..63 look-back
- * on TMA-staged tiles, 64..71 streaming kernels with that tile shape, 96 the two-pass chunked form.  Returns the previous id.
- * Results do not depend on it beyond fp32 reassociation. */
-int ssb_scan_cl_set_tuning(int tuning);
 int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T,
-                           int64_t C, void *workspace, size_t workspace_bytes, void *stream);
+                           int64_t C, int variant, void *workspace, size_t workspace_bytes, void *stream);
 int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate,
-                           float *gvalue, int64_t N, int64_t T, int64_t C, void *workspace,
+                           float *gvalue, int64_t N, int64_t T, int64_t C, int variant, void *workspace,
                            size_t workspace_bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------

@@ -13,8 +13,10 @@ from __future__ import annotations
 import os
 import sys
 
-# Where the reference checkout is mounted; override with SCANSCAM_REFERENCE_DIR.
-DEFAULT_REFERENCE = os.environ.get("SCANSCAM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+# The reference checkout: SCANSCAM_REFERENCE_DIR if set, else a directory named `reference` beside
+# this repository.
+DEFAULT_REFERENCE = os.environ.get("SCANSCAM_REFERENCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def build_reference(ref_root: str = DEFAULT_REFERENCE, verbose: bool = False) -> str | None:

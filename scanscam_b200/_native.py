@@ -9,10 +9,12 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libscanscam_b200.so")
+# SCANSCAM_B200_LIB selects another build of the same library (e.g. the checked build, see build.py).
+LIB_PATH = os.environ.get("SCANSCAM_B200_LIB") or os.path.join(_HERE, "libscanscam_b200.so")
 
 OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED = range(7)
 VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK, VARIANT_FLAT, VARIANT_FLAT_ANY = range(6)
+CL_AUTO, CL_PLAIN, CL_LOOKBACK, CL_LOOKBACK_TMA, CL_STREAM, CL_CHUNKED = range(6)  # ssb_cl_variant_t
 
 _p, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 
@@ -63,9 +65,11 @@ SIGNATURES = {
     "ssb_scan_cl_bwd_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_fwd_f16": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
     "ssb_scan_cl_bwd_f16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
-    "ssb_scan_cl_set_tuning": (_int, [_int]),
-    "ssb_scan_cl_fwd_f32_ex": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
-    "ssb_scan_cl_bwd_f32_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _sz, _p]),
+    "ssb_scan_cl_recommend": (_int, [_i64, _i64, _i64, _int, _int, _int]),
+    "ssb_scan_cl_variant_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int]),
+    "ssb_scan_cl_sigmoid_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "ssb_scan_cl_fwd_f32_ex": (_int, [_p, _p, _p, _i64, _i64, _i64, _int, _p, _sz, _p]),
+    "ssb_scan_cl_bwd_f32_ex": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _int, _p, _sz, _p]),
     "ssb_shard_reduce_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p, _sz, _p]),
     "ssb_shard_reduce_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, _p, _sz, _p]),
     "ssb_shard_reduce_workspace_bytes": (_sz, [_i64, _i64]),

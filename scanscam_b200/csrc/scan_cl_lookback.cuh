@@ -129,9 +129,10 @@ cl_lookback_kernel(const float *__restrict__ gate, const float *__restrict__ in1
         P early_val;
 #pragma unroll
         for (int v = 0; v < VEC; v++) early_val.v[v] = 0.f;
-        if (warp < seq) {
-            early_flag = ld_acquire_u32(flags + rec - 1 - warp);
+        if (warp < seq) {  // lane 0 acquires, the warp barrier orders the other lanes' record loads after it
+            if (lane == 0) early_flag = ld_acquire_u32(flags + rec - 1 - warp);
             early_flag = __shfl_sync(kFullMask, early_flag, 0);
+            __syncwarp();
             if (early_flag == 2u) early_val = load_record_pack<VEC>(values + (rec - 1 - warp) * (32 * VEC) + lane * VEC);
         }
 

@@ -146,9 +146,10 @@ cl_tma_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constan
         // Early, non-blocking look at the predecessor this segment will read on its first look-back pass.
         unsigned early_flag = 0u;
         float early_val = 0.f;
-        if (seg < seq) {
-            early_flag = cl2::ld_acquire_u32(flags + rec - 1 - seg);
+        if (seg < seq) {  // lane 0 acquires, the warp barrier orders the other lanes' record loads after it
+            if (lane == 0) early_flag = cl2::ld_acquire_u32(flags + rec - 1 - seg);
             early_flag = __shfl_sync(kFullMask, early_flag, 0);
+            __syncwarp();
             if (early_flag == 2u) early_val = ld_relaxed_f32(values + (rec - 1 - seg) * CC + c);
         }
 

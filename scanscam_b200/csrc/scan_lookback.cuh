@@ -11,7 +11,7 @@
 // 1): a span's predecessor is then at most K-1 tickets away or belongs to the previous wave,
 // which keeps the look-back short, and all CTAs stay busy however few rows there are.
 //
-// Per-span record in the workspace: 16 bytes, written and read as one unit (see Record).  A map
+// Per-span record in the workspace: 16 bytes, written and read as one scalar 128-bit unit (see Record).  A map
 // with A == 0 is as good as a prefix (it forgets its input), so exact-zero gates cut the
 // look-back short.  Every poll loop gives up after about a second, reports through the device
 // status word and lets the kernel run to completion.
@@ -24,10 +24,12 @@ namespace lookback {
 
 // One 16-byte record per span: {x, y, flag, unused}.  flag 1: (x, y) = (A, B), the span's own
 // map.  flag 2: x = P, the scan value at the span's end with everything before it applied.
-// A record is written with ONE 16-byte store and read with ONE 16-byte load; like the
-// single-word tile descriptors of the published decoupled look-back scan, this relies on
-// naturally aligned 16-byte accesses being performed as single transactions, so a reader that
-// sees the flag also sees the data stored with it.
+// A record is written with ONE 128-bit store and read with ONE 128-bit load, both of the scalar
+// `.b128` type (PTX ISA 8.3): a scalar access is single-copy atomic, so a reader that sees the
+// flag sees the data stored with it.  (The vector forms `.v4.b32` are, in the memory model, four
+// separate 32-bit accesses and would promise no such thing.)  The flag of a record only ever
+// moves 0 -> 1 -> 2 and every state carries all the data its readers need, so relaxed ordering
+// is enough: nothing else is published through the record.
 struct alignas(16) Record {
     float x, y;
     unsigned flag, unused;
@@ -37,16 +39,23 @@ constexpr unsigned kFlagAgg = 1u, kFlagPrefix = 2u;
 constexpr size_t kHeaderBytes = 256;  // ticket counter, padded
 
 __device__ __forceinline__ Record load_record(const Record *p) {
-    Record r;
-    asm volatile("ld.relaxed.gpu.global.v4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(r.x), "=f"(r.y), "=r"(r.flag), "=r"(r.unused)
+    unsigned long long lo, hi;
+    asm volatile("{\n\t.reg .b128 r;\n\tld.relaxed.gpu.global.b128 r, [%2];\n\tmov.b128 {%0, %1}, r;\n\t}"
+                 : "=l"(lo), "=l"(hi)
                  : "l"(p)
                  : "memory");
+    Record r;
+    r.x = __uint_as_float((unsigned)lo);
+    r.y = __uint_as_float((unsigned)(lo >> 32));
+    r.flag = (unsigned)hi;
+    r.unused = (unsigned)(hi >> 32);
     return r;
 }
 
 __device__ __forceinline__ void store_record(Record *p, float x, float y, unsigned flag) {
-    asm volatile("st.relaxed.gpu.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(x), "f"(y), "r"(flag), "r"(0u)
+    const unsigned long long lo = (unsigned long long)__float_as_uint(x) | ((unsigned long long)__float_as_uint(y) << 32);
+    const unsigned long long hi = (unsigned long long)flag;
+    asm volatile("{\n\t.reg .b128 r;\n\tmov.b128 r, {%1, %2};\n\tst.relaxed.gpu.global.b128 [%0], r;\n\t}" ::"l"(p), "l"(lo), "l"(hi)
                  : "memory");
 }
 

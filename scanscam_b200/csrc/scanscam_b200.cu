@@ -7,6 +7,7 @@
 #include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -627,7 +628,7 @@ int dispatch_tma_bwd(int tuning, const float *gate, const float *h, const float 
 }
 
 // Default kernel choice, from sweeps on B200 over T = 64 .. 16M at 67 MB .. 4 GB per tensor
-// (profiles/kernel_family_sweep_b200.md):
+// (`python -m scanscam_b200.tune` reproduces them):
 //   * aligned fp32, T = 32 * 2^k <= 4096 (every benchmark configuration but the long-context
 //     one) -> the TMA-staged flat sweep: spans of whole rows brought in by bulk tensor copies,
 //     32 elements per thread.  Same speed as the register version below within +-1 % (203-209
@@ -682,11 +683,22 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
     return SSB_VARIANT_WARP;
 }
 
+// SSB_VARIANT_AUTO in the _ex entry points: the choice ssb_scan_recommend(..., can_provide_workspace = 1)
+// reports when the caller's scratch is usable (256-byte aligned and large enough for that choice),
+// else the choice made without scratch.
+int pick_with_scratch(bool backward, int64_t rows, int64_t T, bool all_aligned16, const void *workspace, size_t workspace_bytes) {
+    if (workspace != nullptr && aligned_to(workspace, 256)) {
+        const int v = pick_variant(backward, rows, T, all_aligned16, true);
+        if (family_of(v) != SSB_VARIANT_LOOKBACK || workspace_bytes >= lookback_bytes(rows, T, tuning_of(v))) return v;
+    }
+    return pick_variant(backward, rows, T, all_aligned16, false);
+}
+
 }  // namespace
 
 extern "C" {
 
-int ssb_version(void) { return 100; }
+int ssb_version(void) { return 200; }
 
 const char *ssb_status_string(int status) {
     switch (status) {
@@ -731,7 +743,7 @@ int ssb_scan_fwd_f32_ex(const float *gate, const float *value, float *out, int64
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GridScope grid_scope(grid_per_sm_of(variant));
     const bool al16 = aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16);
-    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(false, rows, T, al16);
+    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_with_scratch(false, rows, T, al16, workspace, workspace_bytes);
     const int family = family_of(variant);
     switch (family) {
         case SSB_VARIANT_WARP:
@@ -867,7 +879,7 @@ int ssb_scan_bwd_f32_ex(const float *gate, const float *h, const float *gout, fl
     const GridScope grid_scope(grid_per_sm_of(variant));
     const bool al16 = aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
                       aligned_to(ggate, 16) && aligned_to(gvalue, 16);
-    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_variant(true, rows, T, al16);
+    if (family_of(variant) == SSB_VARIANT_AUTO) variant = pick_with_scratch(true, rows, T, al16, workspace, workspace_bytes);
     const int family = family_of(variant);
     switch (family) {
         case SSB_VARIANT_WARP:
@@ -1209,8 +1221,6 @@ int check_cl(int64_t N, int64_t T, int64_t C, int64_t *n) {
     X(8, 8, 16, 8) X(9, 4, 8, 4) X(10, 8, 32, 16) X(11, 8, 24, 16)
 constexpr int kCl2MinTile = 8;  // every instantiated tile (W*L) must cover at least this many steps
 
-thread_local int t_cl_tuning = 0;
-
 template <int VEC, int kCl2Warps, int L, bool BWD>
 int launch_cl2(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
                int64_t C, void *workspace, size_t workspace_bytes, cudaStream_t st) {
@@ -1441,8 +1451,9 @@ int cl_bwd(const real *gate, const real *h, const real *gout, real *ggate, real 
 }  // namespace
 
 namespace {
-constexpr int kClChunkedId = 96;      // ssb_scan_cl_set_tuning: the two-pass chunked streaming kernels
-constexpr int kClForcePlain = 0x200;  // ssb_scan_cl_set_tuning: the plain kernels, whatever the shape
+int cl_family_of(int variant) { return variant & 0xff; }
+int cl_tuning_of(int variant) { return (variant >> 8) & 0xff; }
+bool cl_scalar_lanes(int variant) { return ((variant >> 16) & 1) != 0; }
 
 // Channel-block width of the streaming kernels for this shape, or 0 when they do not apply: they
 // need a TMA-describable tensor, rows long enough to fill their 128-256 step tiles, and enough
@@ -1456,37 +1467,12 @@ int cl_stream_block(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
     return 0;
 }
 
-// Too few pairs for the above but long rows and scratch at hand: the same kernels over chunks of T
-// in two passes (measured 1.3-4x the look-back kernels from 2048 steps up).
-bool cl_chunked_applies(int64_t N, int64_t T, int64_t C, bool all_aligned16, const void *workspace, size_t workspace_bytes) {
-    return all_aligned16 && cl3_eligible(N, T, C) && T >= 2048 && encode_fn() != nullptr && workspace != nullptr &&
-           aligned_to(workspace, 256) && workspace_bytes >= cls_chunk_workspace_bytes(N, T, C);
+// Too few pairs for the above but long rows: the same kernels over chunks of T in two passes
+// (measured 1.3-4x the look-back kernels from 2048 steps up).  Needs scratch.
+bool cl_chunked_shape(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
+    return all_aligned16 && cl3_eligible(N, T, C) && T >= 2048 && encode_fn() != nullptr;
 }
 
-int cl_stream_fwd(int block, const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, cudaStream_t st) {
-    return block == 64 ? launch_cls<64, 256, 16, 1, 1, false>(gate, value, nullptr, out, nullptr, N, T, C, st)
-                       : launch_cls<32, 256, 16, 2, 2, false>(gate, value, nullptr, out, nullptr, N, T, C, st);
-}
-int cl_stream_bwd(int block, const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
-                  int64_t T, int64_t C, cudaStream_t st) {
-    return block == 64 ? launch_cls<64, 128, 8, 1, 1, true>(gate, h, gout, ggate, gvalue, N, T, C, st)
-                       : launch_cls<32, 128, 16, 2, 1, true>(gate, h, gout, ggate, gvalue, N, T, C, st);
-}
-}  // namespace
-
-extern "C" {
-
-int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, void *stream) {
-    if (t_cl_tuning != kClForcePlain && N > 0 && T > 0 && C > 0 && gate && value && out) {
-        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16));
-        if (block) return cl_stream_fwd(block, gate, value, out, N, T, C, static_cast<cudaStream_t>(stream));
-    }
-    return cl_fwd<float>(gate, value, out, N, T, C, stream);
-}
-
-}  // extern "C"
-
-namespace {
 // Measured on B200: splitting T across CTAs pays when the plain kernels cannot fill the GPU
 // (fewer than ~96 groups of 32 channels) or when there are at least 64 groups of 128 channels
 // to keep the look-back chains short; with very few channels per row the 4-channel lanes of
@@ -1496,14 +1482,143 @@ bool cl_prefers_lookback(int64_t N, int64_t C) {
     const int64_t groups32 = N * ((C + 31) / 32), groups128 = N * ((C + 127) / 128);
     return groups128 >= 64 || groups32 < 96;
 }
+
+// Steps per tile of look-back tuning id `id` (0 = unknown id).
+int cl2_tile_steps(int id, bool backward) {
+    switch (id) {
+#define X(ID, WW, LF, LB) case ID: return WW * (backward ? LB : LF);
+        SSB_CL2_CONFIGS(X)
+#undef X
+        default: return 0;
+    }
+}
+int cl3_tile_steps(int id, bool backward, int *cc) {
+    switch (id) {
+#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO) case ID: *cc = backward ? BC : FC; return backward ? BT : FT;
+        SSB_CL3_CONFIGS(X)
+#undef X
+        default: *cc = 0; return 0;
+    }
+}
+
+// Scratch a look-back variant needs: one record per tile.
+size_t cl2_need(int64_t N, int64_t T, int64_t C, int id, bool backward, bool vec) {
+    const int steps = cl2_tile_steps(id, backward);
+    if (steps == 0) return 0;
+    const int v = vec ? 4 : 1;
+    return ssb::cl2::workspace_bytes(N * ((C + 32 * v - 1) / (32 * v)) * ((T + steps - 1) / steps), v);
+}
+size_t cl3_need(int64_t N, int64_t T, int64_t C, int id, bool backward) {
+    int cc = 0;
+    const int steps = cl3_tile_steps(id, backward, &cc);
+    if (steps == 0) return 0;
+    return ssb::cl3::workspace_bytes(N * ((C + cc - 1) / cc) * ((T + steps - 1) / steps), cc);
+}
+
+// The choice SSB_CL_VARIANT_AUTO makes, given `ws_avail` bytes of usable scratch.
+int cl_pick(bool backward, int64_t N, int64_t T, int64_t C, bool all_aligned16, size_t ws_avail) {
+    const int block = cl_stream_block(N, T, C, all_aligned16);
+    if (block) return SSB_CL_VARIANT_STREAM | ((block == 64 ? 1 : 0) << 8);
+    if (cl_chunked_shape(N, T, C, all_aligned16) && ws_avail >= cls_chunk_workspace_bytes(N, T, C)) return SSB_CL_VARIANT_CHUNKED;
+    const bool vec = C % 4 == 0 && all_aligned16;
+    if (cl_prefers_lookback(N, C) && ws_avail > 0 && ws_avail >= cl2_need(N, T, C, 0, backward, vec)) return SSB_CL_VARIANT_LOOKBACK;
+    return SSB_CL_VARIANT_PLAIN;
+}
+
+template <bool BWD>
+int cl_f32_ex(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T, int64_t C,
+              int variant, void *workspace, size_t workspace_bytes, void *stream, const char *who) {
+    int64_t n;
+    int rc = check_cl(N, T, C, &n);
+    if (rc != SSB_OK) return rc;
+    if (n == 0) return SSB_OK;
+    if (!gate || !in1 || !out1 || (BWD && (!in2 || !out2))) return fail(SSB_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+    if (!aligned_to(gate, 4) || !aligned_to(in1, 4) || !aligned_to(in2, 4) || !aligned_to(out1, 4) || !aligned_to(out2, 4))
+        return fail(SSB_ERR_ALIGNMENT, "%s: pointers must be 4-byte aligned", who);
+    const bool al16 = aligned_to(gate, 16) && aligned_to(in1, 16) && aligned_to(in2, 16) && aligned_to(out1, 16) &&
+                      aligned_to(out2, 16);
+    const size_t ws_avail = (workspace != nullptr && aligned_to(workspace, 256)) ? workspace_bytes : 0;
+    if (cl_family_of(variant) == SSB_CL_VARIANT_AUTO) variant = cl_pick(BWD, N, T, C, al16, ws_avail);
+    const int id = cl_tuning_of(variant);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool tma_ok = al16 && cl3_eligible(N, T, C) && encode_fn() != nullptr;
+    switch (cl_family_of(variant)) {
+        case SSB_CL_VARIANT_PLAIN:
+            if (!BWD) return cl_fwd<float>(gate, in1, out1, N, T, C, stream);
+            return cl_bwd<float>(gate, in1, in2, out1, out2, N, T, C, stream);
+        case SSB_CL_VARIANT_STREAM:
+            if (!tma_ok) return fail(SSB_ERR_UNSUPPORTED, "%s: the streaming kernels need C %% 4 == 0 and 16-byte aligned tensors", who);
+            switch (id) {
+#define X(ID, FC, FT, FG, FS, FO, BC, BT, BG, BS, BO)                                                              \
+    case ID:                                                                                                        \
+        if constexpr (!BWD) return launch_cls<FC, FT, FG, FS, FO, false>(gate, in1, nullptr, out1, nullptr, N, T, C, st); \
+        else return launch_cls<BC, BT, BG, BS, BO, true>(gate, in1, in2, out1, out2, N, T, C, st);
+                SSB_CLS_CONFIGS(X)
+#undef X
+                default: return fail(SSB_ERR_UNSUPPORTED, "%s: unknown streaming tuning id %d", who, id);
+            }
+        case SSB_CL_VARIANT_CHUNKED:
+            if (!tma_ok) return fail(SSB_ERR_UNSUPPORTED, "%s: the chunked streaming form needs C %% 4 == 0 and 16-byte aligned tensors", who);
+            if (ws_avail < cls_chunk_workspace_bytes(N, T, C))
+                return fail(SSB_ERR_WORKSPACE, "%s: the chunked streaming form needs a 256-byte aligned workspace of %zu bytes (got %zu)",
+                            who, cls_chunk_workspace_bytes(N, T, C), ws_avail);
+            return launch_cls_chunked<BWD>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+        case SSB_CL_VARIANT_LOOKBACK_TMA:
+            if (!tma_ok) return fail(SSB_ERR_UNSUPPORTED, "%s: the TMA look-back kernels need C %% 4 == 0 and 16-byte aligned tensors", who);
+            if (ws_avail == 0) return fail(SSB_ERR_WORKSPACE, "%s: look-back needs a 256-byte aligned workspace", who);
+            switch (id) {
+#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO)                                                                                        \
+    case ID:                                                                                                                          \
+        if constexpr (!BWD) return launch_cl3<FC, FT, FS, FO, false>(gate, in1, nullptr, out1, nullptr, N, T, C, workspace, workspace_bytes, st); \
+        else return launch_cl3<BC, BT, BS, BO, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+                SSB_CL3_CONFIGS(X)
+#undef X
+                default: return fail(SSB_ERR_UNSUPPORTED, "%s: unknown TMA look-back tuning id %d", who, id);
+            }
+        case SSB_CL_VARIANT_LOOKBACK: {
+            if (ws_avail == 0) return fail(SSB_ERR_WORKSPACE, "%s: look-back needs a 256-byte aligned workspace", who);
+            const bool vec = C % 4 == 0 && al16 && !cl_scalar_lanes(variant);
+            switch (id) {
+#define X(ID, WW, LF, LB)                                                                                                          \
+    case ID:                                                                                                                        \
+        if constexpr (!BWD)                                                                                                         \
+            return vec ? launch_cl2<4, WW, LF, false>(gate, in1, nullptr, out1, nullptr, N, T, C, workspace, workspace_bytes, st)   \
+                       : launch_cl2<1, WW, LF, false>(gate, in1, nullptr, out1, nullptr, N, T, C, workspace, workspace_bytes, st);  \
+        else                                                                                                                        \
+            return vec ? launch_cl2<4, WW, LB, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st)           \
+                       : launch_cl2<1, WW, LB, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+                SSB_CL2_CONFIGS(X)
+#undef X
+                default: return fail(SSB_ERR_UNSUPPORTED, "%s: unknown look-back tuning id %d", who, id);
+            }
+        }
+        default:
+            return fail(SSB_ERR_UNSUPPORTED, "%s: channels-last variant %d is not available", who, variant);
+    }
+}
 }  // namespace
 
 extern "C" {
 
-int ssb_scan_cl_set_tuning(int tuning) {
-    const int prev = t_cl_tuning;
-    t_cl_tuning = tuning;
-    return prev;
+int ssb_scan_cl_fwd_f32(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, void *stream) {
+    return cl_f32_ex<false>(gate, value, nullptr, out, nullptr, N, T, C, SSB_CL_VARIANT_AUTO, nullptr, 0, stream, "ssb_scan_cl_fwd_f32");
+}
+
+int ssb_scan_cl_recommend(int64_t N, int64_t T, int64_t C, int backward, int aligned16, int can_provide_workspace) {
+    if (N <= 0 || T <= 0 || C <= 0) return SSB_CL_VARIANT_PLAIN;
+    return cl_pick(backward != 0, N, T, C, aligned16 != 0, can_provide_workspace ? std::numeric_limits<size_t>::max() : 0);
+}
+
+size_t ssb_scan_cl_variant_workspace_bytes(int64_t N, int64_t T, int64_t C, int variant, int backward) {
+    if (N <= 0 || T <= 0 || C <= 0) return 0;
+    switch (cl_family_of(variant)) {
+        case SSB_CL_VARIANT_CHUNKED: return C % 4 == 0 ? cls_chunk_workspace_bytes(N, T, C) : 0;
+        case SSB_CL_VARIANT_LOOKBACK:  // the caller's alignment is unknown here: the larger of the two lane widths
+            return std::max(cl2_need(N, T, C, cl_tuning_of(variant), backward != 0, false),
+                            (C % 4 == 0 && !cl_scalar_lanes(variant)) ? cl2_need(N, T, C, cl_tuning_of(variant), backward != 0, true) : 0);
+        case SSB_CL_VARIANT_LOOKBACK_TMA: return cl3_need(N, T, C, cl_tuning_of(variant), backward != 0);
+        default: return 0;
+    }
 }
 
 size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C) {
@@ -1527,120 +1642,16 @@ size_t ssb_scan_cl_workspace_bytes(int64_t N, int64_t T, int64_t C) {
     return need;
 }
 
-int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C,
+int ssb_scan_cl_fwd_f32_ex(const float *gate, const float *value, float *out, int64_t N, int64_t T, int64_t C, int variant,
                            void *workspace, size_t workspace_bytes, void *stream) {
-    int64_t n;
-    int rc = check_cl(N, T, C, &n);
-    if (rc != SSB_OK) return rc;
-    if (n == 0) return SSB_OK;
-    if (t_cl_tuning == kClForcePlain) return cl_fwd<float>(gate, value, out, N, T, C, stream);
-    if (t_cl_tuning == 0 && gate && value && out) {
-        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16));
-        if (block) return cl_stream_fwd(block, gate, value, out, N, T, C, static_cast<cudaStream_t>(stream));
-        if (cl_chunked_applies(N, T, C, aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16), workspace, workspace_bytes))
-            return launch_cls_chunked<false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes,
-                                             static_cast<cudaStream_t>(stream));
-    }
-    if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
-        (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
-        return cl_fwd<float>(gate, value, out, N, T, C, stream);
-    if (!gate || !value || !out) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_fwd_f32_ex: NULL tensor pointer");
-    if (!aligned_to(gate, 4) || !aligned_to(value, 4) || !aligned_to(out, 4))
-        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_fwd_f32_ex: pointers must be 4-byte aligned");
-    const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(value, 16) && aligned_to(out, 16) &&
-                     !(t_cl_tuning & 0x100);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if ((t_cl_tuning & 0xff) == kClChunkedId) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        return launch_cls_chunked<false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
-    }
-    if ((t_cl_tuning & 0xff) >= 64) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        switch ((t_cl_tuning & 0xff) - 64) {
-#define X(ID, FC, FT, FG, FS, FO, BC, BT, BG, BS, BO) case ID: return launch_cls<FC, FT, FG, FS, FO, false>(gate, value, nullptr, out, nullptr, N, T, C, st);
-            SSB_CLS_CONFIGS(X)
-#undef X
-            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last streaming tuning id %d", t_cl_tuning);
-        }
-    }
-    if ((t_cl_tuning & 0xff) >= 32) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        switch ((t_cl_tuning & 0xff) - 32) {
-#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO) case ID: return launch_cl3<FC, FT, FS, FO, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
-            SSB_CL3_CONFIGS(X)
-#undef X
-            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last TMA tuning id %d", t_cl_tuning);
-        }
-    }
-    switch (t_cl_tuning & 0xff) {
-#define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st) \
-                                              : launch_cl2<1, WW, LF, false>(gate, value, nullptr, out, nullptr, N, T, C, workspace, workspace_bytes, st);
-        SSB_CL2_CONFIGS(X)
-#undef X
-        default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last tuning id %d", t_cl_tuning);
-    }
+    return cl_f32_ex<false>(gate, value, nullptr, out, nullptr, N, T, C, variant, workspace, workspace_bytes, stream,
+                            "ssb_scan_cl_fwd_f32_ex");
 }
 
 int ssb_scan_cl_bwd_f32_ex(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
-                           int64_t T, int64_t C, void *workspace, size_t workspace_bytes, void *stream) {
-    int64_t n;
-    int rc = check_cl(N, T, C, &n);
-    if (rc != SSB_OK) return rc;
-    if (n == 0) return SSB_OK;
-    if (t_cl_tuning == kClForcePlain) return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
-    if (t_cl_tuning == 0 && gate && h && gout && ggate && gvalue) {
-        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
-                                                       aligned_to(ggate, 16) && aligned_to(gvalue, 16));
-        if (block) return cl_stream_bwd(block, gate, h, gout, ggate, gvalue, N, T, C, static_cast<cudaStream_t>(stream));
-        if (cl_chunked_applies(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) && aligned_to(ggate, 16) &&
-                                            aligned_to(gvalue, 16), workspace, workspace_bytes))
-            return launch_cls_chunked<true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes,
-                                            static_cast<cudaStream_t>(stream));
-    }
-    if (workspace == nullptr || workspace_bytes < ssb_scan_cl_workspace_bytes(N, T, C) || !aligned_to(workspace, 256) ||
-        (t_cl_tuning == 0 && !cl_prefers_lookback(N, C)))
-        return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
-    if (!gate || !h || !gout || !ggate || !gvalue) return fail(SSB_ERR_BAD_ARG, "ssb_scan_cl_bwd_f32_ex: NULL tensor pointer");
-    if (!aligned_to(gate, 4) || !aligned_to(h, 4) || !aligned_to(gout, 4) || !aligned_to(ggate, 4) || !aligned_to(gvalue, 4))
-        return fail(SSB_ERR_ALIGNMENT, "ssb_scan_cl_bwd_f32_ex: pointers must be 4-byte aligned");
-    const bool vec = C % 4 == 0 && aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
-                     aligned_to(ggate, 16) && aligned_to(gvalue, 16) && !(t_cl_tuning & 0x100);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if ((t_cl_tuning & 0xff) == kClChunkedId) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        return launch_cls_chunked<true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
-    }
-    if ((t_cl_tuning & 0xff) >= 64) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        switch ((t_cl_tuning & 0xff) - 64) {
-#define X(ID, FC, FT, FG, FS, FO, BC, BT, BG, BS, BO) case ID: return launch_cls<BC, BT, BG, BS, BO, true>(gate, h, gout, ggate, gvalue, N, T, C, st);
-            SSB_CLS_CONFIGS(X)
-#undef X
-            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last streaming tuning id %d", t_cl_tuning);
-        }
-    }
-    if ((t_cl_tuning & 0xff) >= 32) {
-        if (!vec || !cl3_eligible(N, T, C))
-            return fail(SSB_ERR_UNSUPPORTED, "channels-last TMA kernels need C %% 4 == 0 and 16-byte aligned tensors");
-        switch ((t_cl_tuning & 0xff) - 32) {
-#define X(ID, FC, FT, FS, FO, BC, BT, BS, BO) case ID: return launch_cl3<BC, BT, BS, BO, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
-            SSB_CL3_CONFIGS(X)
-#undef X
-            default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last TMA tuning id %d", t_cl_tuning);
-        }
-    }
-    switch (t_cl_tuning & 0xff) {
-#define X(ID, WW, LF, LB) case ID: return vec ? launch_cl2<4, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st) \
-                                              : launch_cl2<1, WW, LB, true>(gate, h, gout, ggate, gvalue, N, T, C, workspace, workspace_bytes, st);
-        SSB_CL2_CONFIGS(X)
-#undef X
-        default: return fail(SSB_ERR_UNSUPPORTED, "unknown channels-last tuning id %d", t_cl_tuning);
-    }
+                           int64_t T, int64_t C, int variant, void *workspace, size_t workspace_bytes, void *stream) {
+    return cl_f32_ex<true>(gate, h, gout, ggate, gvalue, N, T, C, variant, workspace, workspace_bytes, stream,
+                           "ssb_scan_cl_bwd_f32_ex");
 }
 }  // extern "C"
 
@@ -1677,7 +1688,7 @@ int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, v
 extern "C" {
 
 size_t ssb_scan_cl_h16_workspace_bytes(int64_t N, int64_t T, int64_t C) {
-    if (N <= 0 || T <= 0 || C <= 0) return 0;
+    if (N <= 0 || T <= 0 || C <= 0 || N * ((C + 63) / 64) >= 96 || T < 2048 || !cl_h16_eligible(N, T, C)) return 0;
     return cls_chunk_workspace_bytes(N, T, C, 64);
 }
 int ssb_scan_cl_fwd_bf16(const void *gate, const void *value, void *out, int64_t N, int64_t T, int64_t C, void *workspace,
@@ -1738,7 +1749,8 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
     if (!al16 || !cl3_eligible(N, T, C) || encode_fn() == nullptr)
         return fail(SSB_ERR_UNSUPPORTED, "%s needs C %% 4 == 0 and 16-byte aligned tensors (C=%lld)", who, (long long)C);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cl_stream_block(N, T, C, true) == 0 && cl_chunked_applies(N, T, C, true, workspace, workspace_bytes))
+    if (cl_stream_block(N, T, C, true) == 0 && cl_chunked_shape(N, T, C, true) && workspace != nullptr &&
+        aligned_to(workspace, 256) && workspace_bytes >= cls_chunk_workspace_bytes(N, T, C))
         return launch_cls_chunked<BWD, float, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
     if (cl_stream_block(N, T, C, true) == 64) {
         if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
@@ -1750,6 +1762,11 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
 }  // namespace
 
 extern "C" {
+
+size_t ssb_scan_cl_sigmoid_workspace_bytes(int64_t N, int64_t T, int64_t C) {
+    if (N <= 0 || T <= 0 || C <= 0 || cl_stream_block(N, T, C, true) != 0 || !cl_chunked_shape(N, T, C, true)) return 0;
+    return cls_chunk_workspace_bytes(N, T, C);
+}
 
 int ssb_scan_cl_sigmoid_fwd_f32(const float *gate_logits, const float *value, float *out, int64_t N, int64_t T, int64_t C,
                                 void *workspace, size_t workspace_bytes, void *stream) {
@@ -1767,12 +1784,7 @@ int ssb_scan_cl_fwd_f64(const double *gate, const double *value, double *out, in
 }
 int ssb_scan_cl_bwd_f32(const float *gate, const float *h, const float *gout, float *ggate, float *gvalue, int64_t N,
                         int64_t T, int64_t C, void *stream) {
-    if (t_cl_tuning != kClForcePlain && N > 0 && T > 0 && C > 0 && gate && h && gout && ggate && gvalue) {
-        const int block = cl_stream_block(N, T, C, aligned_to(gate, 16) && aligned_to(h, 16) && aligned_to(gout, 16) &&
-                                                       aligned_to(ggate, 16) && aligned_to(gvalue, 16));
-        if (block) return cl_stream_bwd(block, gate, h, gout, ggate, gvalue, N, T, C, static_cast<cudaStream_t>(stream));
-    }
-    return cl_bwd<float>(gate, h, gout, ggate, gvalue, N, T, C, stream);
+    return cl_f32_ex<true>(gate, h, gout, ggate, gvalue, N, T, C, SSB_CL_VARIANT_AUTO, nullptr, 0, stream, "ssb_scan_cl_bwd_f32");
 }
 int ssb_scan_cl_bwd_f64(const double *gate, const double *h, const double *gout, double *ggate, double *gvalue,
                         int64_t N, int64_t T, int64_t C, void *stream) {

@@ -273,11 +273,14 @@ void transposed_linear_scan(torch::Tensor gate, torch::Tensor value, torch::Tens
         rc = fn(gate.data_ptr(), value.data_ptr(), output.data_ptr(), gate.size(0), gate.size(1), gate.size(2),
                 ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     } else if (gate.scalar_type() == torch::kFloat32) {
-        const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        // the kernel that will run, and exactly the scratch it needs (none for the streaming kernels)
+        const int variant = ssb_scan_cl_recommend(gate.size(0), gate.size(1), gate.size(2), 0,
+                                                  aligned16(gate) && aligned16(value) && aligned16(output), 1);
+        const size_t ws_bytes = ssb_scan_cl_variant_workspace_bytes(gate.size(0), gate.size(1), gate.size(2), variant, 0);
         torch::Tensor ws;
         if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
         rc = ssb_scan_cl_fwd_f32_ex(gate.data_ptr<float>(), value.data_ptr<float>(), output.data_ptr<float>(),
-                                    gate.size(0), gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr,
+                                    gate.size(0), gate.size(1), gate.size(2), variant, ws_bytes ? ws.data_ptr() : nullptr,
                                     ws_bytes, current_stream());
     } else {
         rc = ssb_scan_cl_fwd_f64(gate.data_ptr<double>(), value.data_ptr<double>(), output.data_ptr<double>(),
@@ -306,12 +309,15 @@ void transposed_linear_scan_backward(torch::Tensor gate, torch::Tensor output, t
         rc = fn(gate.data_ptr(), output.data_ptr(), outGrad.data_ptr(), gateGradOut.data_ptr(), valueGradOut.data_ptr(),
                 gate.size(0), gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream());
     } else if (gate.scalar_type() == torch::kFloat32) {
-        const size_t ws_bytes = ssb_scan_cl_workspace_bytes(gate.size(0), gate.size(1), gate.size(2));
+        const int variant = ssb_scan_cl_recommend(gate.size(0), gate.size(1), gate.size(2), 1,
+                                                  aligned16(gate) && aligned16(output) && aligned16(outGrad) &&
+                                                      aligned16(gateGradOut) && aligned16(valueGradOut), 1);
+        const size_t ws_bytes = ssb_scan_cl_variant_workspace_bytes(gate.size(0), gate.size(1), gate.size(2), variant, 1);
         torch::Tensor ws;
         if (ws_bytes > 0) ws = scratch(ws_bytes, gate);
         rc = ssb_scan_cl_bwd_f32_ex(gate.data_ptr<float>(), output.data_ptr<float>(), outGrad.data_ptr<float>(),
                                     gateGradOut.data_ptr<float>(), valueGradOut.data_ptr<float>(), gate.size(0),
-                                    gate.size(1), gate.size(2), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                                    gate.size(1), gate.size(2), variant, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
                                     current_stream());
     } else {
         rc = ssb_scan_cl_bwd_f64(gate.data_ptr<double>(), output.data_ptr<double>(), outGrad.data_ptr<double>(),
@@ -330,7 +336,7 @@ void transposed_scan_sigmoid(torch::Tensor logits, torch::Tensor value, torch::T
     check_same(logits, output, "output");
     c10::cuda::CUDAGuard guard(logits.device());
     const int64_t N = logits.size(0), T = logits.size(1), C = logits.size(2);
-    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_workspace_bytes(N, T, C);
+    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_sigmoid_workspace_bytes(N, T, C);
     torch::Tensor ws;
     if (ws_bytes > 0) ws = scratch(ws_bytes, logits);
     void *wp = ws_bytes ? ws.data_ptr() : nullptr;
@@ -355,7 +361,7 @@ void transposed_scan_sigmoid_backward(torch::Tensor logits, torch::Tensor output
     check_same(logits, valueGradOut, "valueGradOut");
     c10::cuda::CUDAGuard guard(logits.device());
     const int64_t N = logits.size(0), T = logits.size(1), C = logits.size(2);
-    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_workspace_bytes(N, T, C);
+    const size_t ws_bytes = is_16bit(logits) ? ssb_scan_cl_h16_workspace_bytes(N, T, C) : ssb_scan_cl_sigmoid_workspace_bytes(N, T, C);
     torch::Tensor ws;
     if (ws_bytes > 0) ws = scratch(ws_bytes, logits);
     void *wp = ws_bytes ? ws.data_ptr() : nullptr;

@@ -5,6 +5,7 @@
     python -m scanscam_b200.tune fused:16384x4096                     (gate logits in; recompute backward)
     python -m scanscam_b200.tune h16:16384x4096                       (bf16 / fp16 storage beside fp32)
     python -m scanscam_b200.tune clh16:64x4096x512                    (the same for channels-last)
+    python -m scanscam_b200.tune shard:1024x131072                    (shard maps of a T-sharded sequence)
 
 For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
 ``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
@@ -22,7 +23,7 @@ from . import _native
 from .workloads import WORKLOADS
 
 FLAT_IDS = range(14)                 # SSB_FLAT_CONFIGS in csrc/scanscam_b200.cu
-TMA_IDS = (0, 1, 5, 6, 8, 10, 32, 33, 36, 37, 48)  # per-warp ring ids; 32.. flat sweep; 48 flat sweep over long rows
+TMA_IDS = (0, 1, 5, 6, 8, 10, 32, 33, 34, 35, 36, 37, 38, 48)  # per-warp ring ids; 32..38 flat sweep; 48 flat sweep over long rows
 LOOKBACK_IDS = range(7)              # SSB_LOOKBACK_CONFIGS
 
 
@@ -104,18 +105,16 @@ def time_channels_last(lib, N, T, C, iters):
         return best
 
     rows = []
-    modes = [("plain", 0x200, False), ("lookback", 1, True), ("auto", 0, True)]
+    modes = [("plain", _native.CL_PLAIN), ("lookback", _native.CL_LOOKBACK), ("auto", _native.CL_AUTO)]
     if C % 4 == 0:  # streaming kernels (a CTA walks all of T through a TMA ring), every tile shape
-        modes += [("chunked", 96, True)]  # the same kernels over chunks of T, two passes
-        modes += [(f"stream{k}", 64 + k, True) for k in range(8)]
-    for label, tuning, use_ws in modes:
-        lib.ssb_scan_cl_set_tuning(tuning)
-        p, nb = (ws.data_ptr(), need) if use_ws else (None, 0)
-        tf = run(lambda: lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, p, nb, st))
+        modes += [("chunked", _native.CL_CHUNKED)]  # the same kernels over chunks of T, two passes
+        modes += [(f"stream{k}", _native.CL_STREAM | (k << 8)) for k in range(8)]
+    for label, variant in modes:
+        p, nb = ws.data_ptr(), need
+        tf = run(lambda: lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), N, T, C, variant, p, nb, st))
         tb = run(lambda: lib.ssb_scan_cl_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(),
-                                                    gb.data_ptr(), N, T, C, p, nb, st))
+                                                    gb.data_ptr(), N, T, C, variant, p, nb, st))
         rows.append((label, 12 * n / tf / 1e6, tf, 20 * n / tb / 1e6, tb))
-    lib.ssb_scan_cl_set_tuning(0)
     return rows
 
 
@@ -130,8 +129,14 @@ def time_channels_last_16bit(lib, N, T, C, iters):
         h, ga, gb = (torch.empty_like(a) for _ in range(3))
         need = (lib.ssb_scan_cl_workspace_bytes if name == "f32" else lib.ssb_scan_cl_h16_workspace_bytes)(N, T, C)
         ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
-        fwd = lib.ssb_scan_cl_fwd_f32_ex if name == "f32" else getattr(lib, f"ssb_scan_cl_fwd_{name}")
-        bwd = lib.ssb_scan_cl_bwd_f32_ex if name == "f32" else getattr(lib, f"ssb_scan_cl_bwd_{name}")
+        if name == "f32":  # the library's own choice, with the scratch at hand
+            def fwd(*args):
+                return lib.ssb_scan_cl_fwd_f32_ex(*args[:6], _native.CL_AUTO, *args[6:])
+
+            def bwd(*args):
+                return lib.ssb_scan_cl_bwd_f32_ex(*args[:8], _native.CL_AUTO, *args[8:])
+        else:
+            fwd, bwd = getattr(lib, f"ssb_scan_cl_fwd_{name}"), getattr(lib, f"ssb_scan_cl_bwd_{name}")
         size = a.element_size()
 
         def run(fn):
@@ -232,16 +237,79 @@ def time_16bit(lib, rows, T, iters):
     return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("shapes")
+MODES = {"fused": 2, "h16": 2, "clh16": 3, "cl": 3, "shard": 2}  # prefix -> number of extents
+
+
+def parse_shape(name: str):
+    """``cfg2`` | ``ROWSxT`` | ``MODE:AxB[xC]`` -> (mode or "rows", extents).  Raises ValueError."""
+    if name in WORKLOADS:
+        return "rows", (WORKLOADS[name].rows, WORKLOADS[name].steps)
+    mode, _, dims = name.rpartition(":")
+    mode = mode or "rows"
+    if mode != "rows" and mode not in MODES:
+        raise ValueError(f"unknown sweep mode {mode!r} in {name!r}")
+    try:
+        extents = tuple(int(v) for v in dims.lower().split("x"))
+    except ValueError:
+        raise ValueError(f"cannot read the extents of {name!r}") from None
+    if len(extents) != (2 if mode == "rows" else MODES[mode]) or min(extents) <= 0:
+        raise ValueError(f"{name!r}: expected {2 if mode == 'rows' else MODES[mode]} positive extents")
+    return mode, extents
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("shapes", help="comma-separated: a workload name, ROWSxT, cl:NxTxC, fused:ROWSxT, h16:ROWSxT, "
+                                   "clh16:NxTxC, shard:ROWSxT")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--families", default="warp,flat,tma,lookback")
     ap.add_argument("--json", default=None)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
+    args.parsed = [(name, *parse_shape(name)) for name in args.shapes.split(",")]
+    known = {"warp", "flat", "tma", "lookback"}
+    bad = set(args.families.split(",")) - known
+    if bad:
+        ap.error(f"unknown kernel families {sorted(bad)}; choose from {sorted(known)}")
+    return args
+
+
+def time_shard_maps(lib, rows, T, iters):
+    """The shard maps of a T-sharded sequence (near-unit gates): full reduction, early-terminated walks."""
+    a = torch.rand(rows, T, device="cuda") * 0.01 + 0.99
+    b, g = torch.randn_like(a) * 0.1, torch.randn_like(a)
+    agg = torch.empty(rows, 2, device="cuda")
+    walked = torch.zeros(1, dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    out = []
+    for label, cut in (("full walk (cut < 0)", -1.0), ("exact zero (cut = 0)", 0.0), ("cut = 2^-40", 2.0 ** -40)):
+        for kind, fn, other in (("fwd", lib.ssb_shard_map_fwd_f32, b), ("bwd", lib.ssb_shard_map_bwd_f32, g)):
+            for _ in range(3):
+                _native.check(fn(a.data_ptr(), other.data_ptr(), agg.data_ptr(), rows, T, cut, None, st))
+            walked.zero_()
+            _native.check(fn(a.data_ptr(), other.data_ptr(), agg.data_ptr(), rows, T, cut, walked.data_ptr(), st))
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn(a.data_ptr(), other.data_ptr(), agg.data_ptr(), rows, T, cut, None, st)
+            e1.record()
+            torch.cuda.synchronize()
+            out.append((f"{label} {kind}", e0.elapsed_time(e1) / iters, walked.item() / rows))
+    return out
+
+
+def main(argv=None):
+    args = parse_args(argv)
     lib = _native.load()
     results = {}
-    for name in args.shapes.split(","):
+    for name, mode, extents in args.parsed:
+        if mode == "shard":  # shard maps of a T-sharded sequence: shard:ROWSxT
+            rows, T = extents
+            print(f"# shard maps, rows={rows} T={T} (near-unit gates)")
+            for label, ms, steps in time_shard_maps(lib, rows, T, args.iters):
+                results[f"{name}/{label}"] = {"ms": ms, "steps_walked_per_row": steps}
+                print(f"{label:28s} {ms:8.4f} ms  {steps:10.0f} steps walked per row", flush=True)
+            continue
         if name.startswith("fused:"):  # gate logits in: fused:ROWSxT
             rows, T = (int(v) for v in name[6:].lower().split("x"))
             print(f"# fused sigmoid gate, rows={rows} T={T} ({rows * T * 4 / 1e6:.0f} MB per tensor)")

@@ -1,5 +1,7 @@
 """Helpers for the GPU parity tests: call the C-ABI with torch device buffers, compare with the
 CPU oracle."""
+import os
+
 import numpy as np
 import torch
 
@@ -63,28 +65,44 @@ def bwd(a, h, g, c_in=None, h_prev=None, variant=AUTO, workspace=None):
     return ga, gb
 
 
-def cl_workspace(a):
-    need = _native.load().ssb_scan_cl_workspace_bytes(*a.shape)
+def cl_variant(mode):
+    """Test shorthand -> ssb_cl_variant_t value.  True: look-back, default tile.  "plain": the plain
+    kernels.  Integers keep the numbering of the tuning tables: 2..31 look-back tile shapes,
+    32..37 look-back on TMA-staged tiles, 64..71 streaming tile shapes, 96 the chunked form."""
+    if mode is True:
+        return _native.CL_LOOKBACK
+    if mode == "plain":
+        return _native.CL_PLAIN
+    if isinstance(mode, int) and mode == 96:
+        return _native.CL_CHUNKED
+    if isinstance(mode, int) and mode >= 64:
+        return _native.CL_STREAM | ((mode - 64) << 8)
+    if isinstance(mode, int) and mode >= 32:
+        return _native.CL_LOOKBACK_TMA | ((mode - 32) << 8)
+    if isinstance(mode, int) and mode > 1:
+        return _native.CL_LOOKBACK | (mode << 8)
+    raise ValueError(mode)
+
+
+def cl_workspace(a, variant=None, backward=False):
+    """Scratch for a channels-last call: what the variant asks for, or the bound over all variants."""
+    lib = _native.load()
+    need = (lib.ssb_scan_cl_workspace_bytes(*a.shape) if variant is None
+            else lib.ssb_scan_cl_variant_workspace_bytes(*a.shape, variant, int(backward)))
     return torch.empty(max(need, 1), dtype=torch.uint8, device=a.device), need
 
 
 def cl_fwd(a, b, scratch=False):
-    """scratch=True: the look-back kernels (float32 only), with a workspace as a caller would pass."""
+    """scratch=False: the plain entry points (no scratch).  Otherwise a family pinned through the
+    _ex entry point with the scratch that family asks for (float32 only); see cl_variant."""
     lib = _native.load()
     out = torch.empty_like(a)
     N, T, C = a.shape
-    if scratch == "plain":  # the plain kernels, whatever the library would pick
-        lib.ssb_scan_cl_set_tuning(0x200)
-        rc = lib.ssb_scan_cl_fwd_f32(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, _native.stream_of(a))
-        lib.ssb_scan_cl_set_tuning(0)
-        _native.check(rc)
-        return out
     if scratch:
-        ws, need = cl_workspace(a)
-        lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)  # always look-back
-        _native.check(lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, ws.data_ptr(),
-                                                 need, _native.stream_of(a)))
-        lib.ssb_scan_cl_set_tuning(0)
+        variant = cl_variant(scratch)
+        ws, need = cl_workspace(a, variant, False)
+        _native.check(lib.ssb_scan_cl_fwd_f32_ex(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, variant,
+                                                 ws.data_ptr() if need else None, need, _native.stream_of(a)))
         return out
     fn = lib.ssb_scan_cl_fwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_fwd_f64
     _native.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), N, T, C, _native.stream_of(a)))
@@ -95,19 +113,12 @@ def cl_bwd(a, h, g, scratch=False):
     lib = _native.load()
     ga, gb = torch.empty_like(a), torch.empty_like(a)
     N, T, C = a.shape
-    if scratch == "plain":
-        lib.ssb_scan_cl_set_tuning(0x200)
-        rc = lib.ssb_scan_cl_bwd_f32(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C,
-                                     _native.stream_of(a))
-        lib.ssb_scan_cl_set_tuning(0)
-        _native.check(rc)
-        return ga, gb
     if scratch:
-        ws, need = cl_workspace(a)
-        lib.ssb_scan_cl_set_tuning(scratch if isinstance(scratch, int) and scratch > 1 else 1)
+        variant = cl_variant(scratch)
+        ws, need = cl_workspace(a, variant, True)
         _native.check(lib.ssb_scan_cl_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(),
-                                                 N, T, C, ws.data_ptr(), need, _native.stream_of(a)))
-        lib.ssb_scan_cl_set_tuning(0)
+                                                 N, T, C, variant, ws.data_ptr() if need else None, need,
+                                                 _native.stream_of(a)))
         return ga, gb
     fn = lib.ssb_scan_cl_bwd_f32 if a.dtype == torch.float32 else lib.ssb_scan_cl_bwd_f64
     _native.check(fn(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), N, T, C,
@@ -125,7 +136,12 @@ def max_norm_err(x, ref):
     """max|x - ref| / max|ref| : the parity metric (elementwise relative error is meaningless
     near zero crossings, where the fp32 oracle itself is several percent from fp64)."""
     x = x.detach().cpu().numpy() if isinstance(x, torch.Tensor) else x
-    return float(np.abs(x.astype(np.float64) - ref.astype(np.float64)).max() / (float(np.abs(ref).max()) + 1e-300))
+    err = float(np.abs(x.astype(np.float64) - ref.astype(np.float64)).max() / (float(np.abs(ref).max()) + 1e-300))
+    report = os.environ.get("SSB_PARITY_REPORT")  # opt-in: one line per comparison, for the error survey
+    if report:
+        with open(report, "a") as f:
+            f.write(f"{os.environ.get('PYTEST_CURRENT_TEST', '?').split(' ')[0]}\t{err:.3e}\n")
+    return err
 
 
 def allclose_ref(x, ref, atol=1e-4, rtol=1e-5):

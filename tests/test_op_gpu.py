@@ -342,3 +342,30 @@ def test_fused_sigmoid_gate_channels_last(dtype, shape):
     h.backward(g.mT)
     for x, r in ((h, ref), (z1.grad, zf.grad), (b1.grad, bf.grad)):
         assert float((x.detach().float() - r.detach()).abs().max() / r.detach().abs().max()) < tol
+
+
+@pytest.mark.parametrize("shape", [(8, 4096, 512), (16, 1024, 256)])
+def test_channels_last_wrappers_hold_no_scratch_when_the_kernel_needs_none(shape):
+    """Shapes whose channels-last kernels stream a whole sequence per CTA use no workspace: a call
+    through the reference's wrapper names must not hold more device memory than its inputs and its
+    outputs (the reference allocates nothing beyond them either, scanscam/cuda.py:76-77,90-93)."""
+    from scanscam_b200 import _native
+
+    lib = _native.load()
+    assert lib.ssb_scan_cl_variant_workspace_bytes(*shape, lib.ssb_scan_cl_recommend(*shape, 0, 1, 1), 0) == 0
+    assert lib.ssb_scan_cl_variant_workspace_bytes(*shape, lib.ssb_scan_cl_recommend(*shape, 1, 1, 1), 1) == 0
+    x, y, z = (torch.randn(shape, device="cuda") for _ in range(3))
+    cuda.transposed_linear_scan_forward(x, y, 32)  # warm-up: one-time allocations of the runtime
+    torch.cuda.synchronize()
+    one = x.numel() * 4
+    base = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    h = cuda.transposed_linear_scan_forward(x, y, 32)
+    torch.cuda.synchronize()
+    assert torch.cuda.max_memory_allocated() - base <= one + (1 << 20), (torch.cuda.max_memory_allocated() - base, one)
+    base = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    ga, gb = cuda.transposed_linear_scan_backward(x, h, z, 32)
+    torch.cuda.synchronize()
+    assert torch.cuda.max_memory_allocated() - base <= 2 * one + (1 << 20)
+    _gpu.device_ok()

@@ -383,6 +383,34 @@ def test_cfg3_full_size_under_auto_sampled():
     _gpu.device_ok()
 
 
+def test_auto_uses_the_callers_workspace_when_it_is_large_enough():
+    """SSB_VARIANT_AUTO through the _ex entry points: with a workspace of the size
+    ssb_scan_workspace_bytes reports for the recommended variant, a few very long rows run the
+    kernels that split a row across CTAs (they write their records / chunk maps to the workspace);
+    with a workspace that is too small the call falls back to the no-scratch choice and leaves it
+    untouched.  Results are the oracle's either way."""
+    lib = _native.load()
+    rows, T = 16, 1 << 20
+    a, b, g = make_inputs("nearunit", (rows, T), seed=41)
+    h_ref, ga_ref, gb_ref = _gpu.oracle_all(a, b, g)
+    da, db, dg, dh = a.cuda(), b.cuda(), g.cuda(), dev(h_ref)
+    for backward in (0, 1):
+        variant = lib.ssb_scan_recommend(rows, T, backward, 1, 1)
+        assert (variant & 0xff) == LOOKBACK
+        need = lib.ssb_scan_workspace_bytes(rows, T, variant)
+        assert need > 0
+        for nbytes in (need, 4096):
+            ws = torch.full((nbytes,), 0xAB, dtype=torch.uint8, device="cuda")
+            if backward:
+                ga, gb = _gpu.bwd(da, dh, dg, variant=AUTO, workspace=(ws, nbytes))
+                assert _gpu.max_norm_err(gb, gb_ref) < TOL and _gpu.max_norm_err(ga, ga_ref) < TOL
+            else:
+                assert _gpu.max_norm_err(_gpu.fwd(da, db, variant=AUTO, workspace=(ws, nbytes)), h_ref) < TOL
+            touched = bool((ws != 0xAB).any().item())
+            assert touched == (nbytes == need), (backward, nbytes, touched)
+    _gpu.device_ok()
+
+
 # ---- long rows: spans of one row on different CTAs, carries by decoupled look-back ----------
 LONG_SHAPES = [(3, 8192), (1, 1048576), (5, 40000), (64, 16384), (700, 8196), (2, 4100), (17, 262144)]
 

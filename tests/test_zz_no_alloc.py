@@ -18,6 +18,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import _gpu  # noqa: E402
 
+import oracle  # noqa: E402
 from scanscam_b200 import _native  # noqa: E402
 from scanscam_b200.workloads import make_inputs  # noqa: E402
 
@@ -36,7 +37,9 @@ def static_forward(a, b, h_in=None):
 
 def test_two_calls_in_a_row_match_the_workspace_entry_point():
     """Same kernel, scratch from the library instead of from the caller; the second call is a
-    different, larger problem, so it meets the first call's leftovers in the shared scratch."""
+    different, larger problem, so it meets the first call's leftovers in the shared scratch.
+    Each result is compared with the existing entry point (caller's workspace) and, because that is
+    the same kernel, also with the CPU oracle started from the same carries."""
     for seed, (rows, T), gates in ((1, (24, 40960), "nearunit"), (2, (300, 8200), "resets")):
         a, b, _ = make_inputs(gates, (rows, T), seed=seed)
         carry = torch.randn(rows, generator=torch.Generator().manual_seed(seed))
@@ -47,6 +50,31 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
         err = float((got - expected).abs().max() / expected.abs().max())
         assert err < TOL, (rows, T, err)
         assert torch.allclose(got, expected, atol=1e-4, rtol=1e-5)
+        h_ref = oracle.scan_forward(a.numpy(), b.numpy(), h_in=carry.numpy())
+        assert _gpu.max_norm_err(got, h_ref) < TOL and _gpu.allclose_ref(got, h_ref)
+
+
+def test_without_a_carry_and_without_touching_the_allocator():
+    """h_in = NULL is the reference's case (the scan starts from zero).  And the property the entry
+    point exists for: between the moment the tensors exist and the moment the result is complete,
+    the amount of free device memory does not change -- nothing was allocated, by the runtime or
+    by any library (the first call on the device has already looked up the scratch address)."""
+    rows, T = 40, 24576
+    a, b, _ = make_inputs("sigmoid2", (rows, T), seed=3)
+    da, db = a.cuda(), b.cuda()
+    h_ref = oracle.scan_forward(a.numpy(), b.numpy())
+    assert _gpu.max_norm_err(static_forward(da, db), h_ref) < TOL      # first call on this device, at the latest
+    lib = _native.load()
+    out = torch.empty_like(da)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    _native.check(lib.ssb_scan_fwd_f32_static(da.data_ptr(), db.data_ptr(), out.data_ptr(), rows, T, None,
+                                              _native.stream_of(da)))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert _gpu.max_norm_err(out, h_ref) < TOL and _gpu.allclose_ref(out, h_ref)
+    _gpu.device_ok()
 
 
 def test_problems_beyond_the_built_in_scratch_are_refused():
