@@ -52,7 +52,9 @@ typedef enum ssb_variant {
                                 sweep over rows that are a multiple (>= 2) of 4096 */
     SSB_VARIANT_LOOKBACK = 3, /* T split across CTAs with decoupled look-back; needs a workspace.  Tuning id 16
                                  (variant | 16 << 8): no look-back but two passes over 4096-step chunks of T
-                                 run as rows of their own (chunk maps, carries, scan) */
+                                 run as rows of their own (chunk maps, carries, scan).  Tuning id 17: the same
+                                 with long chunks whose maps are folded only as far as the gate product needs
+                                 (it stops at 2^-40), then one sweep: for a few very long rows */
     SSB_VARIANT_FLAT = 4,    /* memcpy-like sweep, CTA-wide scan of 16 KB spans; needs T % 4 == 0, 16-B aligned base */
     SSB_VARIANT_FLAT_ANY = 5 /* the same sweep with per-element row boundaries: any T, 16-B aligned base */
 } ssb_variant_t;

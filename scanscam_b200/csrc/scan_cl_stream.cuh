@@ -293,6 +293,93 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     if (timed_out && lane == 0) report_device_wait(7);
 }
 
+// The chunk maps of the two-pass form without reading whole chunks: the same maps as the REDUCE
+// instantiation above (layout and meaning of `maps`), folded from the end of the chunk that the NEXT
+// chunk depends on -- the forward map from the chunk's last step towards its first, the reverse map
+// from its first step towards the last -- in tiles of SEG*TS steps, and abandoned as soon as the
+// product of the gates walked so far has dropped to |A| <= cut in every one of the unit's 32
+// channels: what was not walked could change B by at most cut times the state entering the walked
+// part.  cut = 0 stops only at exactly-zero products; rows whose products stay above the cut are
+// walked in full.  Plain vector loads (the walk's length is not known in advance, so nothing is
+// prefetched past it): thread (seg, cg) reads 4 adjacent channels of TS consecutive steps, the 8
+// threads of a quarter warp one 128-byte row.  fp32, 32-channel blocks, C % 4 == 0.
+template <int SEG, int TS, bool BWD, bool SIGMOID = false>
+__global__ void __launch_bounds__(8 * SEG)
+cl_tail_map_kernel(const float *__restrict__ gate, const float *__restrict__ in1,  // value | gout
+                   int64_t T, int64_t C, int64_t n_units, int cblocks, int64_t chunk_steps, int chunks, float cut,
+                   float *__restrict__ maps) {
+    constexpr int CC = 32, CG = 8, THREADS = CG * SEG, NW = THREADS / 32, SPW = 4, TT = SEG * TS;
+    __shared__ float4 s_tot[NW][CG][2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cg = tid % CG, seg = tid / CG, seg_in_warp = lane / CG;
+    const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+        const int chunk = (int)(unit % chunks);
+        const int64_t pair = unit / chunks;
+        const int64_t n = pair / cblocks;
+        const int c = (int)(pair % cblocks) * CC + cg * 4;
+        const bool c_ok = c < C;  // C % 4 == 0: a float4 is all in or all out
+        const int64_t lo = (int64_t)chunk * chunk_steps, hi = lo + chunk_steps < T ? lo + chunk_steps : T;
+        const float *ga = gate + n * T * C + c, *xa = in1 + n * T * C + c;
+        float4 sA = one4, sB = zero4;
+        for (int64_t walked = 0; walked < hi - lo; walked += TT) {
+            // this thread's TS steps of the tile; steps outside the chunk are the identity
+            const int64_t t0 = (BWD ? lo + walked : hi - walked - TT) + (int64_t)seg * TS;
+            float4 a[TS], x[TS];
+#pragma unroll
+            for (int k = 0; k < TS; k++) {
+                const int64_t t = t0 + k;
+                if (c_ok && t >= lo && t < hi) {
+                    a[k] = __ldcs(reinterpret_cast<const float4 *>(ga + t * C));
+                    x[k] = __ldcs(reinterpret_cast<const float4 *>(xa + t * C));
+                    if (SIGMOID) a[k] = sigmoid4(a[k]);
+                } else {
+                    a[k] = one4;
+                    x[k] = zero4;
+                }
+            }
+            Map4 m;
+            if (!BWD) {
+                m.A = a[0]; m.B = x[0];
+#pragma unroll
+                for (int k = 1; k < TS; k++) { m.B = fma4(a[k], m.B, x[k]); m.A = mul4(m.A, a[k]); }
+            } else {
+                m.A = one4; m.B = zero4;
+#pragma unroll
+                for (int k = TS - 1; k >= 0; k--) { m.B = mul4(a[k], add4(x[k], m.B)); m.A = mul4(m.A, a[k]); }
+            }
+#pragma unroll
+            for (int d = 1; d < SPW; d <<= 1) {
+                const float4 pA = shfl4(m.A, d * CG, !BWD), pB = shfl4(m.B, d * CG, !BWD);
+                const bool has = BWD ? (seg_in_warp + d < SPW) : (seg_in_warp >= d);
+                if (has) { m.B = fma4(m.A, pB, m.B); m.A = mul4(m.A, pA); }
+            }
+            if (seg_in_warp == (BWD ? 0 : SPW - 1)) {
+                s_tot[warp][cg][0] = m.A;
+                s_tot[warp][cg][1] = m.B;
+            }
+            __syncthreads();
+            float4 tA = one4, tB = zero4;  // the tile's map for this thread's 4 channels
+#pragma unroll
+            for (int q = 0; q < NW; q++) {
+                const int w = BWD ? NW - 1 - q : q;
+                const float4 wA = s_tot[w][cg][0], wB = s_tot[w][cg][1];
+                tB = fma4(wA, tB, wB);
+                tA = mul4(tA, wA);
+            }
+            // the tile lies before (forward) / after (reverse) everything walked so far
+            sB = fma4(sA, tB, sB);
+            sA = mul4(sA, tA);
+            const bool small = fabsf(sA.x) <= cut && fabsf(sA.y) <= cut && fabsf(sA.z) <= cut && fabsf(sA.w) <= cut;
+            if (__syncthreads_and(small || !c_ok)) break;  // also the barrier that frees s_tot for the next tile
+        }
+        if (seg == 0) {
+            *reinterpret_cast<float4 *>(maps + (unit * 2) * CC + cg * 4) = sA;
+            *reinterpret_cast<float4 *>(maps + (unit * 2 + 1) * CC + cg * 4) = sB;
+        }
+    }
+}
+
 // Folds the chunk maps of each (batch element, channel block) pair into the state entering every
 // chunk: forward left to right, backward right to left.  One thread per pair and channel.
 template <bool BWD>

@@ -353,8 +353,44 @@ size_t chunked_bytes(int64_t rows, int64_t T, size_t elem = 4) {  // maps [rows*
     return round256(views * 2 * elem) + 2 * round256(views * elem);
 }
 
+// Tuning id 17 of the family: long chunks with early-terminated maps.  A row is cut into K chunks of
+// whole 4096-element spans; pass 1 folds each chunk's map from the end its successor depends on and
+// stops once the product of the gates walked so far has dropped to kChunkCut (scan_shard.cuh), so
+// that gates below one cost a few thousand steps per chunk instead of a second pass over the
+// tensor; then the carries are folded as for id 16 and the chunks run as rows of the span-by-span
+// sweep.  K is the smallest divisor of T/4096 that gives at least kTailViews chunks in all (the
+// sweep walks whole chunks per CTA and wants several per SM), chunks of at least two spans; rows too
+// short for that get as many chunks as they have.
+constexpr int kChunkedTailId = 17;
+constexpr int kTailThreads = 256, kTailU = 2;  // map walk in 2048-element pieces: it overshoots the cut by half a piece on average
+constexpr float kChunkCut = 9.094947017729282e-13f;  // 2^-40: far below fp32 rounding of the scan itself
+constexpr int64_t kTailViews = 1024, kTailMinViews = 64;
+constexpr int64_t kTailMaxRows = 256;  // the default up to this many rows (measured 1.5-2.2x look-back up to 96 rows, equal at 256)
+int64_t tail_chunks(int64_t rows, int64_t T) {  // K, or 0 when the shape does not fit
+    if (rows <= 0 || T % 4096 != 0) return 0;
+    const int64_t n4 = T / 4096;
+    int64_t enough = 0, most = 0;  // smallest K that reaches kTailViews chunks; largest K of all
+    for (int64_t d = 1; d * d <= n4; d++) {
+        if (n4 % d != 0) continue;
+        for (int64_t k : {d, n4 / d}) {
+            if (n4 / k < 2 || rows * k > 0x7fffffffLL) continue;
+            if (rows * k >= kTailViews && (enough == 0 || k < enough)) enough = k;
+            if (k > most) most = k;
+        }
+    }
+    if (enough) return enough;
+    return rows * most >= kTailMinViews ? most : 0;  // short rows: as many chunks as there are, if they can occupy the GPU at all
+}
+size_t chunked_tail_bytes(int64_t rows, int64_t T) {  // maps [views][2], carry [views], h_prev [views]
+    const int64_t K = tail_chunks(rows, T);
+    if (K == 0) return 0;
+    const size_t views = (size_t)rows * (size_t)K;
+    return round256(views * 8) + 2 * round256(views * 4);
+}
+
 size_t lookback_bytes(int64_t rows, int64_t T, int tuning) {
     if (tuning == kChunkedId) return chunked_bytes(rows, T);
+    if (tuning == kChunkedTailId) return chunked_tail_bytes(rows, T);
     const int cap = lookback_cap(tuning);
     if (cap == 0 || T % 4 != 0) return 0;
     const int64_t pieces = (T / 4 + cap - 1) / cap;
@@ -427,11 +463,17 @@ int launch_chunked(const real *gate, const real *in1, const real *in2, real *out
 }
 
 template <bool BWD>
+int launch_chunked_tail(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows, int64_t T,
+                        const float *carry_in, const float *h_prev, void *workspace, size_t workspace_bytes, cudaStream_t st);
+
+template <bool BWD>
 int dispatch_lookback(int tuning, const float *gate, const float *in1, const float *in2, float *out1, float *out2,
                       int64_t rows, int64_t T, const float *carry_in, const float *h_prev, void *workspace,
                       size_t workspace_bytes, cudaStream_t st) {
     if (tuning == kChunkedId)
         return launch_chunked<BWD>(gate, in1, in2, out1, out2, rows, T, carry_in, h_prev, workspace, workspace_bytes, st);
+    if (tuning == kChunkedTailId)
+        return launch_chunked_tail<BWD>(gate, in1, in2, out1, out2, rows, T, carry_in, h_prev, workspace, workspace_bytes, st);
     if (!lookback_eligible(rows, T, tuning))
         return fail(SSB_ERR_UNSUPPORTED, "look-back kernels need 16-byte aligned tensors, T %% 4 == 0 and rows longer than one span (T=%lld)", (long long)T);
     const size_t need = lookback_bytes(rows, T, tuning);
@@ -584,6 +626,40 @@ int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::t
     return check_launch("tma_flat_kernel");
 }
 
+template <bool BWD>
+int launch_chunked_tail(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t rows, int64_t T,
+                        const float *carry_in, const float *h_prev, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int64_t K = tail_chunks(rows, T);
+    if (K == 0 || encode_fn() == nullptr)
+        return fail(SSB_ERR_UNSUPPORTED, "the long-chunk form needs T to be a multiple of 4096 with a divisor that yields at least %lld "
+                    "chunks of two or more spans (rows=%lld T=%lld)", (long long)kTailViews, (long long)rows, (long long)T);
+    const size_t need = chunked_tail_bytes(rows, T);
+    if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 256))
+        return fail(SSB_ERR_WORKSPACE, "the long-chunk form needs a 256-byte aligned workspace of %zu bytes (got %zu)", need, workspace_bytes);
+    const int64_t views = rows * K, len = T / K;
+    char *ws = static_cast<char *>(workspace);
+    float *maps = reinterpret_cast<float *>(ws);
+    float *carry = reinterpret_cast<float *>(ws + round256((size_t)views * 8));
+    float *hprev = reinterpret_cast<float *>(ws + round256((size_t)views * 8) + round256((size_t)views * 4));
+    // pass 1: every chunk's map, walked from the end the next chunk depends on, as far as the gate product needs
+    auto mk = ssb::shard::tail_map_kernel<kTailThreads, kTailU, BWD>;
+    const int grid = persistent_grid<600000 + (BWD ? 1 : 0)>(mk, kTailThreads, views);
+    mk<<<grid, kTailThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(BWD ? in2 : in1), views,
+                                      len / 4, kChunkCut, maps, nullptr);
+    int rc = check_launch("tail_map_kernel");
+    if (rc != SSB_OK) return rc;
+    // pass 2: the state entering every chunk (one warp per row folds its K maps in order)
+    ssb::lookback::chunk_carry_kernel<BWD, float><<<(int)((rows * 32 + 255) / 256), 256, 0, st>>>(maps, rows, K, carry_in, carry);
+    if ((rc = check_launch("chunk_carry_kernel")) != SSB_OK) return rc;
+    if (BWD) {
+        ssb::lookback::chunk_h_prev_kernel<float><<<(int)((views + 255) / 256), 256, 0, st>>>(in1, rows, K, len, h_prev, hprev);
+        if ((rc = check_launch("chunk_h_prev_kernel")) != SSB_OK) return rc;
+    }
+    // pass 3: the chunks as rows of the span-by-span sweep, each started from its entering state
+    if (!BWD) return launch_tmaflat<128, 4, 2, false, false, false, float, true>(gate, in1, nullptr, out1, nullptr, views, len, carry, nullptr, st);
+    return launch_tmaflat<128, 3, 1, true, false, false, float, true>(gate, in1, in2, out1, out2, views, len, carry, hprev, st);
+}
+
 // `variant` carries the family in its low byte and a tuning id in bits 8..15 (0 = default).
 int family_of(int variant) { return variant & 0xff; }
 int tuning_of(int variant) { return (variant >> 8) & 0xff; }
@@ -655,10 +731,18 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
     // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 4, 16 and
     // 64 rows; at 1-2 rows the serial carry pass over the chunks takes the gain back, from 96 rows up
     // look-back is at 3.5-6 TB/s and wins).
+    if (workspace_ok && all_aligned16 && rows <= kTailMaxRows && T >= 65536 && tail_chunks(rows, T) != 0 && encode_fn() != nullptr)
+        return SSB_VARIANT_LOOKBACK | (kChunkedTailId << 8);
     if (workspace_ok && all_aligned16 && rows >= 4 && rows <= 80 && T >= 65536 && chunked_len(T) == 4096 &&
         T / 4096 <= 4096 && chunked_eligible(rows, T) && encode_fn() != nullptr)
         return SSB_VARIANT_LOOKBACK | (kChunkedId << 8);
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
+    // Small problems (a few spans per SM at most, e.g. [4,256,1024]): the kernels are a few microseconds
+    // long and what counts is how fast the grid gets going, not the steady state: 512-element spans of
+    // 128 threads x 1 float4 give every SM several CTAs at once (6.6 against 7.5 us per forward +
+    // backward on [1024,1024] inside a CUDA graph).
+    if (all_aligned16 && flat_eligible(rows, T) && T <= 4096 && rows * T <= (int64_t)sm_count() * 4 * 4096)
+        return SSB_VARIANT_FLAT | (12 << 8);
     if (all_aligned16 && tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr) {
         // power-of-two rows that fit a span: the TMA-staged sweep (forward 128 lines x 2 stages;
         // backward 128 lines x 3 stages for 4096-step rows, 64 lines x 2 stages below)
@@ -1333,14 +1417,26 @@ int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typ
 
 // Two-pass form for shapes with few (batch element, channel block) pairs: chunk maps, carries, scan.
 constexpr int kClsChunkTile = 256;   // chunk lengths are multiples of this (every tile height divides it)
-constexpr int kClsChunkUnits = 384;  // aim for about this many units (2.6 per SM)
 
-// `cc`: channels per block (32 for fp32, 64 for 16-bit storage)
+// `cc`: channels per block (32 for fp32, 64 for 16-bit storage).  A chunk is p tiles; the scan pass
+// gives every SM one chunk at a time, so its duration is rounds * (p + start-up) tile times with
+// rounds = ceil(pairs * chunks / SMs), and the map pass walks about two tiles per chunk.  p is the
+// value that minimises that estimate (e.g. 4 pairs x 1024 tiles: 37 chunks of 28 tiles = exactly
+// one chunk per SM, instead of 47 chunks that need two rounds).
 int64_t cls_chunk_steps(int64_t N, int64_t T, int64_t C, int cc = 32) {
     const int64_t pairs = N * ((C + cc - 1) / cc), tiles = (T + kClsChunkTile - 1) / kClsChunkTile;
-    int64_t chunks = (kClsChunkUnits + pairs - 1) / pairs;
-    if (chunks > tiles) chunks = tiles;
-    return ((tiles + chunks - 1) / chunks) * kClsChunkTile;
+    const int64_t slots = sm_count();
+    int64_t best_p = tiles;
+    double best_cost = 1e300;
+    for (int64_t p = tiles < 4 ? tiles : 4; p <= tiles; p++) {
+        const int64_t chunks = (tiles + p - 1) / p, units = pairs * chunks;
+        if (units > 64 * slots) continue;
+        const int64_t rounds = (units + slots - 1) / slots;
+        const double cost = (double)rounds * ((double)p + 2.0) + (double)units * (p < 2 ? (double)p : 2.0) * 0.67 / (double)slots;
+        if (cost < best_cost) { best_cost = cost; best_p = p; }
+        if (chunks == 1) break;
+    }
+    return best_p * kClsChunkTile;
 }
 size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C, int cc = 32) {
     const int64_t steps = cls_chunk_steps(N, T, C, cc), chunks = (T + steps - 1) / steps;
@@ -1357,7 +1453,17 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
         return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
                     cls_chunk_workspace_bytes(N, T, C, CC), workspace_bytes);
     float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * CC;
-    int rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO, SIGMOID>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
+    int rc;
+    if constexpr (sizeof(IO) == 4) {
+        // pass 1 walks each chunk only as far as its gate products need (stops at 2^-40 in all 32 channels)
+        auto mk = ssb::cls::cl_tail_map_kernel<32, 8, BWD, SIGMOID>;
+        const int64_t units = pairs * chunks;
+        const int grid = persistent_grid<700000 + (BWD ? 1 : 0) + (SIGMOID ? 2 : 0)>(mk, 256, units);
+        mk<<<grid, 256, 0, st>>>(gate, BWD ? in2 : in1, T, C, units, (int)((C + CC - 1) / CC), steps, (int)chunks, kChunkCut, maps);
+        rc = check_launch("cl_tail_map_kernel");
+    } else {
+        rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO, SIGMOID>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
+    }
     if (rc != SSB_OK) return rc;
     const int64_t threads = pairs * CC;
     ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
@@ -1840,7 +1946,6 @@ int ssb_shard_carry_f32(const float *aggs, int n_shards, int shard, int reverse,
 }  // extern "C"
 
 namespace {
-constexpr int kTailThreads = 256, kTailU = 2;  // 2048-element chunks: the walk overshoots the cut by half a chunk on average
 
 template <bool BWD>
 int shard_map(const float *gate, const float *in1, float *agg, int64_t rows, int64_t T, float cut,

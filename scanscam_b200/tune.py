@@ -38,6 +38,7 @@ def variants(families):
     if "lookback" in families:
         out += [(f"lookback{t}", _native.VARIANT_LOOKBACK | (t << 8)) for t in LOOKBACK_IDS]
         out.append(("chunked", _native.VARIANT_LOOKBACK | (16 << 8)))  # two passes over chunks of T
+        out.append(("chunked17", _native.VARIANT_LOOKBACK | (17 << 8)))  # long chunks, early-terminated maps, one sweep
     return out
 
 

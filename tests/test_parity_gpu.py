@@ -412,7 +412,7 @@ def test_auto_uses_the_callers_workspace_when_it_is_large_enough():
 
 
 # ---- long rows: spans of one row on different CTAs, carries by decoupled look-back ----------
-LONG_SHAPES = [(3, 8192), (1, 1048576), (5, 40000), (64, 16384), (700, 8196), (2, 4100), (17, 262144)]
+LONG_SHAPES = [(3, 8192), (1, 1048576), (5, 40000), (64, 16384), (700, 8196), (2, 4100), (17, 262144), (6, 1048576)]
 
 
 @pytest.mark.parametrize("shape", LONG_SHAPES)
@@ -427,7 +427,7 @@ def test_lookback_long_rows(shape, gates):
     da, db, dg, dh, dc = a.cuda(), b.cuda(), g.cuda(), dev(h_ref), carry.cuda()
     lib = _native.load()
     ran = 0
-    for tuning in list(range(7)) + [16]:  # 16: the two-pass form over chunks of T (no look-back)
+    for tuning in list(range(7)) + [16, 17]:  # 16, 17: the chunked forms (no look-back): 4096-step chunks; long chunks with early-terminated maps
         variant = _gpu.lookback_variant(tuning)
         if lib.ssb_scan_workspace_bytes(rows, T, variant) == 0:
             continue
