@@ -79,11 +79,32 @@ def test_workspace_query(native):
 def test_kernel_recommendation_for_row_lengths_that_need_no_device(native):
     """The part of the default policy that does not depend on a driver being present."""
     flat = _native.VARIANT_FLAT
-    assert native.ssb_scan_recommend(64, 4092, 0, 1, 0) == flat | (6 << 8)   # fills the 4096-element span
-    assert native.ssb_scan_recommend(64, 3000, 0, 1, 0) == flat | (4 << 8)   # 27 % of it idle: the smaller span
-    assert native.ssb_scan_recommend(64, 2200, 1, 1, 0) == flat | (4 << 8)
-    assert native.ssb_scan_recommend(64, 4100, 0, 1, 0) == flat | (4 << 8)   # a full piece and a 4-element one
-    assert native.ssb_scan_recommend(64, 6000, 0, 1, 0) == flat | (6 << 8)
-    assert native.ssb_scan_recommend(64, 6000, 1, 1, 0) == flat | (9 << 8)
+    assert native.ssb_scan_recommend(4096, 4092, 0, 1, 0) == flat | (6 << 8)   # fills the 4096-element span
+    assert native.ssb_scan_recommend(4096, 3000, 0, 1, 0) == flat | (4 << 8)   # 27 % of it idle: the smaller span
+    assert native.ssb_scan_recommend(4096, 2200, 1, 1, 0) == flat | (4 << 8)
+    assert native.ssb_scan_recommend(4096, 4100, 0, 1, 0) == flat | (4 << 8)   # a full piece and a 4-element one
+    assert native.ssb_scan_recommend(4096, 6000, 0, 1, 0) == flat | (6 << 8)
+    assert native.ssb_scan_recommend(4096, 6000, 1, 1, 0) == flat | (9 << 8)
     assert native.ssb_scan_recommend(64, 1001, 0, 1, 0) == _native.VARIANT_WARP
     assert native.ssb_scan_recommend(64, 1000, 0, 0, 0) == _native.VARIANT_WARP  # unaligned tensors
+    # small problems (a few spans per SM): short spans so that the grid gets going at once
+    assert native.ssb_scan_recommend(1024, 1024, 0, 1, 0) == flat | (12 << 8)
+    assert native.ssb_scan_recommend(1024, 1024, 1, 1, 0) == flat | (12 << 8)
+    assert native.ssb_scan_recommend(64, 4092, 0, 1, 0) == flat | (12 << 8)
+
+
+def test_channels_last_recommendation_and_scratch_sizes(native):
+    """No hidden state: the choice is a function of the shape and of the scratch on offer, and the
+    scratch query answers for the variant that will run (nothing for the kernels that need none)."""
+    plain, chunked = _native.CL_PLAIN, _native.CL_CHUNKED
+    v = native.ssb_scan_cl_recommend(3, 107, 197, 0, 1, 1)          # odd channel count, short: plain or look-back, never TMA
+    assert (v & 0xff) in (plain, _native.CL_LOOKBACK)
+    assert native.ssb_scan_cl_recommend(3, 107, 197, 0, 1, 0) == plain
+    assert native.ssb_scan_cl_variant_workspace_bytes(8, 4096, 512, plain, 0) == 0
+    assert native.ssb_scan_cl_variant_workspace_bytes(8, 4096, 512, _native.CL_STREAM, 1) == 0
+    need = native.ssb_scan_cl_variant_workspace_bytes(4, 65536, 256, chunked, 0)
+    assert 0 < need < 4 * 65536 * 256 * 4 // 100                     # chunk maps and carries: far below a tensor
+    assert native.ssb_scan_cl_variant_workspace_bytes(4, 65536, 256, _native.CL_LOOKBACK, 0) > need
+    assert native.ssb_scan_cl_workspace_bytes(4, 65536, 256) >= native.ssb_scan_cl_variant_workspace_bytes(
+        4, 65536, 256, _native.CL_LOOKBACK, 1)
+    assert native.ssb_scan_cl_sigmoid_workspace_bytes(0, 5, 5) == 0
