@@ -39,7 +39,9 @@ typedef enum ssb_status {
     SSB_ERR_LAUNCH = 3,      /* the CUDA runtime or driver rejected a call; see ssb_last_error */
     SSB_ERR_DEVICE_WAIT = 4, /* a bounded device-side wait ran out (reported by ssb_device_status) */
     SSB_ERR_WORKSPACE = 5,   /* workspace missing or smaller than ssb_scan_workspace_bytes says */
-    SSB_ERR_UNSUPPORTED = 6  /* the requested kernel variant cannot run this shape */
+    SSB_ERR_UNSUPPORTED = 6, /* the requested kernel variant cannot run this shape */
+    SSB_ERR_DEVICE_CHECK = 7 /* checked build only: a kernel computed an index outside its tensor; the access was
+                                skipped (reported by ssb_device_status) */
 } ssb_status_t;
 
 /* Kernel families, for callers that want to pin one (tests, tuning sweeps).
@@ -389,9 +391,23 @@ int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int6
  * stays usable.  `scratch`: 32 bytes of 16-byte aligned device memory. */
 int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream);
 
+/* The checked build.  The same sources compiled with -DSSB_CHECKED (`python -m scanscam_b200.build
+ * --checked` -> libscanscam_b200_checked.so) make every kernel that computes its own global
+ * addresses test each index against its tensor's extent first; an index outside is not
+ * dereferenced, the status word becomes SSB_ERR_DEVICE_CHECK with a code for the site, and the
+ * kernel runs to its normal end: nothing traps, the context stays usable.  It stands in for a
+ * memory checker where none can be run, at a few per cent of speed.  (The reference has neither.)
+ * ssb_checked_build: 1 in that build, 0 in the ordinary one.
+ * ssb_selftest_index_check: launches one thread that submits an out-of-range index VALUE to the
+ * test (no memory is touched); afterwards ssb_device_status() reports SSB_ERR_DEVICE_CHECK once.
+ * Returns SSB_ERR_UNSUPPORTED in the ordinary build. */
+int ssb_checked_build(void);
+int ssb_selftest_index_check(void *stream);
+
 /* Synchronises the current device, returns and clears its device-side status word:
- * SSB_OK, or SSB_ERR_DEVICE_WAIT if a kernel's bounded wait (mbarrier, look-back flag)
- * gave up since the last call.  *detail (optional) receives the kernel-specific code. */
+ * SSB_OK, SSB_ERR_DEVICE_WAIT if a kernel's bounded wait (mbarrier, look-back flag) gave up since
+ * the last call, or SSB_ERR_DEVICE_CHECK from the checked build.  *detail (optional) receives the
+ * kernel-specific code. */
 int ssb_device_status(int *detail);
 
 #ifdef __cplusplus

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # SCANSCAM_B200_LIB selects another build of the same library (e.g. the checked build, see build.py).
 LIB_PATH = os.environ.get("SCANSCAM_B200_LIB") or os.path.join(_HERE, "libscanscam_b200.so")
 
-OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED = range(7)
+OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_DEVICE_CHECK = range(8)
 VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK, VARIANT_FLAT, VARIANT_FLAT_ANY = range(6)
 CL_AUTO, CL_PLAIN, CL_LOOKBACK, CL_LOOKBACK_TMA, CL_STREAM, CL_CHUNKED = range(6)  # ssb_cl_variant_t
 
@@ -77,6 +77,8 @@ SIGNATURES = {
     "ssb_shard_map_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_shard_map_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_selftest_wait_timeout": (_int, [_p, _sz, _p]),
+    "ssb_checked_build": (_int, []),
+    "ssb_selftest_index_check": (_int, [_p]),
     "ssb_device_status": (_int, [ctypes.POINTER(_int)]),
 }
 

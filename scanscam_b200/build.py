@@ -1,7 +1,8 @@
 """In-tree build of the native parts: ``python -m scanscam_b200.build``.
 
 1. ``libscanscam_b200.so`` -- the CUDA kernels and the C-ABI launch layer, compiled by nvcc
-   for sm_100a only (no torch involved).
+   for sm_100a only (no torch involved).  With ``--checked`` also
+   ``libscanscam_b200_checked.so``: the same library with device-side index tests.
 2. ``scanscam_ext*.so``    -- the PyTorch extension module, a thin C++ client of (1).
 
 Both land next to this file so that they are found by ``import scanscam_b200`` without any
@@ -19,6 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libscanscam_b200.so")
+LIB_CHECKED = os.path.join(HERE, "libscanscam_b200_checked.so")
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -34,20 +36,23 @@ def _cuda_sources() -> list[str]:
         os.path.join(INCLUDE, "scanscam_b200.h")]
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    """nvcc -> libscanscam_b200.so (C-ABI, sm_100a)."""
+def build_library(force: bool = False, verbose: bool = False, checked: bool = False) -> str:
+    """nvcc -> libscanscam_b200.so (C-ABI, sm_100a).  ``checked``: the same sources with -DSSB_CHECKED
+    (device-side index tests that report through the status word instead of faulting) ->
+    libscanscam_b200_checked.so; select it at run time with SCANSCAM_B200_LIB=<that path>."""
     srcs = _cuda_sources()
-    if not force and _newer(LIB, srcs):
-        return LIB
+    lib = LIB_CHECKED if checked else LIB
+    if not force and _newer(lib, srcs):
+        return lib
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
-           "-o", LIB, os.path.join(CSRC, "scanscam_b200.cu")]
+           *(["-DSSB_CHECKED"] if checked else []), "-o", lib, os.path.join(CSRC, "scanscam_b200.cu")]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
         print(" ".join(cmd))
     subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 def ext_path() -> str | None:
@@ -87,12 +92,16 @@ def build_extension(force: bool = False, verbose: bool = False) -> str:
     return out
 
 
-def build_all(force: bool = False, verbose: bool = False) -> None:
+def build_all(force: bool = False, verbose: bool = False, checked: bool = False) -> None:
     build_library(force, verbose)
     build_extension(force, verbose)
+    if checked:
+        build_library(force, verbose, checked=True)
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--checked" in sys.argv)
     print(LIB)
     print(ext_path())
+    if "--checked" in sys.argv:
+        print(LIB_CHECKED)

@@ -34,7 +34,7 @@ cl_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ value,
 #pragma unroll
         for (int k = 0; k < L; k++) {
             const int64_t t = tb + k;
-            if (c_ok && t < T) {
+            if (c_ok && t < T && SSB_INDEX_OK(base + t * C, N * T * C, 50)) {
                 a[k] = __ldcs(gate + base + t * C);
                 b[k] = __ldcs(value + base + t * C);
             } else {
@@ -57,7 +57,7 @@ cl_fwd_kernel(const real *__restrict__ gate, const real *__restrict__ value,
         for (int k = 0; k < L; k++) {
             h = fma_<real>(a[k], h, b[k]);
             const int64_t t = tb + k;
-            if (c_ok && t < T) __stcs(out + base + t * C, h);
+            if (c_ok && t < T && SSB_INDEX_OK(base + t * C, N * T * C, 51)) __stcs(out + base + t * C, h);
         }
         __syncthreads();  // all warps have read the carry and the maps of this tile
         if (warp == WS - 1) sCarry[lane] = h;
@@ -88,7 +88,7 @@ cl_bwd_kernel(const real *__restrict__ gate, const real *__restrict__ hout,
 #pragma unroll
         for (int k = 0; k < L; k++) {
             const int64_t t = tb + k;
-            if (c_ok && t < T) {
+            if (c_ok && t < T && SSB_INDEX_OK(base + t * C, N * T * C, 52)) {
                 a[k] = __ldcs(gate + base + t * C);
                 g[k] = __ldcs(gout + base + t * C);
                 hp[k] = t > 0 ? __ldcs(hout + base + (t - 1) * C) : real(0);
@@ -114,7 +114,7 @@ cl_bwd_kernel(const real *__restrict__ gate, const real *__restrict__ hout,
             const real gb = g[k] + cc;
             cc = a[k] * gb;
             const int64_t t = tb + k;
-            if (c_ok && t < T) {
+            if (c_ok && t < T && SSB_INDEX_OK(base + t * C, N * T * C, 53)) {
                 __stcs(gvalue + base + t * C, gb);
                 __stcs(ggate + base + t * C, gb * hp[k]);
             }

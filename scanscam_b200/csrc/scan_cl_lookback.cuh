@@ -140,7 +140,7 @@ cl_lookback_kernel(const float *__restrict__ gate, const float *__restrict__ in1
 #pragma unroll
         for (int k = 0; k < L; k++) {
             const int64_t tt = t_first + k;
-            if (c_ok && tt < geo.T) {
+            if (c_ok && tt < geo.T && SSB_INDEX_OK(base + tt * geo.C, geo.N * geo.T * geo.C, 60)) {
                 a[k] = load_stream<float, VEC>(gate + base + tt * geo.C);
                 if (!BWD) {
                     x[k] = load_stream<float, VEC>(in1 + base + tt * geo.C);
@@ -317,7 +317,7 @@ cl_lookback_kernel(const float *__restrict__ gate, const float *__restrict__ in1
                     o.v[v] = start.v[v];
                 }
                 const int64_t tt = t_first + k;
-                if (c_ok && tt < geo.T) store_stream<float, VEC>(out1 + base + tt * geo.C, o);
+                if (c_ok && tt < geo.T && SSB_INDEX_OK(base + tt * geo.C, geo.N * geo.T * geo.C, 61)) store_stream<float, VEC>(out1 + base + tt * geo.C, o);
             }
         } else {
 #pragma unroll
@@ -331,7 +331,7 @@ cl_lookback_kernel(const float *__restrict__ gate, const float *__restrict__ in1
                     oa.v[v] = gb * x[k].v[v];
                 }
                 const int64_t tt = t_first + k;
-                if (c_ok && tt < geo.T) {
+                if (c_ok && tt < geo.T && SSB_INDEX_OK(base + tt * geo.C, geo.N * geo.T * geo.C, 62)) {
                     store_stream<float, VEC>(out1 + base + tt * geo.C, oa);
                     store_stream<float, VEC>(out2 + base + tt * geo.C, og);
                 }

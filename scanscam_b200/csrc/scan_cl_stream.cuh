@@ -329,7 +329,7 @@ cl_tail_map_kernel(const float *__restrict__ gate, const float *__restrict__ in1
 #pragma unroll
             for (int k = 0; k < TS; k++) {
                 const int64_t t = t0 + k;
-                if (c_ok && t >= lo && t < hi) {
+                if (c_ok && t >= lo && t < hi && SSB_INDEX_OK(n * T * C + c + t * C, (n_units / chunks / cblocks) * T * C, 70)) {
                     a[k] = __ldcs(reinterpret_cast<const float4 *>(ga + t * C));
                     x[k] = __ldcs(reinterpret_cast<const float4 *>(xa + t * C));
                     if (SIGMOID) a[k] = sigmoid4(a[k]);

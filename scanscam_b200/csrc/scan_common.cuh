@@ -25,6 +25,32 @@ __device__ __forceinline__ void report_device_wait(int detail) {
     }
 }
 
+// Checked build (-DSSB_CHECKED, `python -m scanscam_b200.build --checked`): every kernel that computes
+// its own global addresses tests each index against the tensor's extent before the access.  An
+// index outside [0, extent) is never dereferenced: the access is skipped (a load yields the
+// identity element the kernel uses for padding), the status word is set to SSB_ERR_DEVICE_CHECK
+// with the site's code, and the kernel runs on to its normal end -- no trap, no assert, the
+// context stays usable.  The kernels that move data with bulk tensor copies need no such test:
+// the copy engine clips every box against the extents in the tensor map.  In the ordinary build
+// the test is the constant `true`.
+__device__ __forceinline__ void report_device_check(int site) {
+    if (atomicCAS(&g_status_word[0], 0, 7 /* SSB_ERR_DEVICE_CHECK */) == 0) {
+        g_status_word[1] = site;
+    }
+}
+#ifdef SSB_CHECKED
+__device__ __forceinline__ bool index_in_range(int64_t index, int64_t extent, int site) {
+    if (index >= 0 && index < extent) return true;
+    report_device_check(site);
+    return false;
+}
+#define SSB_INDEX_OK(index, extent, site) ::ssb::index_in_range((int64_t)(index), (int64_t)(extent), (site))
+// Submits one index to the test without touching memory (the self-test of the reporting path).
+__global__ void index_check_probe_kernel(int64_t index, int64_t extent) { (void)SSB_INDEX_OK(index, extent, 99); }
+#else
+#define SSB_INDEX_OK(index, extent, site) true
+#endif
+
 // A naturally aligned pack of VEC scalars; loads/stores of a 16-byte pack compile to one
 // 128-bit memory instruction.
 template <typename real, int VEC>

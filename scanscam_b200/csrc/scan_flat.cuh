@@ -60,6 +60,7 @@ flat_fwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ valu
     const int64_t rps = long_rows ? 1 : CAP / T4;
     const int64_t pieces = long_rows ? (T4 + CAP - 1) / CAP : 1;
     const int64_t n_units = long_rows ? rows : (rows + rps - 1) / rps;  // units handed to CTAs
+    [[maybe_unused]] const int64_t extent = rows * T4;  // float4s per tensor: what a checked build tests indices against
     int buf = 0;
 
     for (int64_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
@@ -80,7 +81,7 @@ flat_fwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ valu
 #pragma unroll
             for (int j = 0; j < U; j++) {
                 const int o = j * THREADS + tid;
-                if (o < n_vec) {
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 10)) {
                     a[j] = __ldcs(gate + first_vec + o);
                     if (SIGMOID) a[j] = sigmoid4(a[j]);
                     b[j] = __ldcs(value + first_vec + o);
@@ -154,7 +155,7 @@ flat_fwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ valu
                 h = fmaf(a[j].z, h, b[j].z); o4.z = h;
                 h = fmaf(a[j].w, h, b[j].w); o4.w = h;
                 const int o = j * THREADS + tid;
-                if (o < n_vec) __stcs(out + first_vec + o, o4);
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 11)) __stcs(out + first_vec + o, o4);
             }
             carry = fmaf(span_A, carry, span_B);
             buf ^= 1;  // the next span writes the other buffer: one barrier per span suffices
@@ -187,6 +188,7 @@ flat_bwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ hout
     const int64_t rps = long_rows ? 1 : CAP / T4;
     const int64_t pieces = long_rows ? (T4 + CAP - 1) / CAP : 1;
     const int64_t n_units = long_rows ? rows : (rows + rps - 1) / rps;
+    [[maybe_unused]] const int64_t extent = rows * T4;  // float4s per tensor (checked builds)
     const float *h_scalar = reinterpret_cast<const float *>(hout);
     int buf = 0;
 
@@ -208,11 +210,11 @@ flat_bwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ hout
             // h just left of the span: only thread 0 needs it, and only inside a long row; the
             // load is issued before the bulk loads so that it never sits on the critical path.
             float edge = 0.f;
-            if (long_rows && tid == 0 && piece > 0) edge = h_scalar[first_vec * 4 - 1];
+            if (long_rows && tid == 0 && piece > 0 && SSB_INDEX_OK(first_vec * 4 - 1, extent * 4, 12)) edge = h_scalar[first_vec * 4 - 1];
 #pragma unroll
             for (int j = 0; j < U; j++) {
                 const int o = j * THREADS + tid;
-                if (o < n_vec) {
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 10)) {
                     a[j] = __ldcs(gate + first_vec + o);
                     if (SIGMOID) a[j] = sigmoid4(a[j]);
                     g[j] = __ldcs(gout + first_vec + o);
@@ -310,7 +312,7 @@ flat_bwd_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ hout
                     oa.w *= a[j].w * (1.f - a[j].w);
                 }
                 const int o = j * THREADS + tid;
-                if (o < n_vec) {
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 13)) {
                     __stcs(ggate + first_vec + o, oa);
                     __stcs(gvalue + first_vec + o, og);
                 }

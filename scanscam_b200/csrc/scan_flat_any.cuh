@@ -40,6 +40,7 @@ __host__ __device__ inline int64_t rows_per_unit(int64_t T) {
 }
 
 __device__ __forceinline__ float4 load4_guarded(const float *base, int64_t e4, int64_t n_total) {
+    if (!SSB_INDEX_OK(e4, n_total + 3, 80)) return make_float4(0.f, 0.f, 0.f, 0.f);  // e4 may trail the end by up to 3 slack elements
     if (e4 + 4 <= n_total) return __ldcs(reinterpret_cast<const float4 *>(base + e4));
     float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
     if (e4 < n_total) r.x = base[e4];
@@ -182,7 +183,7 @@ flat_any_fwd_kernel(const float *__restrict__ gate, const float *__restrict__ va
                 h = fmaf(a[j].z, h, b[j].z); o4.z = h;
                 h = fmaf(a[j].w, h, b[j].w); o4.w = h;
                 const int o = j * THREADS + tid;
-                if (o < n_vec) store4_masked(out, (first_vec + o) * 4, o4, mk[j]);
+                if (o < n_vec && SSB_INDEX_OK((first_vec + o) * 4, n_total + 3, 81)) store4_masked(out, (first_vec + o) * 4, o4, mk[j]);
             }
             carry = fmaf(span_A, carry, span_B);
             buf ^= 1;
@@ -304,7 +305,7 @@ flat_any_bwd_kernel(const float *__restrict__ gate, const float *__restrict__ ho
                 gb = g[j].y + c; c = a[j].y * gb; og.y = gb; oa.y = gb * left[1];
                 gb = g[j].x + c; og.x = gb; oa.x = gb * left[0];
                 const int o = j * THREADS + tid;
-                if (o < n_vec) {
+                if (o < n_vec && SSB_INDEX_OK((first_vec + o) * 4, n_total + 3, 82)) {
                     store4_masked(ggate, (first_vec + o) * 4, oa, mk[j]);
                     store4_masked(gvalue, (first_vec + o) * 4, og, mk[j]);
                 }

@@ -154,6 +154,7 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
     const float *h_scalar = reinterpret_cast<const float *>(in1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t n_tickets = order.tickets();
+    [[maybe_unused]] const int64_t extent = order.rows * T4;  // float4s per tensor (checked builds)
     int buf = 0;
     bool timed_out = false;
 
@@ -188,11 +189,11 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
 
         float4 a[U], x[U], y[U];
         float edge = 0.f;
-        if (BWD && tid == 0 && piece > 0) edge = h_scalar[first_vec * 4 - 1];
+        if (BWD && tid == 0 && piece > 0 && SSB_INDEX_OK(first_vec * 4 - 1, extent * 4, 20)) edge = h_scalar[first_vec * 4 - 1];
 #pragma unroll
         for (int j = 0; j < U; j++) {
             const int o = j * THREADS + tid;
-            if (o < n_vec) {
+            if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 21)) {
                 a[j] = __ldcs(gate + first_vec + o);
                 x[j] = __ldcs(in1 + first_vec + o);
                 if (BWD) y[j] = __ldcs(in2 + first_vec + o);
@@ -292,7 +293,7 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
                 h = fmaf(a[j].z, h, x[j].z); o4.z = h;
                 h = fmaf(a[j].w, h, x[j].w); o4.w = h;
                 const int o = j * THREADS + tid;
-                if (o < n_vec) __stcs(out1 + first_vec + o, o4);
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 22)) __stcs(out1 + first_vec + o, o4);
             }
         } else {
 #pragma unroll
@@ -315,7 +316,7 @@ lookback_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
                 gb = y[j].y + c; c = a[j].y * gb; og.y = gb; oa.y = gb * x[j].x;
                 gb = y[j].x + c; og.x = gb; oa.x = gb * hl;
                 const int o = j * THREADS + tid;
-                if (o < n_vec) {
+                if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 23)) {
                     __stcs(out1 + first_vec + o, oa);
                     __stcs(out2 + first_vec + o, og);
                 }
@@ -359,6 +360,7 @@ span_maps_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1
     __shared__ float2 s_tot[2][NE];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t n_spans = rows * pieces;
+    [[maybe_unused]] const int64_t extent = rows * T4;
     int buf = 0;
     // piece-major order: the spans in flight are the same piece of consecutive rows
     for (int64_t s = blockIdx.x; s < n_spans; s += gridDim.x) {
@@ -371,7 +373,7 @@ span_maps_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1
         for (int j = 0; j < U; j++) {
             const int o = j * THREADS + tid;
             float4 a = make_float4(1.f, 1.f, 1.f, 1.f), x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (o < n_vec) {
+            if (o < n_vec && SSB_INDEX_OK(first_vec + o, extent, 24)) {
                 a = __ldcs(gate + first_vec + o);
                 x = __ldcs(in1 + first_vec + o);
             }
@@ -485,7 +487,9 @@ __global__ void chunk_h_prev_kernel(const real *__restrict__ h, int64_t rows, in
                                     const real *__restrict__ h_prev0, real *__restrict__ h_prev_view) {
     const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= rows * K) return;
-    h_prev_view[v] = (v % K) > 0 ? h[v * chunk_len - 1] : (h_prev0 != nullptr ? h_prev0[v / K] : real(0));
+    h_prev_view[v] = ((v % K) > 0 && SSB_INDEX_OK(v * chunk_len - 1, rows * K * chunk_len, 25))
+                         ? h[v * chunk_len - 1]
+                         : (h_prev0 != nullptr && (v % K) == 0 ? h_prev0[v / K] : real(0));
 }
 
 }  // namespace lookback

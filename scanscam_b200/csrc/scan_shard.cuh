@@ -61,7 +61,7 @@ tail_map_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ in1,
             for (int j = 0; j < U; j++) {
                 const int o = j * THREADS + tid;
                 float4 a = make_float4(1.f, 1.f, 1.f, 1.f), x = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (o < n) {
+                if (o < n && SSB_INDEX_OK(row * T4 + lo + o, rows * T4, 30)) {
                     a = __ldcs(ga + o);
                     x = __ldcs(xa + o);
                 }

@@ -42,7 +42,7 @@ warp_rows_fwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ val
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
-                if (idx < T) {  // T % VEC == 0 whenever VEC > 1, so a pack is all in or all out
+                if (idx < T && SSB_INDEX_OK(row * T + idx, rows * T, 40)) {  // T % VEC == 0 whenever VEC > 1, so a pack is all in or all out
                     a[u] = load_stream_io<real, io_t, VEC>(g + idx);
                     b[u] = load_stream_io<real, io_t, VEC>(v + idx);
                 } else {
@@ -79,7 +79,7 @@ warp_rows_fwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ val
                         o.v[k] = h;
                     }
                     const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
-                    if (idx < T) store_stream_io<real, io_t, VEC>(out + row * T + idx, o);
+                    if (idx < T && SSB_INDEX_OK(row * T + idx, rows * T, 41)) store_stream_io<real, io_t, VEC>(out + row * T + idx, o);
                 } else {
                     a_row *= At;
                 }
@@ -121,13 +121,13 @@ warp_rows_bwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ hou
             Pack<real, VEC> a[U], g[U], h[U];
             real edge = real(0);  // h just left of this chunk
             if constexpr (!REDUCE) {
-                if (t0 > 0) edge = widen<real, io_t>(hh_[t0 - 1]);
+                if (t0 > 0 && SSB_INDEX_OK(row * T + t0 - 1, rows * T, 42)) edge = widen<real, io_t>(hh_[t0 - 1]);
                 else if (h_prev != nullptr) edge = h_prev[row];
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
-                if (idx < T) {
+                if (idx < T && SSB_INDEX_OK(row * T + idx, rows * T, 43)) {
                     a[u] = load_stream_io<real, io_t, VEC>(ga_ + idx);
                     g[u] = load_stream_io<real, io_t, VEC>(gg_ + idx);
                     if constexpr (!REDUCE) h[u] = load_stream_io<real, io_t, VEC>(hh_ + idx);
@@ -177,7 +177,7 @@ warp_rows_bwd_kernel(const io_t *__restrict__ gate, const io_t *__restrict__ hou
                         oa.v[k] = gb * (k > 0 ? h[u].v[k > 0 ? k - 1 : 0] : left);
                     }
                     const int64_t idx = t0 + (int64_t)(u * 32 + lane) * VEC;
-                    if (idx < T) {
+                    if (idx < T && SSB_INDEX_OK(row * T + idx, rows * T, 44)) {
                         store_stream_io<real, io_t, VEC>(ggate + row * T + idx, oa);
                         store_stream_io<real, io_t, VEC>(gvalue + row * T + idx, ob);
                     }

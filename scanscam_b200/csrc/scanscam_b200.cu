@@ -793,6 +793,7 @@ const char *ssb_status_string(int status) {
         case SSB_ERR_DEVICE_WAIT: return "device-side wait ran out";
         case SSB_ERR_WORKSPACE: return "workspace missing or too small";
         case SSB_ERR_UNSUPPORTED: return "variant does not support this shape";
+        case SSB_ERR_DEVICE_CHECK: return "checked build: index outside its tensor";
         default: return "unknown status";
     }
 }
@@ -1996,6 +1997,24 @@ int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream)
     return check_launch("wait_probe_kernel");
 }
 
+int ssb_checked_build(void) {
+#ifdef SSB_CHECKED
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+int ssb_selftest_index_check(void *stream) {
+#ifdef SSB_CHECKED
+    ssb::index_check_probe_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(5, 4);
+    return check_launch("index_check_probe_kernel");
+#else
+    (void)stream;
+    return fail(SSB_ERR_UNSUPPORTED, "ssb_selftest_index_check: this is not the checked build");
+#endif
+}
+
 int ssb_device_status(int *detail) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
@@ -2006,7 +2025,9 @@ int ssb_device_status(int *detail) {
     if (word[0] != 0) {
         const int zero[2] = {0, 0};
         (void)cudaMemcpyToSymbol(ssb::g_status_word, zero, sizeof(zero));
-        return fail(word[0], "a device-side wait ran out (kernel code %d)", word[1]);
+        return word[0] == SSB_ERR_DEVICE_CHECK
+                   ? fail(word[0], "a kernel computed an index outside its tensor and skipped the access (site %d)", word[1])
+                   : fail(word[0], "a device-side wait ran out (kernel code %d)", word[1]);
     }
     return SSB_OK;
 }

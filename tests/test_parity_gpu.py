@@ -475,14 +475,16 @@ def test_lookback_workspace_contract():
         _gpu.fwd(short, short, variant=v, workspace=(torch.empty(4096, dtype=torch.uint8, device="cuda"), 4096))
     assert err.value.status == _native.ERR_UNSUPPORTED
     # the recommendation: look-back only for long rows and only when the caller can supply scratch
-    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) == LOOKBACK | (16 << 8)   # few long rows: two-pass chunked form
-    assert lib.ssb_scan_recommend(256, 65536, 0, 1, 1) == LOOKBACK
+    assert lib.ssb_scan_recommend(64, 65536, 0, 1, 1) == LOOKBACK | (17 << 8)   # few long rows: long chunks, early-terminated maps
+    assert lib.ssb_scan_recommend(256, 65536, 1, 1, 1) == LOOKBACK | (17 << 8)
+    assert lib.ssb_scan_recommend(300, 65536, 0, 1, 1) == LOOKBACK              # from there on look-back keeps up
     assert lib.ssb_scan_recommend(2048, 65536, 0, 1, 1) == TMA | (48 << 8)        # many long rows of whole spans
     assert lib.ssb_scan_recommend(1024, 65536, 1, 1, 0) == TMA | (48 << 8)
     assert lib.ssb_scan_recommend(1024, 65536, 0, 1, 1) == LOOKBACK               # the forward only from 2048 rows
     assert lib.ssb_scan_recommend(64, 65540, 0, 1, 1) == LOOKBACK               # T not a multiple of 4096
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
-    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
+    assert lib.ssb_scan_recommend(4096, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
+    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) == FLAT | (12 << 8)  # ... unless the whole problem is a few spans per SM
     assert lib.ssb_scan_recommend(64, 4092, 0, 1, 1) & 0xff == FLAT
     assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff in (WARP, FLAT_ANY)
     assert lib.ssb_scan_recommend(64, 65536, 1, 0, 1) & 0xff == WARP
