@@ -47,7 +47,7 @@ def _worker(rank, world, port, gates, rows, steps, out_dir):
 @pytest.mark.parametrize("gates,rows,steps", [("nearunit", 64, 32768), ("sigmoid2", 33, 4096), ("resets", 16, 8200),
                                               ("nearunit", 40, 131072), ("randn", 16, 8192), ("ones", 8, 4096)])
 def test_sequence_parallel_scan_on_nccl(tmp_path, gates, rows, steps):
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)  # every GPU of the box, up to eight
     if world < 2:
         pytest.skip("needs at least two GPUs")
     while steps % world:
