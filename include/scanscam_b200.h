@@ -320,7 +320,9 @@ typedef enum ssb_cl_variant {
     SSB_CL_VARIANT_LOOKBACK = 2,     /* tiles of one channel group on different CTAs, decoupled look-back; ids 0..12 */
     SSB_CL_VARIANT_LOOKBACK_TMA = 3, /* the same on tiles staged by bulk tensor copies; ids 0..5; C % 4 == 0 */
     SSB_CL_VARIANT_STREAM = 4,       /* a CTA walks all of T, tiles through a bulk-tensor ring; ids 0..7; no scratch */
-    SSB_CL_VARIANT_CHUNKED = 5       /* the streaming kernels over chunks of T in two passes (maps, then scan) */
+    SSB_CL_VARIANT_CHUNKED = 5,      /* the streaming kernels over chunks of T in two passes (maps, then scan) */
+    SSB_CL_VARIANT_NARROW = 6        /* C = 4, 8 or 16: a CTA walks a whole batch element, tiles are contiguous bytes
+                                        moved by untiled bulk copies; no scratch; AUTO's choice from 64 batch elements up */
 } ssb_cl_variant_t;
 
 /* What SSB_CL_VARIANT_AUTO would run for this fp32 problem (`can_provide_workspace` != 0: assume

@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("SCANSCAM_B200_LIB") or os.path.join(_HERE, "libscansc
 
 OK, ERR_BAD_ARG, ERR_ALIGNMENT, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_DEVICE_CHECK = range(8)
 VARIANT_AUTO, VARIANT_WARP, VARIANT_TMA, VARIANT_LOOKBACK, VARIANT_FLAT, VARIANT_FLAT_ANY = range(6)
-CL_AUTO, CL_PLAIN, CL_LOOKBACK, CL_LOOKBACK_TMA, CL_STREAM, CL_CHUNKED = range(6)  # ssb_cl_variant_t
+CL_AUTO, CL_PLAIN, CL_LOOKBACK, CL_LOOKBACK_TMA, CL_STREAM, CL_CHUNKED, CL_NARROW = range(7)  # ssb_cl_variant_t
 
 _p, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 

@@ -16,6 +16,7 @@
 
 #include "scan_cl.cuh"
 #include "scan_cl_lookback.cuh"
+#include "scan_cl_narrow.cuh"
 #include "scan_cl_stream.cuh"
 #include "scan_cl_tma.cuh"
 #include "scan_common.cuh"
@@ -1526,6 +1527,46 @@ int launch_cl3(const float *gate, const float *in1, const float *in2, float *out
     return check_launch("cl_tma_kernel");
 }
 
+// Narrow channels-last tensors (C = 4, 8 or 16): a CTA walks a whole batch element, tiles move as
+// untiled bulk copies.  Forward: runs of 15 steps, two stages, two staging slots (180 KB); backward:
+// runs of 11 steps, two stages, one staging slot (176 KB).
+bool cl_narrow_eligible(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
+    return all_aligned16 && (C == 4 || C == 8 || C == 16) && N >= 1 && T >= 1 && N <= 0x7fffffffLL;
+}
+
+template <int CG, bool BWD>
+int launch_cl_narrow_cg(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+                        cudaStream_t st) {
+    constexpr int TS = BWD ? 11 : 15, OUTBUF = BWD ? 1 : 2;
+    using Cfg = ssb::cln::Config<CG, TS, 4, 2, OUTBUF, BWD>;
+    auto kern = ssb::cln::cl_narrow_kernel<CG, TS, 4, 2, OUTBUF, BWD>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        return check_launch("cudaFuncSetAttribute(cl_narrow_kernel)");
+    static std::atomic<int> cached_occ{0};  // one per instantiation of this function template
+    int occ = cached_occ.load(std::memory_order_relaxed);
+    if (occ == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::THREADS, Cfg::SMEM_BYTES) != cudaSuccess || occ <= 0) {
+            (void)cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ.store(occ, std::memory_order_relaxed);
+    }
+    const int64_t cap = (int64_t)sm_count() * occ;
+    kern<<<(int)(N < cap ? N : cap), Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(gate, in1, in2, out1, out2, N, T);
+    return check_launch("cl_narrow_kernel");
+}
+
+template <bool BWD>
+int launch_cl_narrow(const float *gate, const float *in1, const float *in2, float *out1, float *out2, int64_t N, int64_t T,
+                     int64_t C, cudaStream_t st) {
+    switch (C) {
+        case 4: return launch_cl_narrow_cg<1, BWD>(gate, in1, in2, out1, out2, N, T, st);
+        case 8: return launch_cl_narrow_cg<2, BWD>(gate, in1, in2, out1, out2, N, T, st);
+        case 16: return launch_cl_narrow_cg<4, BWD>(gate, in1, in2, out1, out2, N, T, st);
+        default: return fail(SSB_ERR_UNSUPPORTED, "the narrow channels-last kernels take C = 4, 8 or 16 (C=%lld)", (long long)C);
+    }
+}
+
 template <typename real>
 int cl_fwd(const real *gate, const real *value, real *out, int64_t N, int64_t T, int64_t C, void *stream) {
     int64_t n;
@@ -1624,6 +1665,8 @@ size_t cl3_need(int64_t N, int64_t T, int64_t C, int id, bool backward) {
 
 // The choice SSB_CL_VARIANT_AUTO makes, given `ws_avail` bytes of usable scratch.
 int cl_pick(bool backward, int64_t N, int64_t T, int64_t C, bool all_aligned16, size_t ws_avail) {
+    // a handful of channels: whole batch elements per CTA, once there are enough of them to occupy the GPU
+    if (cl_narrow_eligible(N, T, C, all_aligned16) && N >= 64 && T >= 64) return SSB_CL_VARIANT_NARROW;
     const int block = cl_stream_block(N, T, C, all_aligned16);
     if (block) return SSB_CL_VARIANT_STREAM | ((block == 64 ? 1 : 0) << 8);
     if (cl_chunked_shape(N, T, C, all_aligned16) && ws_avail >= cls_chunk_workspace_bytes(N, T, C)) return SSB_CL_VARIANT_CHUNKED;
@@ -1653,6 +1696,10 @@ int cl_f32_ex(const float *gate, const float *in1, const float *in2, float *out1
         case SSB_CL_VARIANT_PLAIN:
             if (!BWD) return cl_fwd<float>(gate, in1, out1, N, T, C, stream);
             return cl_bwd<float>(gate, in1, in2, out1, out2, N, T, C, stream);
+        case SSB_CL_VARIANT_NARROW:
+            if (!cl_narrow_eligible(N, T, C, al16))
+                return fail(SSB_ERR_UNSUPPORTED, "%s: the narrow kernels need C = 4, 8 or 16 and 16-byte aligned tensors (C=%lld)", who, (long long)C);
+            return launch_cl_narrow<BWD>(gate, in1, in2, out1, out2, N, T, C, st);
         case SSB_CL_VARIANT_STREAM:
             if (!tma_ok) return fail(SSB_ERR_UNSUPPORTED, "%s: the streaming kernels need C %% 4 == 0 and 16-byte aligned tensors", who);
             switch (id) {

@@ -107,6 +107,8 @@ def time_channels_last(lib, N, T, C, iters):
 
     rows = []
     modes = [("plain", _native.CL_PLAIN), ("lookback", _native.CL_LOOKBACK), ("auto", _native.CL_AUTO)]
+    if C in (4, 8, 16):
+        modes += [("narrow", _native.CL_NARROW)]  # whole batch elements per CTA, untiled bulk copies
     if C % 4 == 0:  # streaming kernels (a CTA walks all of T through a TMA ring), every tile shape
         modes += [("chunked", _native.CL_CHUNKED)]  # the same kernels over chunks of T, two passes
         modes += [(f"stream{k}", _native.CL_STREAM | (k << 8)) for k in range(8)]

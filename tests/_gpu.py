@@ -73,6 +73,8 @@ def cl_variant(mode):
         return _native.CL_LOOKBACK
     if mode == "plain":
         return _native.CL_PLAIN
+    if mode == "narrow":
+        return _native.CL_NARROW
     if isinstance(mode, int) and mode == 96:
         return _native.CL_CHUNKED
     if isinstance(mode, int) and mode >= 64:

@@ -83,7 +83,8 @@ def test_golden_vectors_channels_last(name):
 # [N, T, C]: wide, narrow, odd C (scalar path), C % 4 == 0 but not a multiple of 128, one long
 # sequence with few channels (many tiles chained by look-back), T below one tile, unaligned base
 @pytest.mark.parametrize("shape", [(2, 300, 512), (3, 107, 197), (5, 613, 107), (2, 1000, 36), (1, 20000, 8),
-                                   (1, 70000, 128), (4, 5, 64), (2, 64, 4), (16, 257, 256), (32, 300, 256), (3, 700, 1100)])
+                                   (1, 70000, 128), (4, 5, 64), (2, 64, 4), (16, 257, 256), (32, 300, 256), (3, 700, 1100),
+                                   (300, 961, 8), (70, 2000, 16), (5, 1, 8), (200, 1920, 4)])
 @pytest.mark.parametrize("gates", ["randn", "nearunit"])
 def test_channels_last_with_scratch(shape, gates):
     a, b, g = make_inputs(gates, shape, seed=29)
@@ -94,6 +95,8 @@ def test_channels_last_with_scratch(shape, gates):
     modes = [True, 12, 7, False]  # look-back: default tile and two other tile shapes; the library's own choice
     if a.dtype == torch.float32:
         modes.append("plain")
+    if shape[2] in (4, 8, 16):
+        modes.append("narrow")  # whole batch elements per CTA, untiled bulk copies
     if shape[2] % 4 == 0:
         modes += [32, 33, 34, 35, 36, 37]  # TMA-staged tiles, every tile shape of the table
         modes += [96]  # streaming kernels over chunks of T: chunk maps, carries, scan
