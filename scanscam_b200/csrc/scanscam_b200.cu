@@ -737,7 +737,11 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
     if (workspace_ok && all_aligned16 && rows >= 4 && rows <= 80 && T >= 65536 && chunked_len(T) == 4096 &&
         T / 4096 <= 4096 && chunked_eligible(rows, T) && encode_fn() != nullptr)
         return SSB_VARIANT_LOOKBACK | (kChunkedId << 8);
-    if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096) return SSB_VARIANT_LOOKBACK;
+    // Look-back: rows longer than a span when there are too few of them to give every CTA a row of its own,
+    // or when they are long (from 16384 steps).  Many rows just above a span (16384 x 4100: a full span and a
+    // 4-element one per row) are left to the flat sweep below, which packs them better (6.3 against 4.2-4.7 TB/s).
+    if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096 && (rows < 1024 || T >= 16384))
+        return SSB_VARIANT_LOOKBACK;
     // Small problems (a few spans per SM at most, e.g. [4,256,1024]): the kernels are a few microseconds
     // long and what counts is how fast the grid gets going, not the steady state: 512-element spans of
     // 128 threads x 1 float4 give every SM several CTAs at once (6.6 against 7.5 us per forward +

@@ -28,7 +28,9 @@ LOOKBACK_IDS = range(7)              # SSB_LOOKBACK_CONFIGS
 
 
 def variants(families):
-    out = []
+    out = [("auto", None)]  # the library's own choice, per direction
+    if "any" in families:
+        out += [("any0", _native.VARIANT_FLAT_ANY), ("any1", _native.VARIANT_FLAT_ANY | (1 << 8))]
     if "warp" in families:
         out.append(("warp", _native.VARIANT_WARP))
     if "flat" in families:
@@ -43,19 +45,22 @@ def variants(families):
 
 
 def time_variant(lib, rows, T, variant, tensors, iters):
+    """``variant`` None: what the library recommends per direction when the caller can supply scratch."""
     a, b, g, h, ga, gb = tensors
     st = torch.cuda.current_stream().cuda_stream
-    ws_bytes = lib.ssb_scan_workspace_bytes(rows, T, variant)
+    v_f = lib.ssb_scan_recommend(rows, T, 0, 1, 1) if variant is None else variant
+    v_b = lib.ssb_scan_recommend(rows, T, 1, 1, 1) if variant is None else variant
+    ws_bytes = max(lib.ssb_scan_workspace_bytes(rows, T, v_f), lib.ssb_scan_workspace_bytes(rows, T, v_b))
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=a.device)
     ws_ptr = ws.data_ptr() if ws_bytes else None
 
     def fwd():
-        return lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, variant, ws_ptr,
+        return lib.ssb_scan_fwd_f32_ex(a.data_ptr(), b.data_ptr(), h.data_ptr(), rows, T, None, v_f, ws_ptr,
                                        ws_bytes, st)
 
     def bwd():
         return lib.ssb_scan_bwd_f32_ex(a.data_ptr(), h.data_ptr(), g.data_ptr(), ga.data_ptr(), gb.data_ptr(), rows, T,
-                                       None, None, variant, ws_ptr, ws_bytes, st)
+                                       None, None, v_b, ws_ptr, ws_bytes, st)
 
     res = {}
     for kind, fn, nbytes in (("fwd", fwd, 12), ("bwd", bwd, 20)):
@@ -269,7 +274,7 @@ def parse_args(argv=None):
     ap.add_argument("--json", default=None)
     args = ap.parse_args(argv)
     args.parsed = [(name, *parse_shape(name)) for name in args.shapes.split(",")]
-    known = {"warp", "flat", "tma", "lookback"}
+    known = {"warp", "flat", "tma", "lookback", "any"}
     bad = set(args.families.split(",")) - known
     if bad:
         ap.error(f"unknown kernel families {sorted(bad)}; choose from {sorted(known)}")
