@@ -478,40 +478,61 @@ def measure_t_sharded(args, torch, dist, timer, lib, native, workloads, world, r
     b = torch.randn(rows, T_local, generator=gen, device="cuda").mul_(0.1)
     g = torch.randn(rows, T_local, generator=gen, device="cuda")
     walked = torch.zeros(1, dtype=torch.int64, device="cuda")
-    out = {}
-
-    def step(count=None):
-        h, h_in = sharded.sharded_scan_forward(a, b, cut=cut, walked=count)
-        ga, gb = sharded.sharded_scan_backward(a, h, g, h_in, cut=cut, walked=count)
-        out["h"], out["ga"], out["gb"] = h, ga, gb
-
-    for _ in range(3):
-        step()
     steps = max(1, args.ts_steps)
-    ms = timer.max_over_ranks([timer.region_ms(lambda: [step() for _ in range(steps)])])[0] / steps
-    step(walked)
-    torch.cuda.synchronize()
-    walked_all = timer.max_over_ranks([float(walked.item())])[0]  # per tensor, forward + backward, slowest rank
-    n_local = rows * T_local
-    # a row sample against the unsharded kernels on rank 0
     idx = torch.arange(3, rows, rows // 8, device="cuda")[:8]
-    sample = [x[idx].contiguous() for x in (a, b, g, out["h"], out["ga"], out["gb"])]
-    gathered = []
-    for x in sample:
-        parts = [torch.empty_like(x) for _ in range(world)]
-        dist.all_gather(parts, x)
-        gathered.append(torch.cat(parts, dim=1))
-    max_err = None
-    if rank == 0:
-        fa, fb, fg, sh, sga, sgb = gathered
-        r, st = fa.shape[0], timer.stream.cuda_stream
-        h1, ga1, gb1 = torch.empty_like(fa), torch.empty_like(fa), torch.empty_like(fa)
-        native.check(lib.ssb_scan_fwd_f32(fa.data_ptr(), fb.data_ptr(), h1.data_ptr(), r, T, None, st))
-        native.check(lib.ssb_scan_bwd_f32(fa.data_ptr(), h1.data_ptr(), fg.data_ptr(), ga1.data_ptr(), gb1.data_ptr(), r, T,
-                                          None, None, st))
+    n_local = rows * T_local
+
+    def measure(exchange):
+        """(ms per step, elements walked by the map kernels in one step, max error on the row sample)."""
+        out = {}
+
+        def step(count=None):
+            h, h_in = sharded.sharded_scan_forward(a, b, cut=cut, walked=count, exchange=exchange)
+            ga, gb = sharded.sharded_scan_backward(a, h, g, h_in, cut=cut, walked=count, exchange=exchange)
+            out["h"], out["ga"], out["gb"] = h, ga, gb
+
+        timer.barrier()
+        for _ in range(3):
+            step()
+        ms = timer.max_over_ranks([timer.region_ms(lambda: [step() for _ in range(steps)])])[0] / steps
+        walked.zero_()
+        step(walked)
         torch.cuda.synchronize()
-        max_err = max(float((x - y).abs().max() / y.abs().max()) for x, y in ((sh, h1), (sga, ga1), (sgb, gb1)))
-    del a, b, g, out, gathered, sample
+        walked_all = timer.max_over_ranks([float(walked.item())])[0]  # per tensor, forward + backward, slowest rank
+        # a row sample against the unsharded kernels on rank 0
+        sample = [x[idx].contiguous() for x in (a, b, g, out["h"], out["ga"], out["gb"])]
+        gathered = []
+        for x in sample:
+            parts = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(parts, x)
+            gathered.append(torch.cat(parts, dim=1))
+        max_err = None
+        if rank == 0:
+            fa, fb, fg, sh, sga, sgb = gathered
+            r, st = fa.shape[0], timer.stream.cuda_stream
+            h1, ga1, gb1 = torch.empty_like(fa), torch.empty_like(fa), torch.empty_like(fa)
+            native.check(lib.ssb_scan_fwd_f32(fa.data_ptr(), fb.data_ptr(), h1.data_ptr(), r, T, None, st))
+            native.check(lib.ssb_scan_bwd_f32(fa.data_ptr(), h1.data_ptr(), fg.data_ptr(), ga1.data_ptr(), gb1.data_ptr(), r, T,
+                                              None, None, st))
+            torch.cuda.synchronize()
+            max_err = max(float((x - y).abs().max() / y.abs().max()) for x, y in ((sh, h1), (sga, ga1), (sgb, gb1)))
+        return ms, walked_all, max_err
+
+    ms, walked_all, max_err = measure(None)
+    # the same steps with the maps exchanged through peer memory instead of NCCL, where the box allows it
+    peer = {"unavailable": "peer memory exchange could not be set up (GPUs not all visible, no peer access, or IPC refused)"}
+    try:
+        exchange = sharded.PeerCarryExchange.create(rows)
+        if exchange is not None:
+            p_ms, _, p_err = measure(exchange)
+            peer = {"value": rows * T / (p_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": p_ms,
+                    "max_err_vs_unsharded": p_err, "launches_per_step_per_rank": 6,
+                    "what": "map kernels store into every rank's buffer over NVLink and raise a flag; the carry kernels wait "
+                            "(bounded) for all ranks' flags: no collective call"}
+            del exchange
+    except Exception as exc:
+        peer = {"failed": f"{type(exc).__name__}: {exc}"}
+    del a, b, g
     torch.cuda.empty_cache()
     return {
         "workload": f"cfg3 {list(w.shape)} fp32 fwd+bwd, gates {w.gates}, T split over {world} ranks",
@@ -520,7 +541,7 @@ def measure_t_sharded(args, torch, dist, timer, lib, native, workloads, world, r
         "map_walk": {"cut": cut, "elements_per_row_and_direction": walked_all / rows / 2, "shard_length": T_local},
         "collective": "2 x NCCL all_gather of [rows, 2] fp32 per step",
         "max_err_vs_unsharded": max_err, "checked": "8 rows x full T: h, grad_gate, grad_value against ssb_scan_fwd/bwd_f32 on one GPU",
-        "launches_per_step_per_rank": 6,
+        "launches_per_step_per_rank": 6, "peer_exchange": peer,
     }
 
 
@@ -734,7 +755,10 @@ def run_gpu_arm(args, workload):
             t_sharded = measure_t_sharded(args, torch, dist, timer, lib, _native, workloads, world, rank)
         except Exception as exc:  # the main measurement stands; say what happened
             t_sharded = {"failed": f"{type(exc).__name__}: {exc}"}
-        _check_status(lib, _native)
+        try:  # a bounded wait that ran out in the sharded steps is reported in their record, not raised
+            _check_status(lib, _native)
+        except Exception as exc:
+            t_sharded["device_status"] = str(exc)
 
     if rank != 0:
         if world > 1:

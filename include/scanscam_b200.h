@@ -387,6 +387,41 @@ int ssb_shard_map_fwd_f32(const float *gate, const float *value, float *agg, int
 int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T,
                           float cut, unsigned long long *walked, void *stream);
 
+/* ------------------------------------------------------------------------------------
+ * The same exchange without a collective library: the map kernel stores its result straight into
+ * every rank's buffer over NVLink (plain peer stores), and the carry kernel waits for them.
+ * (No counterpart in the reference.)  For ONE process per GPU on one node with peer access
+ * between all GPUs; the ranks call both entry points in the same order with the same `epoch`.
+ *
+ *   ssb_peer_exchange_t: `world` <= 8 ranks, this process's `rank`, `rows`, and for every rank r
+ *     `buffers[r]` = the address, in THIS process, of rank r's exchange buffer of
+ *     ssb_peer_exchange_bytes(world, rows) bytes (rank's own: an ordinary device allocation; the
+ *     others': mapped through CUDA IPC or any other peer mapping).  Zero the buffers once, and
+ *     synchronise all ranks, before the first call.
+ *   ssb_shard_map_publish_f32: as ssb_shard_map_fwd/bwd_f32 (`backward` selects the recurrence);
+ *     every row's map goes to slot [direction][epoch & 1][rank] of every rank's buffer, and the
+ *     last CTA to finish raises flag = epoch at every rank.  T % 4 == 0, 16-byte aligned tensors
+ *     (SSB_ERR_UNSUPPORTED otherwise: use the collective path).
+ *   ssb_shard_carry_peer_f32: waits until all `world` flags of this rank's buffer have reached
+ *     `epoch` -- every wait is bounded at about a second, after which ssb_device_status() reports
+ *     SSB_ERR_DEVICE_WAIT and the kernel ends -- then writes carry[rows]: the state this rank's
+ *     shard starts from (fold of the ranks before it, or after it for the reverse recurrence).
+ *   `epoch` starts at 1 and goes up by one per call and direction; the two directions have buffers
+ *   and epochs of their own.  Because every rank waits for every rank, no rank runs more than one
+ *   call ahead, and the two slot generations (epoch parity) never collide.
+ * ---------------------------------------------------------------------------------- */
+typedef struct ssb_peer_exchange {
+    int world, rank;
+    int64_t rows;
+    void *buffers[8];
+} ssb_peer_exchange_t;
+size_t ssb_peer_exchange_bytes(int world, int64_t rows);
+int ssb_shard_map_publish_f32(const float *gate, const float *other, int64_t rows, int64_t T, float cut, int backward,
+                              const ssb_peer_exchange_t *exchange, unsigned epoch, unsigned long long *walked,
+                              void *stream);
+int ssb_shard_carry_peer_f32(const ssb_peer_exchange_t *exchange, unsigned epoch, int backward, float *carry,
+                             void *stream);
+
 /* Self-test of the bounded-wait machinery: launches one warp that looks back at a record which
  * is never published.  The kernel returns by itself after the poll's time limit (about one
  * second); afterwards ssb_device_status() reports SSB_ERR_DEVICE_WAIT once and the context

@@ -76,11 +76,20 @@ SIGNATURES = {
     "ssb_shard_carry_f32": (_int, [_p, _int, _int, _int, _i64, _p, _p]),
     "ssb_shard_map_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_shard_map_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
+    "ssb_peer_exchange_bytes": (_sz, [_int, _i64]),
+    "ssb_shard_map_publish_f32": (_int, [_p, _p, _i64, _i64, ctypes.c_float, _int, _p, ctypes.c_uint, _p, _p]),
+    "ssb_shard_carry_peer_f32": (_int, [_p, ctypes.c_uint, _int, _p, _p]),
     "ssb_selftest_wait_timeout": (_int, [_p, _sz, _p]),
     "ssb_checked_build": (_int, []),
     "ssb_selftest_index_check": (_int, [_p]),
     "ssb_device_status": (_int, [ctypes.POINTER(_int)]),
 }
+
+class PeerExchangeStruct(ctypes.Structure):
+    """``ssb_peer_exchange_t``."""
+
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("rows", ctypes.c_int64), ("buffers", ctypes.c_void_p * 8)]
+
 
 _lib = None
 

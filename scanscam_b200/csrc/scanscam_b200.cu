@@ -646,7 +646,7 @@ int launch_chunked_tail(const float *gate, const float *in1, const float *in2, f
     auto mk = ssb::shard::tail_map_kernel<kTailThreads, kTailU, BWD>;
     const int grid = persistent_grid<600000 + (BWD ? 1 : 0)>(mk, kTailThreads, views);
     mk<<<grid, kTailThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(BWD ? in2 : in1), views,
-                                      len / 4, kChunkCut, maps, nullptr);
+                                      len / 4, kChunkCut, maps, nullptr, ssb::shard::PeerExchange(), 0, 0u);
     int rc = check_launch("tail_map_kernel");
     if (rc != SSB_OK) return rc;
     // pass 2: the state entering every chunk (one warp per row folds its K maps in order)
@@ -2021,7 +2021,7 @@ int shard_map(const float *gate, const float *in1, float *agg, int64_t rows, int
     auto kern = ssb::shard::tail_map_kernel<kTailThreads, kTailU, BWD>;
     const int grid = persistent_grid<600000 + (BWD ? 1 : 0)>(kern, kTailThreads, rows);
     kern<<<grid, kTailThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1), rows,
-                                        T / 4, cut, agg, walked);
+                                        T / 4, cut, agg, walked, ssb::shard::PeerExchange(), 0, 0u);
     return check_launch("tail_map_kernel");
 }
 }  // namespace
@@ -2036,6 +2036,70 @@ int ssb_shard_map_fwd_f32(const float *gate, const float *value, float *agg, int
 int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int64_t rows, int64_t T, float cut,
                           unsigned long long *walked, void *stream) {
     return shard_map<true>(gate, gout, agg, rows, T, cut, walked, stream, "ssb_shard_map_bwd_f32");
+}
+
+}  // extern "C"
+
+namespace {
+int to_peer_exchange(const ssb_peer_exchange_t *ex, ssb::shard::PeerExchange *px, const char *who) {
+    if (ex == nullptr || ex->world < 1 || ex->world > ssb::shard::kMaxPeers || ex->rank < 0 || ex->rank >= ex->world || ex->rows < 0)
+        return fail(SSB_ERR_BAD_ARG, "%s: bad exchange descriptor (world 1..%d, 0 <= rank < world)", who, ssb::shard::kMaxPeers);
+    px->world = ex->world;
+    px->rank = ex->rank;
+    px->rows = ex->rows;
+    for (int r = 0; r < ssb::shard::kMaxPeers; r++) {
+        px->buf[r] = r < ex->world ? static_cast<unsigned char *>(ex->buffers[r]) : nullptr;
+        if (r < ex->world && (px->buf[r] == nullptr || !aligned_to(px->buf[r], 256)))
+            return fail(SSB_ERR_BAD_ARG, "%s: exchange buffer of rank %d is NULL or not 256-byte aligned", who, r);
+    }
+    return SSB_OK;
+}
+
+template <bool BWD>
+int shard_map_publish(const float *gate, const float *in1, int64_t rows, int64_t T, float cut, const ssb::shard::PeerExchange &px,
+                      unsigned epoch, unsigned long long *walked, cudaStream_t st) {
+    auto kern = ssb::shard::tail_map_kernel<kTailThreads, kTailU, BWD, true>;
+    const int grid = persistent_grid<610000 + (BWD ? 1 : 0)>(kern, kTailThreads, rows);
+    kern<<<grid, kTailThreads, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(in1), rows,
+                                        T / 4, cut, nullptr, walked, px, (int)(epoch & 1u), epoch);
+    return check_launch("tail_map_kernel<publish>");
+}
+}  // namespace
+
+extern "C" {
+
+size_t ssb_peer_exchange_bytes(int world, int64_t rows) {
+    if (world < 1 || world > ssb::shard::kMaxPeers || rows <= 0) return 0;
+    return ssb::shard::px_total_bytes(world, rows);
+}
+
+int ssb_shard_map_publish_f32(const float *gate, const float *other, int64_t rows, int64_t T, float cut, int backward,
+                              const ssb_peer_exchange_t *exchange, unsigned epoch, unsigned long long *walked, void *stream) {
+    int64_t n;
+    int rc = check_shape(rows, T, &n);
+    if (rc != SSB_OK) return rc;
+    ssb::shard::PeerExchange px;
+    if ((rc = to_peer_exchange(exchange, &px, "ssb_shard_map_publish_f32")) != SSB_OK) return rc;
+    if (rows != px.rows || rows == 0) return fail(SSB_ERR_BAD_ARG, "ssb_shard_map_publish_f32: rows=%lld, the exchange was made for %lld", (long long)rows, (long long)px.rows);
+    if (!gate || !other) return fail(SSB_ERR_BAD_ARG, "ssb_shard_map_publish_f32: NULL pointer");
+    if (T == 0 || T % 4 != 0 || !aligned_to(gate, 16) || !aligned_to(other, 16) || !aligned_to(walked, 8))
+        return fail(SSB_ERR_UNSUPPORTED, "ssb_shard_map_publish_f32 needs T %% 4 == 0 and 16-byte aligned tensors (T=%lld)", (long long)T);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return backward ? shard_map_publish<true>(gate, other, rows, T, cut, px, epoch, walked, st)
+                    : shard_map_publish<false>(gate, other, rows, T, cut, px, epoch, walked, st);
+}
+
+int ssb_shard_carry_peer_f32(const ssb_peer_exchange_t *exchange, unsigned epoch, int backward, float *carry, void *stream) {
+    ssb::shard::PeerExchange px;
+    int rc = to_peer_exchange(exchange, &px, "ssb_shard_carry_peer_f32");
+    if (rc != SSB_OK) return rc;
+    if (px.rows == 0) return SSB_OK;
+    if (!carry || !aligned_to(carry, 4)) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_peer_f32: carry is NULL or misaligned");
+    const int block = 256;
+    const int64_t grid = (px.rows + block - 1) / block;
+    if (grid > 0x7fffffffLL) return fail(SSB_ERR_BAD_ARG, "ssb_shard_carry_peer_f32: too many rows");
+    ssb::shard::peer_carry_kernel<<<(int)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(px, backward ? 1 : 0, (int)(epoch & 1u), epoch, carry);
+    return check_launch("peer_carry_kernel");
 }
 
 int ssb_selftest_wait_timeout(void *scratch, size_t scratch_bytes, void *stream) {

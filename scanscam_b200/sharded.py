@@ -21,6 +21,9 @@ for ``grad_gate`` at the shard's first step, is the forward's ``h_in``.
 
 Bytes moved per element and direction: the scan's 12 / 20 plus 8 x (walked fraction of the shard).
 
+Steps 1-3 also exist without the collective library (:class:`PeerCarryExchange`): the map kernel
+stores its result into every rank's buffer through peer memory and the carry kernel waits for it.
+
 The numeric work is delegated to an *ops* object so the exchange logic can be exercised on CPU
 process groups (gloo) with stand-in ops supplied by the tests; the default ops call the CUDA
 extension and nothing else.
@@ -89,6 +92,97 @@ class CudaShardOps:
         return grad_gate, grad_value
 
 
+class PeerCarryExchange:
+    """The exchange step without a collective: every rank's map kernel stores its ``[rows, 2]`` result
+    straight into every other rank's buffer over NVLink, and the carry kernel waits for them
+    (``ssb_shard_map_publish_f32`` / ``ssb_shard_carry_peer_f32``).  Two kernel launches per
+    direction before the scan instead of map, all-gather, carry.
+
+    Needs one process per GPU on one node, every process seeing all the GPUs under the same
+    indices, and peer access between them; the buffers are exchanged once, here, as CUDA IPC
+    handles through the process group.  ``PeerCarryExchange.create`` returns ``None`` where that
+    is not possible (the callers then keep the collective path).  All ranks must make the same
+    sequence of forward / backward calls with an exchange object: the epochs are counted locally.
+    """
+
+    def __init__(self, rows: int, group=None, device: Optional[torch.device] = None):
+        from torch.multiprocessing.reductions import rebuild_cuda_tensor, reduce_tensor
+
+        from . import _native
+
+        self.lib = _native.load()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.rows = int(rows)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        nbytes = self.lib.ssb_peer_exchange_bytes(self.world, self.rows)
+        if nbytes == 0:
+            raise ValueError(f"peer exchange supports 1..8 ranks and at least one row (world={self.world}, rows={rows})")
+        self.buffer = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+        self.peers = [self.buffer] * self.world
+        if self.world > 1:
+            _, args = reduce_tensor(self.buffer)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, args, group=group)
+            self.peers = [self.buffer if r == self.rank else rebuild_cuda_tensor(*handles[r]) for r in range(self.world)]
+        self.struct = _native.PeerExchangeStruct()
+        self.struct.world, self.struct.rank, self.struct.rows = self.world, self.rank, self.rows
+        for r, t in enumerate(self.peers):
+            self.struct.buffers[r] = t.data_ptr()
+        self.epoch = [0, 0]  # forward, backward
+        if self.world > 1:
+            dist.barrier(group=group)  # every buffer is zeroed and mapped everywhere before anyone publishes
+        self._check = _native.check
+        self._byref = _native.ctypes.byref
+
+    @classmethod
+    def create(cls, rows: int, group=None, device: Optional[torch.device] = None) -> Optional["PeerCarryExchange"]:
+        """An exchange for ``rows`` rows, or None when this job cannot use peer memory (more than 8
+        ranks, fewer visible GPUs than ranks, no peer access, IPC refused).  Collective: call it on
+        every rank of the group."""
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        ok = torch.cuda.is_available() and world <= 8 and torch.cuda.device_count() >= world
+        if ok and world > 1:
+            me = torch.cuda.current_device()
+            ok = all(torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        ex = None
+        if ok:
+            try:
+                ex = cls(rows, group, device)
+            except Exception:  # an IPC refusal on one rank must not leave the others with an exchange
+                ex = None
+        if world > 1:
+            agree = torch.tensor([1 if ex is not None else 0], device="cuda")
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
+            if int(agree.item()) == 0:
+                ex = None
+        return ex
+
+    def publish_map(self, gate: torch.Tensor, other: torch.Tensor, backward: bool, cut: float,
+                    walked: Optional[torch.Tensor] = None) -> None:
+        assert gate.shape == other.shape and gate.shape[0] == self.rows and gate.dtype == torch.float32
+        d = 1 if backward else 0
+        self.epoch[d] += 1
+        stream = torch.cuda.current_stream(gate.device).cuda_stream
+        self._check(self.lib.ssb_shard_map_publish_f32(gate.data_ptr(), other.data_ptr(), self.rows, gate.shape[1], cut, d,
+                                                       self._byref(self.struct), self.epoch[d],
+                                                       None if walked is None else walked.data_ptr(), stream))
+
+    def carry(self, backward: bool) -> torch.Tensor:
+        d = 1 if backward else 0
+        out = torch.empty(self.rows, dtype=torch.float32, device=self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self.lib.ssb_shard_carry_peer_f32(self._byref(self.struct), self.epoch[d], d, out.data_ptr(), stream))
+        return out
+
+    @staticmethod
+    def usable_for(gate: torch.Tensor) -> bool:
+        """The publishing map kernel takes 16-byte aligned fp32 rows of a multiple of 4 steps."""
+        return gate.dtype == torch.float32 and gate.shape[1] % 4 == 0 and gate.data_ptr() % 16 == 0
+
+
 def _gather_maps(agg: torch.Tensor, group) -> torch.Tensor:
     """all_gather of the per-row maps -> ``[world, rows, 2]`` (identity for a single rank)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -104,30 +198,40 @@ def _rank(group) -> int:
 
 
 def sharded_scan_forward(gate: torch.Tensor, value: torch.Tensor, group=None, ops: Any = CudaShardOps,
-                         cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None
-                         ) -> Tuple[torch.Tensor, torch.Tensor]:
+                         cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None,
+                         exchange: Optional["PeerCarryExchange"] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Forward of this rank's T-slice. ``gate``/``value``: ``[rows, T_local]`` contiguous.
 
     Returns ``(h_local, h_in)`` where ``h_in`` (``[rows]``) is h just before the slice.  ``cut``:
     see the module docstring.  ``walked``: optional one-element int64 tensor on the inputs' device
-    that accumulates how many elements per tensor the map pass read.
+    that accumulates how many elements per tensor the map pass read.  ``exchange``: a
+    :class:`PeerCarryExchange` made for this group and row count replaces the all-gather by peer
+    stores (every rank has to pass one, or none).
     """
     assert gate.shape == value.shape and gate.dim() == 2
     gate, value = gate.contiguous(), value.contiguous()
-    maps = _gather_maps(ops.map_forward(gate, value, cut, walked), group)
-    h_in = ops.carry(maps, _rank(group), False)
+    if exchange is not None and exchange.usable_for(gate) and value.data_ptr() % 16 == 0:
+        exchange.publish_map(gate, value, False, cut, walked)
+        h_in = exchange.carry(False)
+    else:
+        maps = _gather_maps(ops.map_forward(gate, value, cut, walked), group)
+        h_in = ops.carry(maps, _rank(group), False)
     return ops.scan_forward(gate, value, h_in), h_in
 
 
 def sharded_scan_backward(gate: torch.Tensor, output: torch.Tensor, out_grad: torch.Tensor,
                           h_in: torch.Tensor, group=None, ops: Any = CudaShardOps,
-                          cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None
-                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+                          cut: float = DEFAULT_CUT, walked: Optional[torch.Tensor] = None,
+                          exchange: Optional["PeerCarryExchange"] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Backward of this rank's T-slice; ``h_in`` is what :func:`sharded_scan_forward` returned."""
     assert gate.shape == output.shape == out_grad.shape and gate.dim() == 2
     gate, output, out_grad = gate.contiguous(), output.contiguous(), out_grad.contiguous()
-    maps = _gather_maps(ops.map_backward(gate, out_grad, cut, walked), group)
-    c_in = ops.carry(maps, _rank(group), True)
+    if exchange is not None and exchange.usable_for(gate) and out_grad.data_ptr() % 16 == 0:
+        exchange.publish_map(gate, out_grad, True, cut, walked)
+        c_in = exchange.carry(True)
+    else:
+        maps = _gather_maps(ops.map_backward(gate, out_grad, cut, walked), group)
+        c_in = ops.carry(maps, _rank(group), True)
     return ops.scan_backward(gate, output, out_grad, c_in, h_in)
 
 
@@ -135,27 +239,29 @@ class ShardedScan(torch.autograd.Function):
     """Autograd Function over the local slice; gradients stay sharded like the inputs."""
 
     @staticmethod
-    def forward(ctx: Any, gate: torch.Tensor, value: torch.Tensor, group, ops, cut: float) -> torch.Tensor:
+    def forward(ctx: Any, gate: torch.Tensor, value: torch.Tensor, group, ops, cut: float, exchange) -> torch.Tensor:
         rows_shape = gate.shape
         g2, v2 = gate.reshape(-1, rows_shape[-1]), value.reshape(-1, rows_shape[-1])
-        out, h_in = sharded_scan_forward(g2, v2, group, ops, cut)
+        out, h_in = sharded_scan_forward(g2, v2, group, ops, cut, exchange=exchange)
         ctx.save_for_backward(g2, out, h_in)
-        ctx.group, ctx.ops, ctx.rows_shape, ctx.cut = group, ops, rows_shape, cut
+        ctx.group, ctx.ops, ctx.rows_shape, ctx.cut, ctx.exchange = group, ops, rows_shape, cut, exchange
         return out.reshape(rows_shape)
 
     @staticmethod
     def backward(ctx: Any, output_grad: torch.Tensor):
         gate, out, h_in = ctx.saved_tensors
-        gg, gv = sharded_scan_backward(gate, out, output_grad.reshape(gate.shape), h_in, ctx.group, ctx.ops, ctx.cut)
-        return gg.reshape(ctx.rows_shape), gv.reshape(ctx.rows_shape), None, None, None
+        gg, gv = sharded_scan_backward(gate, out, output_grad.reshape(gate.shape), h_in, ctx.group, ctx.ops, ctx.cut,
+                                       exchange=ctx.exchange)
+        return gg.reshape(ctx.rows_shape), gv.reshape(ctx.rows_shape), None, None, None, None
 
 
 def scan_sequence_parallel(gate: torch.Tensor, value: torch.Tensor, group: Optional[Any] = None,
-                           ops: Any = CudaShardOps, cut: float = DEFAULT_CUT) -> torch.Tensor:
+                           ops: Any = CudaShardOps, cut: float = DEFAULT_CUT,
+                           exchange: Optional[PeerCarryExchange] = None) -> torch.Tensor:
     """``scan`` for a sequence sharded along its last axis over ``group`` (default: the world).
 
     Every rank passes its own ``[N, ..., T_local]`` slice (slices in rank order form the full
     sequence) and receives the matching slice of the result.
     """
     assert gate.shape == value.shape and gate.dim() >= 2
-    return ShardedScan.apply(gate, value, group, ops, cut)
+    return ShardedScan.apply(gate, value, group, ops, cut, exchange)

@@ -356,6 +356,55 @@ def test_virtual_t_shards_through_the_sharded_module(gates, n_shards, cut):
     _gpu.device_ok()
 
 
+def test_peer_exchange_emulated_on_one_gpu():
+    """ssb_shard_map_publish_f32 / ssb_shard_carry_peer_f32 with four "ranks" that are four buffers on
+    ONE device: every rank's publish is launched before any rank's carry, so no kernel ever waits for
+    a later launch (the flags it polls are already up).  Three epochs in a row exercise both slot
+    generations and the reuse of a slot; carries are compared with ssb_shard_carry_f32 on the maps
+    of the collective path."""
+    lib = _native.load()
+    world, rows, step = 4, 40, 8192
+    a, b, g = make_inputs("nearunit", (rows, step * world), seed=17)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    nbytes = lib.ssb_peer_exchange_bytes(world, rows)
+    assert nbytes > 0 and lib.ssb_peer_exchange_bytes(9, rows) == 0
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    structs = []
+    for r in range(world):
+        ex = _native.PeerExchangeStruct()
+        ex.world, ex.rank, ex.rows = world, r, rows
+        for q in range(world):
+            ex.buffers[q] = bufs[q].data_ptr()
+        structs.append(ex)
+    st = _native.stream_of(da)
+    cut = 2.0 ** -40
+    for epoch in (1, 2, 3):
+        scale = float(epoch)  # different data every epoch: a stale slot would show
+        parts = [[(x[:, r * step:(r + 1) * step] * (scale if i else 1.0)).contiguous() for i, x in enumerate((da, db, dg))]
+                 for r in range(world)]
+        for backward in (0, 1):
+            ref_maps = torch.empty(world, rows, 2, device="cuda")
+            for r, (pa, pb, pg) in enumerate(parts):
+                other = pg if backward else pb
+                fn = lib.ssb_shard_map_bwd_f32 if backward else lib.ssb_shard_map_fwd_f32
+                _native.check(fn(pa.data_ptr(), other.data_ptr(), ref_maps[r].data_ptr(), rows, step, cut, None, st))
+                _native.check(lib.ssb_shard_map_publish_f32(pa.data_ptr(), other.data_ptr(), rows, step, cut, backward,
+                                                            _native.ctypes.byref(structs[r]), epoch, None, st))
+            for r in range(world):
+                got, want = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+                _native.check(lib.ssb_shard_carry_peer_f32(_native.ctypes.byref(structs[r]), epoch, backward, got.data_ptr(), st))
+                _native.check(lib.ssb_shard_carry_f32(ref_maps.data_ptr(), world, r, backward, rows, want.data_ptr(), st))
+                assert torch.equal(got, want), (epoch, backward, r, float((got - want).abs().max()))
+    # refusals: a shape the publishing kernel does not take, a descriptor that makes no sense
+    odd = torch.rand(rows, 1001, device="cuda")
+    assert lib.ssb_shard_map_publish_f32(odd.data_ptr(), odd.data_ptr(), rows, 1001, cut, 0, _native.ctypes.byref(structs[0]), 4,
+                                         None, st) == _native.ERR_UNSUPPORTED
+    bad = _native.PeerExchangeStruct()
+    bad.world, bad.rank, bad.rows = 4, 7, rows
+    assert lib.ssb_shard_carry_peer_f32(_native.ctypes.byref(bad), 1, 0, odd.data_ptr(), st) == _native.ERR_BAD_ARG
+    _gpu.device_ok()
+
+
 def test_cfg3_full_size_under_auto_sampled():
     """cfg3 as configured -- [1024, 2^20], near-unit gates, the kernels AUTO picks at that size --
     at full size on the GPU; a strided sample of 16 rows against the oracle, the backward fed with

@@ -24,20 +24,28 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, gates, rows, steps, out_dir):
+def _worker(rank, world, port, gates, rows, steps, out_dir, peer=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from scanscam_b200 import sharded
+        from scanscam_b200 import _native, sharded
 
+        exchange = None
+        if peer:  # the exchange through peer memory instead of the all-gather
+            exchange = sharded.PeerCarryExchange.create(rows)
+            assert exchange is not None, "peer memory exchange could not be set up on this box"
         a, b, g = make_inputs(gates, (rows, steps), seed=3)
         lo, hi = rank * steps // world, (rank + 1) * steps // world
-        a_l = a[:, lo:hi].contiguous().cuda().requires_grad_(True)
-        b_l = b[:, lo:hi].contiguous().cuda().requires_grad_(True)
-        h_l = sharded.scan_sequence_parallel(a_l, b_l)
-        h_l.backward(g[:, lo:hi].contiguous().cuda())
+        dist.barrier()  # the ranks start their first call together (the peers' waits are bounded at a second)
+        for rep in range(3 if peer else 1):  # several calls in a row: both slot generations, slot reuse
+            a_l = a[:, lo:hi].contiguous().cuda().requires_grad_(True)
+            b_l = b[:, lo:hi].contiguous().cuda().requires_grad_(True)
+            h_l = sharded.scan_sequence_parallel(a_l, b_l, exchange=exchange)
+            h_l.backward(g[:, lo:hi].contiguous().cuda())
         torch.cuda.synchronize()
+        detail = _native.ctypes.c_int(0)
+        _native.check(_native.load().ssb_device_status(_native.ctypes.byref(detail)))  # no wait ran out
         torch.save({"h": h_l.detach().cpu(), "ga": a_l.grad.cpu(), "gb": b_l.grad.cpu()},
                    os.path.join(out_dir, f"r{rank}.pt"))
     finally:
@@ -47,12 +55,23 @@ def _worker(rank, world, port, gates, rows, steps, out_dir):
 @pytest.mark.parametrize("gates,rows,steps", [("nearunit", 64, 32768), ("sigmoid2", 33, 4096), ("resets", 16, 8200),
                                               ("nearunit", 40, 131072), ("randn", 16, 8192), ("ones", 8, 4096)])
 def test_sequence_parallel_scan_on_nccl(tmp_path, gates, rows, steps):
+    _run_and_check(tmp_path, gates, rows, steps, peer=False)
+
+
+@pytest.mark.parametrize("gates,rows,steps", [("nearunit", 40, 131072), ("randn", 16, 8192), ("ones", 8, 4096)])
+def test_sequence_parallel_scan_through_peer_memory(tmp_path, gates, rows, steps):
+    """The same operator with the shard maps exchanged by peer stores and flags instead of NCCL
+    (PeerCarryExchange): one process per GPU, every wait bounded, three calls in a row."""
+    _run_and_check(tmp_path, gates, rows, steps, peer=True)
+
+
+def _run_and_check(tmp_path, gates, rows, steps, peer):
     world = min(torch.cuda.device_count(), 8)  # every GPU of the box, up to eight
     if world < 2:
         pytest.skip("needs at least two GPUs")
     while steps % world:
         world -= 1
-    mp.spawn(_worker, args=(world, _free_port(), gates, rows, steps, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), gates, rows, steps, str(tmp_path), peer), nprocs=world, join=True)
     parts = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     h = torch.cat([p["h"] for p in parts], dim=1).numpy()
     ga = torch.cat([p["ga"] for p in parts], dim=1).numpy()
