@@ -416,6 +416,11 @@ typedef struct ssb_peer_exchange {
     void *buffers[8];
 } ssb_peer_exchange_t;
 size_t ssb_peer_exchange_bytes(int world, int64_t rows);
+/* Lets kernels of the CURRENT device load from and store to memory of `peer_device` (the two must be
+ * peer-capable: NVLink or PCIe peer-to-peer).  Mapping another process's allocation into this
+ * process (CUDA IPC) places it on the device it was allocated on and does not by itself open that
+ * device to this one: call this once per peer before the first ssb_shard_map_publish_f32.  Idempotent. */
+int ssb_enable_peer_access(int peer_device);
 int ssb_shard_map_publish_f32(const float *gate, const float *other, int64_t rows, int64_t T, float cut, int backward,
                               const ssb_peer_exchange_t *exchange, unsigned epoch, unsigned long long *walked,
                               void *stream);

@@ -2073,6 +2073,25 @@ size_t ssb_peer_exchange_bytes(int world, int64_t rows) {
     return ssb::shard::px_total_bytes(world, rows);
 }
 
+int ssb_enable_peer_access(int peer_device) {
+    int dev = -1, can = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (peer_device == dev) return SSB_OK;
+    e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+    if (e != cudaSuccess || !can) {
+        (void)cudaGetLastError();
+        return fail(SSB_ERR_UNSUPPORTED, "device %d cannot access device %d as a peer", dev, peer_device);
+    }
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return SSB_OK;
+    }
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaDeviceEnablePeerAccess(%d) from device %d: %s", peer_device, dev, cudaGetErrorString(e));
+    return SSB_OK;
+}
+
 int ssb_shard_map_publish_f32(const float *gate, const float *other, int64_t rows, int64_t T, float cut, int backward,
                               const ssb_peer_exchange_t *exchange, unsigned epoch, unsigned long long *walked, void *stream) {
     int64_t n;

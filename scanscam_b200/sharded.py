@@ -127,6 +127,14 @@ class PeerCarryExchange:
             handles = [None] * self.world
             dist.all_gather_object(handles, args, group=group)
             self.peers = [self.buffer if r == self.rank else rebuild_cuda_tensor(*handles[r]) for r in range(self.world)]
+            # A mapped buffer lives on its owner's device; kernels of THIS device may touch it only once
+            # peer access to that device is switched on in this process.
+            with torch.cuda.device(self.device):
+                for r, t in enumerate(self.peers):
+                    if t.device != self.device:
+                        _native.check(self.lib.ssb_enable_peer_access(t.device.index))
+                    elif r != self.rank:
+                        raise RuntimeError("two ranks share one GPU: the peer exchange needs one process per GPU")
         self.struct = _native.PeerExchangeStruct()
         self.struct.world, self.struct.rank, self.struct.rows = self.world, self.rank, self.rows
         for r, t in enumerate(self.peers):
