@@ -529,7 +529,8 @@ def measure_t_sharded(args, torch, dist, timer, lib, native, workloads, world, r
                     "max_err_vs_unsharded": p_err, "launches_per_step_per_rank": 6,
                     "what": "map kernels store into every rank's buffer over NVLink and raise a flag; the carry kernels wait "
                             "(bounded) for all ranks' flags: no collective call"}
-            del exchange
+            timer.barrier()
+            exchange.close()
     except Exception as exc:
         peer = {"failed": f"{type(exc).__name__}: {exc}"}
     del a, b, g

@@ -395,9 +395,9 @@ int ssb_shard_map_bwd_f32(const float *gate, const float *gout, float *agg, int6
  *
  *   ssb_peer_exchange_t: `world` <= 8 ranks, this process's `rank`, `rows`, and for every rank r
  *     `buffers[r]` = the address, in THIS process, of rank r's exchange buffer of
- *     ssb_peer_exchange_bytes(world, rows) bytes (rank's own: an ordinary device allocation; the
- *     others': mapped through CUDA IPC or any other peer mapping).  Zero the buffers once, and
- *     synchronise all ranks, before the first call.
+ *     ssb_peer_exchange_bytes(world, rows) bytes (the rank's own from ssb_peer_buffer_create, the
+ *     others' from ssb_peer_buffer_open, or any other zeroed allocation / peer mapping that kernels
+ *     of this device can address).  Synchronise all ranks after mapping, before the first call.
  *   ssb_shard_map_publish_f32: as ssb_shard_map_fwd/bwd_f32 (`backward` selects the recurrence);
  *     every row's map goes to slot [direction][epoch & 1][rank] of every rank's buffer, and the
  *     last CTA to finish raises flag = epoch at every rank.  T % 4 == 0, 16-byte aligned tensors
@@ -416,11 +416,20 @@ typedef struct ssb_peer_exchange {
     void *buffers[8];
 } ssb_peer_exchange_t;
 size_t ssb_peer_exchange_bytes(int world, int64_t rows);
-/* Lets kernels of the CURRENT device load from and store to memory of `peer_device` (the two must be
- * peer-capable: NVLink or PCIe peer-to-peer).  Mapping another process's allocation into this
- * process (CUDA IPC) places it on the device it was allocated on and does not by itself open that
- * device to this one: call this once per peer before the first ssb_shard_map_publish_f32.  Idempotent. */
-int ssb_enable_peer_access(int peer_device);
+/* Set-up helpers for the exchange buffers (called once per job, not per step; these four are the
+ * only entry points of the library that allocate or map device memory).
+ *   ssb_peer_buffer_create: allocates `bytes` of zeroed device memory on the current device
+ *     (cudaMalloc, so that the allocation is exportable as a whole) and writes its 64-byte CUDA IPC
+ *     handle, to be sent to the other ranks by any means.
+ *   ssb_peer_buffer_open: maps another process's buffer from its handle WITH THIS PROCESS'S OWN DEVICE
+ *     CURRENT, which is what makes it addressable by kernels of this device (peer access between
+ *     the two devices is switched on as needed); the two devices must be peer-capable.
+ *   ssb_peer_buffer_close / ssb_peer_buffer_destroy: unmap a peer's buffer / free the own one. */
+#define SSB_IPC_HANDLE_BYTES 64
+int ssb_peer_buffer_create(size_t bytes, void **ptr, unsigned char handle[SSB_IPC_HANDLE_BYTES]);
+int ssb_peer_buffer_open(const unsigned char handle[SSB_IPC_HANDLE_BYTES], void **ptr);
+int ssb_peer_buffer_close(void *ptr);
+int ssb_peer_buffer_destroy(void *ptr);
 int ssb_shard_map_publish_f32(const float *gate, const float *other, int64_t rows, int64_t T, float cut, int backward,
                               const ssb_peer_exchange_t *exchange, unsigned epoch, unsigned long long *walked,
                               void *stream);

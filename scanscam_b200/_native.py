@@ -77,7 +77,10 @@ SIGNATURES = {
     "ssb_shard_map_fwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_shard_map_bwd_f32": (_int, [_p, _p, _p, _i64, _i64, ctypes.c_float, _p, _p]),
     "ssb_peer_exchange_bytes": (_sz, [_int, _i64]),
-    "ssb_enable_peer_access": (_int, [_int]),
+    "ssb_peer_buffer_create": (_int, [_sz, ctypes.POINTER(_p), ctypes.c_char_p]),
+    "ssb_peer_buffer_open": (_int, [ctypes.c_char_p, ctypes.POINTER(_p)]),
+    "ssb_peer_buffer_close": (_int, [_p]),
+    "ssb_peer_buffer_destroy": (_int, [_p]),
     "ssb_shard_map_publish_f32": (_int, [_p, _p, _i64, _i64, ctypes.c_float, _int, _p, ctypes.c_uint, _p, _p]),
     "ssb_shard_carry_peer_f32": (_int, [_p, ctypes.c_uint, _int, _p, _p]),
     "ssb_selftest_wait_timeout": (_int, [_p, _sz, _p]),

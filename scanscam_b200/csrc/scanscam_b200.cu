@@ -2073,22 +2073,55 @@ size_t ssb_peer_exchange_bytes(int world, int64_t rows) {
     return ssb::shard::px_total_bytes(world, rows);
 }
 
-int ssb_enable_peer_access(int peer_device) {
-    int dev = -1, can = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
-    if (peer_device == dev) return SSB_OK;
-    e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
-    if (e != cudaSuccess || !can) {
-        (void)cudaGetLastError();
-        return fail(SSB_ERR_UNSUPPORTED, "device %d cannot access device %d as a peer", dev, peer_device);
+static_assert(sizeof(cudaIpcMemHandle_t) == SSB_IPC_HANDLE_BYTES, "the header's handle size is CUDA's");
+
+int ssb_peer_buffer_create(size_t bytes, void **ptr, unsigned char handle[SSB_IPC_HANDLE_BYTES]) {
+    if (ptr == nullptr || handle == nullptr || bytes == 0) return fail(SSB_ERR_BAD_ARG, "ssb_peer_buffer_create: NULL argument or zero size");
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    cudaIpcMemHandle_t h;
+    if ((e = cudaMemset(p, 0, bytes)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess ||
+        (e = cudaIpcGetMemHandle(&h, p)) != cudaSuccess) {
+        (void)cudaFree(p);
+        return fail(SSB_ERR_LAUNCH, "exchange buffer set-up: %s", cudaGetErrorString(e));
     }
-    e = cudaDeviceEnablePeerAccess(peer_device, 0);
-    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return SSB_OK;
+}
+
+int ssb_peer_buffer_open(const unsigned char handle[SSB_IPC_HANDLE_BYTES], void **ptr) {
+    if (ptr == nullptr || handle == nullptr) return fail(SSB_ERR_BAD_ARG, "ssb_peer_buffer_open: NULL argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);  // mapped for the CURRENT device
+    if (e != cudaSuccess) {
         (void)cudaGetLastError();
-        return SSB_OK;
+        return fail(SSB_ERR_LAUNCH, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
     }
-    if (e != cudaSuccess) return fail(SSB_ERR_LAUNCH, "cudaDeviceEnablePeerAccess(%d) from device %d: %s", peer_device, dev, cudaGetErrorString(e));
+    *ptr = p;
+    return SSB_OK;
+}
+
+int ssb_peer_buffer_close(void *ptr) {
+    if (ptr == nullptr) return SSB_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(SSB_ERR_LAUNCH, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+    }
+    return SSB_OK;
+}
+
+int ssb_peer_buffer_destroy(void *ptr) {
+    if (ptr == nullptr) return SSB_OK;
+    cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(SSB_ERR_LAUNCH, "cudaFree: %s", cudaGetErrorString(e));
+    }
     return SSB_OK;
 }
 

@@ -98,18 +98,17 @@ class PeerCarryExchange:
     (``ssb_shard_map_publish_f32`` / ``ssb_shard_carry_peer_f32``).  Two kernel launches per
     direction before the scan instead of map, all-gather, carry.
 
-    Needs one process per GPU on one node, every process seeing all the GPUs under the same
-    indices, and peer access between them; the buffers are exchanged once, here, as CUDA IPC
-    handles through the process group.  ``PeerCarryExchange.create`` returns ``None`` where that
+    Needs one process per GPU on one node and peer access between the GPUs; each rank allocates its
+    buffer with ``ssb_peer_buffer_create`` and maps the others' from their CUDA IPC handles, sent once,
+    here, through the process group, with its own device current (``ssb_peer_buffer_open``).  ``PeerCarryExchange.create`` returns ``None`` where that
     is not possible (the callers then keep the collective path).  All ranks must make the same
     sequence of forward / backward calls with an exchange object: the epochs are counted locally.
     """
 
     def __init__(self, rows: int, group=None, device: Optional[torch.device] = None):
-        from torch.multiprocessing.reductions import rebuild_cuda_tensor, reduce_tensor
-
         from . import _native
 
+        ct = _native.ctypes
         self.lib = _native.load()
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -119,31 +118,55 @@ class PeerCarryExchange:
         nbytes = self.lib.ssb_peer_exchange_bytes(self.world, self.rows)
         if nbytes == 0:
             raise ValueError(f"peer exchange supports 1..8 ranks and at least one row (world={self.world}, rows={rows})")
-        self.buffer = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
-        torch.cuda.synchronize(self.device)
-        self.peers = [self.buffer] * self.world
-        if self.world > 1:
-            _, args = reduce_tensor(self.buffer)
-            handles = [None] * self.world
-            dist.all_gather_object(handles, args, group=group)
-            self.peers = [self.buffer if r == self.rank else rebuild_cuda_tensor(*handles[r]) for r in range(self.world)]
-            # A mapped buffer lives on its owner's device; kernels of THIS device may touch it only once
-            # peer access to that device is switched on in this process.
-            with torch.cuda.device(self.device):
-                for r, t in enumerate(self.peers):
-                    if t.device != self.device:
-                        _native.check(self.lib.ssb_enable_peer_access(t.device.index))
-                    elif r != self.rank:
-                        raise RuntimeError("two ranks share one GPU: the peer exchange needs one process per GPU")
+        self._own = ct.c_void_p()
+        self._mapped = []
+        handle = ct.create_string_buffer(64)
+        problem = None  # every rank walks through the same collectives whatever goes wrong locally
+        with torch.cuda.device(self.device):  # allocate, and map the peers' buffers, with THIS rank's device current
+            if self.lib.ssb_peer_buffer_create(nbytes, ct.byref(self._own), handle) != _native.OK:
+                problem = self.lib.ssb_last_error().decode()
+            pointers = [self._own.value] * self.world
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, (handle.raw if problem is None else None, self.device.index), group=group)
+                if problem is None and any(raw is None for raw, _ in handles):
+                    problem = "another rank could not allocate its exchange buffer"
+                if problem is None and len({dev for _, dev in handles}) != self.world:
+                    problem = "two ranks share one GPU: the peer exchange needs one process per GPU"
+                for r, (raw, _) in enumerate(handles):
+                    if problem is None and r != self.rank:
+                        p = ct.c_void_p()
+                        if self.lib.ssb_peer_buffer_open(raw, ct.byref(p)) != _native.OK:
+                            problem = self.lib.ssb_last_error().decode()
+                        else:
+                            self._mapped.append(p)
+                            pointers[r] = p.value
+                agree = torch.tensor([0 if problem is None else 1], device=self.device)
+                dist.all_reduce(agree, op=dist.ReduceOp.MAX, group=group)  # also: every buffer is zeroed and mapped everywhere
+                if int(agree.item()) != 0 and problem is None:
+                    problem = "another rank could not map the exchange buffers"
+        if problem is not None:
+            self.close()
+            raise RuntimeError(f"peer exchange set-up failed: {problem}")
         self.struct = _native.PeerExchangeStruct()
         self.struct.world, self.struct.rank, self.struct.rows = self.world, self.rank, self.rows
-        for r, t in enumerate(self.peers):
-            self.struct.buffers[r] = t.data_ptr()
+        for r, p in enumerate(pointers):
+            self.struct.buffers[r] = p
         self.epoch = [0, 0]  # forward, backward
-        if self.world > 1:
-            dist.barrier(group=group)  # every buffer is zeroed and mapped everywhere before anyone publishes
         self._check = _native.check
-        self._byref = _native.ctypes.byref
+        self._byref = ct.byref
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees the own one.  Collective in effect: call it on every
+        rank, after the last step has completed everywhere (e.g. behind a barrier)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._mapped:
+                self.lib.ssb_peer_buffer_close(p)
+            self._mapped = []
+            if self._own is not None and self._own.value:
+                self.lib.ssb_peer_buffer_destroy(self._own)
+            self._own = None
 
     @classmethod
     def create(cls, rows: int, group=None, device: Optional[torch.device] = None) -> Optional["PeerCarryExchange"]:
@@ -151,21 +174,20 @@ class PeerCarryExchange:
         ranks, fewer visible GPUs than ranks, no peer access, IPC refused).  Collective: call it on
         every rank of the group."""
         world = dist.get_world_size(group) if dist.is_initialized() else 1
-        ok = torch.cuda.is_available() and world <= 8 and torch.cuda.device_count() >= world
+        ok = torch.cuda.is_available() and world <= 8
         if ok and world > 1:
             me = torch.cuda.current_device()
             ok = all(torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
-        ex = None
-        if ok:
-            try:
-                ex = cls(rows, group, device)
-            except Exception:  # an IPC refusal on one rank must not leave the others with an exchange
-                ex = None
-        if world > 1:
-            agree = torch.tensor([1 if ex is not None else 0], device="cuda")
+        if world > 1:  # all ranks or none: the constructor is collective
+            agree = torch.tensor([1 if ok else 0], device="cuda")
             dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
-            if int(agree.item()) == 0:
-                ex = None
+            ok = int(agree.item()) == 1
+        if not ok:
+            return None
+        try:
+            ex = cls(rows, group, device)  # raises on every rank or on none
+        except RuntimeError:
+            ex = None
         return ex
 
     def publish_map(self, gate: torch.Tensor, other: torch.Tensor, backward: bool, cut: float,

@@ -48,6 +48,9 @@ def _worker(rank, world, port, gates, rows, steps, out_dir, peer=False):
         _native.check(_native.load().ssb_device_status(_native.ctypes.byref(detail)))  # no wait ran out
         torch.save({"h": h_l.detach().cpu(), "ga": a_l.grad.cpu(), "gb": b_l.grad.cpu()},
                    os.path.join(out_dir, f"r{rank}.pt"))
+        if exchange is not None:
+            dist.barrier()  # nobody unmaps while a peer may still be storing
+            exchange.close()
     finally:
         dist.destroy_process_group()
 
