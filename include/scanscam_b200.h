@@ -10,9 +10,10 @@
  * its kernels on that stream without synchronising, and returns an `ssb_status_t`.
  * Outputs are caller-allocated, as in the reference extension, whose functions all
  * have the shape `void f(Tensor inputs..., Tensor outputs...)`
- * (reference: src/scanscam_cuda.cu:725-737).  No entry point allocates device
+ * (reference: src/scanscam_cuda.cu:725-737).  No compute entry point allocates device
  * memory; the ones that need scratch take it from the caller (see
- * ssb_scan_workspace_bytes).  No torch types appear here: the PyTorch extension
+ * ssb_scan_workspace_bytes).  (The set-up helpers ssb_peer_buffer_* of the multi-GPU
+ * exchange are the exception, and say so.)  No torch types appear here: the PyTorch extension
  * `scanscam_ext` and any other FFI binding (ctypes, cgo, JNI ...) are equal clients.
  *
  * "rows" layout   : dense [rows, T], scan axis innermost and contiguous.
