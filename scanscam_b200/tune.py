@@ -6,6 +6,7 @@
     python -m scanscam_b200.tune h16:16384x4096                       (bf16 / fp16 storage beside fp32)
     python -m scanscam_b200.tune clh16:64x4096x512                    (the same for channels-last)
     python -m scanscam_b200.tune shard:1024x131072                    (shard maps of a T-sharded sequence)
+    python -m scanscam_b200.tune f64:16384x4096,clf64:64x4096x512     (the fp64 entry points)
 
 For each shape (a named workload or ROWSxT) and variant it reports the best of three groups of
 ``iters`` back-to-back launches, forward and backward separately, timed with CUDA events, as
@@ -245,7 +246,53 @@ def time_16bit(lib, rows, T, iters):
     return out
 
 
-MODES = {"fused": 2, "h16": 2, "clh16": 3, "cl": 3, "shard": 2}  # prefix -> number of extents
+def time_fp64(lib, extents, iters):
+    """Kernel times of the fp64 entry points: rows layout (ROWSxT; without and with scratch) or
+    channels-last (NxTxC)."""
+    st = torch.cuda.current_stream().cuda_stream
+    shape = tuple(extents)
+    a = torch.rand(*shape, device="cuda", dtype=torch.float64) * 0.2 + 0.8
+    b, g = torch.randn_like(a), torch.randn_like(a)
+    h, ga, gb = (torch.empty_like(a) for _ in range(3))
+    p = [t.data_ptr() for t in (a, b, g, h, ga, gb)]
+    n = a.numel()
+
+    def run(fn):
+        for _ in range(3):
+            _native.check(fn())
+        best = float("inf")
+        for _ in range(3):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / iters)
+        return best
+
+    out = []
+    if len(shape) == 3:
+        N, T, C = shape
+        tf = run(lambda: lib.ssb_scan_cl_fwd_f64(p[0], p[1], p[3], N, T, C, st))
+        tb = run(lambda: lib.ssb_scan_cl_bwd_f64(p[0], p[3], p[2], p[4], p[5], N, T, C, st))
+        out.append(("f64 channels-last", 24 * n / tf / 1e6, tf, 40 * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+        return out
+    rows, T = shape
+    tf = run(lambda: lib.ssb_scan_fwd_f64(p[0], p[1], p[3], rows, T, None, st))
+    tb = run(lambda: lib.ssb_scan_bwd_f64(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, st))
+    out.append(("f64", 24 * n / tf / 1e6, tf, 40 * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+    need = lib.ssb_scan_f64_workspace_bytes(rows, T)
+    if need:
+        ws = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+        tf = run(lambda: lib.ssb_scan_fwd_f64_ex(p[0], p[1], p[3], rows, T, None, ws.data_ptr(), need, st))
+        tb = run(lambda: lib.ssb_scan_bwd_f64_ex(p[0], p[3], p[2], p[4], p[5], rows, T, None, None, ws.data_ptr(), need, st))
+        out.append(("f64 with scratch", 24 * n / tf / 1e6, tf, 40 * n / tb / 1e6, tb, n / (tf + tb) / 1e6))
+    return out
+
+
+MODES = {"fused": 2, "h16": 2, "clh16": 3, "cl": 3, "shard": 2, "f64": 2, "clf64": 3}  # prefix -> number of extents
 
 
 def parse_shape(name: str):
@@ -268,7 +315,7 @@ def parse_shape(name: str):
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("shapes", help="comma-separated: a workload name, ROWSxT, cl:NxTxC, fused:ROWSxT, h16:ROWSxT, "
-                                   "clh16:NxTxC, shard:ROWSxT")
+                                   "clh16:NxTxC, shard:ROWSxT, f64:ROWSxT, clf64:NxTxC")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--families", default="warp,flat,tma,lookback")
     ap.add_argument("--json", default=None)
@@ -317,6 +364,13 @@ def main(argv=None):
             for label, ms, steps in time_shard_maps(lib, rows, T, args.iters):
                 results[f"{name}/{label}"] = {"ms": ms, "steps_walked_per_row": steps}
                 print(f"{label:28s} {ms:8.4f} ms  {steps:10.0f} steps walked per row", flush=True)
+            continue
+        if mode in ("f64", "clf64"):  # fp64 entry points: f64:ROWSxT, clf64:NxTxC
+            print(f"# fp64, {'[N,T,C]' if mode == 'clf64' else 'rows x T'} = {'x'.join(map(str, extents))}")
+            print(f"{'entry points':18s} {'fwd GB/s':>9s} {'fwd ms':>8s} {'bwd GB/s':>9s} {'bwd ms':>8s} {'Gelem/s':>8s}")
+            for label, fg, tf, bg, tb, ge in time_fp64(lib, extents, args.iters):
+                results[f"{name}/{label}"] = {"fwd": {"ms": tf, "GBps": fg}, "bwd": {"ms": tb, "GBps": bg}, "gelem_s": ge}
+                print(f"{label:18s} {fg:9.0f} {tf:8.4f} {bg:9.0f} {tb:8.4f} {ge:8.1f}", flush=True)
             continue
         if name.startswith("fused:"):  # gate logits in: fused:ROWSxT
             rows, T = (int(v) for v in name[6:].lower().split("x"))
