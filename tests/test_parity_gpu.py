@@ -356,14 +356,15 @@ def test_virtual_t_shards_through_the_sharded_module(gates, n_shards, cut):
     _gpu.device_ok()
 
 
-def test_peer_exchange_emulated_on_one_gpu():
-    """ssb_shard_map_publish_f32 / ssb_shard_carry_peer_f32 with four "ranks" that are four buffers on
+@pytest.mark.parametrize("world,rows,step", [(4, 40, 8192), (8, 700, 2048), (2, 257, 4096)])
+def test_peer_exchange_emulated_on_one_gpu(world, rows, step):
+    """ssb_shard_map_publish_f32 / ssb_shard_carry_peer_f32 with `world` "ranks" that are buffers on
     ONE device: every rank's publish is launched before any rank's carry, so no kernel ever waits for
     a later launch (the flags it polls are already up).  Three epochs in a row exercise both slot
     generations and the reuse of a slot; carries are compared with ssb_shard_carry_f32 on the maps
-    of the collective path."""
+    of the collective path.  The largest supported world (8) and row counts that need several CTAs
+    of the carry kernel are among the cases."""
     lib = _native.load()
-    world, rows, step = 4, 40, 8192
     a, b, g = make_inputs("nearunit", (rows, step * world), seed=17)
     da, db, dg = a.cuda(), b.cuda(), g.cuda()
     nbytes = lib.ssb_peer_exchange_bytes(world, rows)
@@ -400,7 +401,7 @@ def test_peer_exchange_emulated_on_one_gpu():
     assert lib.ssb_shard_map_publish_f32(odd.data_ptr(), odd.data_ptr(), rows, 1001, cut, 0, _native.ctypes.byref(structs[0]), 4,
                                          None, st) == _native.ERR_UNSUPPORTED
     bad = _native.PeerExchangeStruct()
-    bad.world, bad.rank, bad.rows = 4, 7, rows
+    bad.world, bad.rank, bad.rows = world, world + 3, rows
     assert lib.ssb_shard_carry_peer_f32(_native.ctypes.byref(bad), 1, 0, odd.data_ptr(), st) == _native.ERR_BAD_ARG
     _gpu.device_ok()
 
