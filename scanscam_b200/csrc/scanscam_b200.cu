@@ -727,6 +727,11 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
     if (all_aligned16 && rows >= (backward ? 1024 : 2048) && T >= 16384 && T % 4096 == 0 && T / 4096 <= 0x7fffffffLL &&
         rows <= 0x7fffffffLL && encode_fn() != nullptr)
         return SSB_VARIANT_TMA | (kTmaFlatLongId << 8);
+    // Forward, about a thousand long rows (too few for the sweep above): the per-warp ring of 16-warp
+    // CTAs beats look-back by 4-6 % from 65536 steps up (6.46 / 6.61 against 6.10 / 6.30 TB/s at
+    // 1024 x 65536 / 131072); at 1536 rows look-back is ahead again (6.1-6.3 against 5.9).
+    if (!backward && all_aligned16 && tma_eligible(rows, T) && T >= 65536 && rows >= 1024 && rows < 1280 && encode_fn() != nullptr)
+        return SSB_VARIANT_TMA | (10 << 8);
     if (all_aligned16 && tma_eligible(rows, T) && T >= 262144 && rows >= 1024) return SSB_VARIANT_TMA | (1 << 8);
     // A few very long rows: a row's look-back chain has too few CTAs behind it to hide its latency, and
     // two passes over 4096-step chunks (20 / 28 bytes per element) win by 10-35 % (measured at 4, 16 and

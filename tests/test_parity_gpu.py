@@ -533,7 +533,8 @@ def test_lookback_workspace_contract():
     assert lib.ssb_scan_recommend(300, 65536, 0, 1, 1) == LOOKBACK              # from there on look-back keeps up
     assert lib.ssb_scan_recommend(2048, 65536, 0, 1, 1) == TMA | (48 << 8)        # many long rows of whole spans
     assert lib.ssb_scan_recommend(1024, 65536, 1, 1, 0) == TMA | (48 << 8)
-    assert lib.ssb_scan_recommend(1024, 65536, 0, 1, 1) == LOOKBACK               # the forward only from 2048 rows
+    assert lib.ssb_scan_recommend(1024, 65536, 0, 1, 1) == TMA | (10 << 8)        # the forward only from 2048 rows: per-warp ring below
+    assert lib.ssb_scan_recommend(1024, 32768, 0, 1, 1) == LOOKBACK
     assert lib.ssb_scan_recommend(64, 65540, 0, 1, 1) == LOOKBACK               # T not a multiple of 4096
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
     assert lib.ssb_scan_recommend(4096, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
