@@ -78,7 +78,7 @@ def parse_args():
                    help="when K steps take less than this, the K-step region is repeated and the median reported")
     p.add_argument("--no-t-sharded", action="store_true", help="N > 1: skip the T-sharded long-context measurement")
     p.add_argument("--no-weak", action="store_true", help="N > 1: skip the weak-scaling measurement")
-    p.add_argument("--ts-steps", type=int, default=6, help="timed steps of the T-sharded measurement")
+    p.add_argument("--ts-steps", type=int, default=20, help="timed steps of the T-sharded measurement")
     p.add_argument("--cut", type=float, default=None, help="early-termination threshold of the shard maps (default: the library's)")
     p.add_argument("--sets", type=int, default=0,
                    help="independent buffer sets the timed steps rotate over (0 = as many as keep the L2 from serving re-reads; "
