@@ -52,6 +52,10 @@ L2_BYTES = 126 << 20
 # DRAM traffic of the backward kernel as ncu counted it: a small record that the profiling step
 # rewrites whenever the kernel changes (see the file itself for the command and the commit).
 TRAFFIC_RECORD = os.path.join(REPO, "profiles", "bwd_kernel_dram_traffic.json")
+# world sizes at which the peer-memory exchange of the T-sharded path has run on real B200s (tests and
+# this bench); at other sizes the default run leaves it out rather than try it first inside the
+# measurement every other number of the line depends on
+PEER_EXCHANGE_WORLDS = frozenset({2, 4})
 
 
 def parse_args():
@@ -79,6 +83,9 @@ def parse_args():
     p.add_argument("--no-t-sharded", action="store_true", help="N > 1: skip the T-sharded long-context measurement")
     p.add_argument("--no-weak", action="store_true", help="N > 1: skip the weak-scaling measurement")
     p.add_argument("--ts-steps", type=int, default=20, help="timed steps of the T-sharded measurement")
+    p.add_argument("--peer-exchange", default="auto", choices=["auto", "on", "off"],
+                   help="T-sharded measurement: also time the shard maps exchanged through peer memory (auto: at the "
+                        "world sizes this exchange has been run at on B200s: 2 and 4)")
     p.add_argument("--cut", type=float, default=None, help="early-termination threshold of the shard maps (default: the library's)")
     p.add_argument("--sets", type=int, default=0,
                    help="independent buffer sets the timed steps rotate over (0 = as many as keep the L2 from serving re-reads; "
@@ -521,8 +528,12 @@ def measure_t_sharded(args, torch, dist, timer, lib, native, workloads, world, r
     ms, walked_all, max_err = measure(None)
     # the same steps with the maps exchanged through peer memory instead of NCCL, where the box allows it
     peer = {"unavailable": "peer memory exchange could not be set up (GPUs not all visible, no peer access, or IPC refused)"}
+    want_peer = args.peer_exchange == "on" or (args.peer_exchange == "auto" and world in PEER_EXCHANGE_WORLDS)
+    if not want_peer:
+        peer = {"skipped": f"--peer-exchange {args.peer_exchange}: measured by default only at world sizes {sorted(PEER_EXCHANGE_WORLDS)}, "
+                           "where it has been run on B200s; --peer-exchange on forces it"}
     try:
-        exchange = sharded.PeerCarryExchange.create(rows)
+        exchange = sharded.PeerCarryExchange.create(rows) if want_peer else None
         if exchange is not None:
             p_ms, _, p_err = measure(exchange)
             peer = {"value": rows * T / (p_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": p_ms,
