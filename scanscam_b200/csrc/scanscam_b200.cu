@@ -1624,6 +1624,35 @@ int cl_stream_block(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
     return 0;
 }
 
+// Which streaming tile shape (tuning id of SSB_CLS_CONFIGS) a direction gets, -1 = none.  A unit is
+// all of T for one (batch element, channel block); units run in rounds over the resident CTAs and
+// the last round is rarely full, so the choice goes by an estimate of rounds x cost of a round:
+//   id 0  32-channel blocks, one CTA per SM;
+//   id 1  64-channel blocks, one CTA per SM: half the units, a round costs 1.81 (forward) / 1.93
+//         (backward) rounds of id 0 -- it wins when that halves the number of rounds;
+//   id 2  32-channel blocks; forward: 128-step tiles, two CTAs per SM, used where one round of it
+//         covers units that id 0 needs two rounds for (up to 1.5 units per SM); backward: 256-step
+//         tiles, one stage: ahead of id 0 on every measured shape with more units than SMs.
+// "Rounds" = the mean of units / slots and its ceiling: CTAs of a part-filled round run faster,
+// they share the memory system with fewer others.  Fitted on [6...96, 2048...8192, 512...1024]
+// (12 shapes, 96 ... 1536 units of 32 channels); the choice is the best or within 3 % of the best
+// pinned id on each of them.
+double cl_rounds(int64_t units, int64_t slots) {
+    return 0.5 * ((double)units / (double)slots + (double)((units + slots - 1) / slots));
+}
+int cl_stream_id(bool backward, int64_t N, int64_t T, int64_t C, bool all_aligned16) {
+    if (cl_stream_block(N, T, C, all_aligned16) == 0) return -1;
+    const int64_t sms = sm_count(), p32 = N * ((C + 31) / 32), p64 = N * ((C + 63) / 64);
+    int id = (backward && p32 > sms) ? 2 : 0;
+    double best = cl_rounds(p32, sms);
+    if (!backward && p32 > sms && 2 * p32 <= 3 * sms && 1.72 * cl_rounds(p32, 2 * sms) < best) {
+        best = 1.72 * cl_rounds(p32, 2 * sms);
+        id = 2;
+    }
+    if (T >= 1024 && (C % 64 == 0 || C >= 512) && (backward ? 1.93 : 1.81) * cl_rounds(p64, sms) < best) id = 1;
+    return id;
+}
+
 // Too few pairs for the above but long rows: the same kernels over chunks of T in two passes
 // (measured 1.3-4x the look-back kernels from 2048 steps up).  Needs scratch.
 bool cl_chunked_shape(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
@@ -1676,8 +1705,8 @@ size_t cl3_need(int64_t N, int64_t T, int64_t C, int id, bool backward) {
 int cl_pick(bool backward, int64_t N, int64_t T, int64_t C, bool all_aligned16, size_t ws_avail) {
     // a handful of channels: whole batch elements per CTA, once there are enough of them to occupy the GPU
     if (cl_narrow_eligible(N, T, C, all_aligned16) && N >= 64 && T >= 64) return SSB_CL_VARIANT_NARROW;
-    const int block = cl_stream_block(N, T, C, all_aligned16);
-    if (block) return SSB_CL_VARIANT_STREAM | ((block == 64 ? 1 : 0) << 8);
+    const int stream_id = cl_stream_id(backward, N, T, C, all_aligned16);
+    if (stream_id >= 0) return SSB_CL_VARIANT_STREAM | (stream_id << 8);
     if (cl_chunked_shape(N, T, C, all_aligned16) && ws_avail >= cls_chunk_workspace_bytes(N, T, C)) return SSB_CL_VARIANT_CHUNKED;
     const bool vec = C % 4 == 0 && all_aligned16;
     if (cl_prefers_lookback(N, C) && ws_avail > 0 && ws_avail >= cl2_need(N, T, C, 0, backward, vec)) return SSB_CL_VARIANT_LOOKBACK;
@@ -1824,6 +1853,19 @@ bool cl_h16_eligible(int64_t N, int64_t T, int64_t C) {
     return C % 8 == 0 && N <= 0x7fffffffLL && T <= 0x7fffff00LL && C <= 0x7fffffffLL && T <= ((1LL << 40) - 1) / 2 / C;
 }
 
+// Whole-T units run in rounds over the resident CTAs, and the last round is rarely full.  The
+// 256-step tiles (512 threads) keep one CTA per SM: rounds of 148.  The 128-step tiles (128 threads,
+// half the shared memory) keep two: rounds of 296 that take 1.65-1.85 times as long (measured on
+// 160 ... 1024 pairs of 64 channels: the factor is lower where the sigmoid adds arithmetic for the
+// second CTA to hide).  Take the smaller estimate; beyond ~1200 pairs the difference is noise.
+bool cl_h16_small_tiles(int64_t pairs, bool backward, bool sigmoid) {
+    const int64_t sms = sm_count();
+    if (pairs <= sms || pairs > 8 * sms) return false;
+    const double factor = !sigmoid ? 1.85 : (backward ? 1.65 : 1.8);
+    const double one = (double)((pairs + sms - 1) / sms), two = (double)((pairs + 2 * sms - 1) / (2 * sms)) * factor;
+    return two < one;
+}
+
 template <typename IO, bool BWD, bool SIGMOID = false>
 int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, void *out2_, int64_t N, int64_t T, int64_t C,
            void *workspace, size_t workspace_bytes, void *stream, const char *who) {
@@ -1843,6 +1885,10 @@ int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, v
     if (pairs < 96 && T >= 2048 && workspace != nullptr && aligned_to(workspace, 256) &&
         workspace_bytes >= cls_chunk_workspace_bytes(N, T, C, 64))
         return launch_cls_chunked<BWD, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
+    if (cl_h16_small_tiles(pairs, BWD, SIGMOID)) {
+        if (!BWD) return launch_cls<64, 128, 8, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+        return launch_cls<64, 128, 8, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);
+    }
     if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
     return launch_cls<64, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
 }
@@ -1915,12 +1961,17 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
     if (cl_stream_block(N, T, C, true) == 0 && cl_chunked_shape(N, T, C, true) && workspace != nullptr &&
         aligned_to(workspace, 256) && workspace_bytes >= cls_chunk_workspace_bytes(N, T, C))
         return launch_cls_chunked<BWD, float, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
-    if (cl_stream_block(N, T, C, true) == 64) {
-        if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-        return launch_cls<64, 128, 8, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+    switch (cl_stream_id(BWD, N, T, C, true)) {  // the tile shapes of SSB_CLS_CONFIGS ids 1, 2, 0
+        case 1:
+            if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<64, 128, 8, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+        case 2:
+            if (!BWD) return launch_cls<32, 128, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<32, 256, 16, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+        default:
+            if (!BWD) return launch_cls<32, 256, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<32, 128, 16, 2, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
     }
-    if (!BWD) return launch_cls<32, 256, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-    return launch_cls<32, 128, 16, 2, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
 }
 }  // namespace
 

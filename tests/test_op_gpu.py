@@ -301,7 +301,7 @@ def test_fused_operators_with_16bit_tensors(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100)])
+@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100), (24, 512, 300), (20, 520, 260)])
 def test_scan_channels_last_with_16bit_tensors(dtype, shape):
     """scan() on channels-last bf16 / fp16 inputs ([N, C, T] views of dense [N, T, C]) against the
     fp32 oracle on the rounded inputs."""
@@ -320,7 +320,7 @@ def test_scan_channels_last_with_16bit_tensors(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100), (3, 12, 50)])
+@pytest.mark.parametrize("shape", [(4, 256, 600), (1, 64, 5000), (2, 24, 100), (3, 12, 50), (24, 512, 300), (20, 520, 260)])
 def test_fused_sigmoid_gate_channels_last(dtype, shape):
     """scan_sigmoid_gate on channels-last inputs ([N, C, T] views of dense [N, T, C]): the fused
     streaming kernels (the last shape's 12 channels fall back to the unfused composition for the

@@ -826,7 +826,8 @@ def test_16bit_fused_entry_points(name, shape):
 
 @pytest.mark.parametrize("name", ["bf16", "f16"])
 @pytest.mark.parametrize("shape,scratch", [((8, 700, 512), False), ((2, 300, 64), False), ((1, 9000, 64), True),
-                                           ((2, 5000, 200), True), ((3, 100, 8), False), ((1, 4096, 1032), True)])
+                                           ((2, 5000, 200), True), ((3, 100, 8), False), ((1, 4096, 1032), True),
+                                           ((24, 300, 512), False), ((20, 260, 520), False)])  # 192 / 180 blocks: two CTAs per SM
 def test_channels_last_16bit_storage(name, shape, scratch):
     """ssb_scan_cl_{fwd,bwd}_{bf16,f16}: [N,T,C] tensors in 16-bit storage; direct streaming and,
     with scratch on few-block shapes, the two-pass chunked form.  Every output within half a unit
