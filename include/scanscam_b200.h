@@ -309,7 +309,9 @@ int ssb_scan_cl_sigmoid_bwd_f16(const void *gate_logits, const void *h, const vo
  * has a 4-channel form).  SSB_CL_VARIANT_AUTO chooses from the shape and from the scratch it was
  * given: shapes with at least 96 (batch element, 32-channel block) pairs, T >= 128, C % 4 == 0 and
  * 16-byte aligned tensors run the streaming kernels, which need no scratch -- the plain entry
- * points above choose them too; with fewer pairs, T >= 2048 and enough scratch the same kernels run
+ * points above choose them too -- with the tile shape (tuning id 0, 1 or 2) that an estimate of
+ * rounds over the SMs favours for that direction, so the forward and the backward of one shape
+ * may report different ids; with fewer pairs, T >= 2048 and enough scratch the same kernels run
  * over chunks of T in two passes; otherwise the look-back kernels when scratch is given and they
  * are faster, else the plain kernels.  A pinned family that cannot run the shape returns
  * SSB_ERR_UNSUPPORTED, one that is given too little scratch SSB_ERR_WORKSPACE.  Results do not

@@ -302,13 +302,28 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
 // part.  cut = 0 stops only at exactly-zero products; rows whose products stay above the cut are
 // walked in full.  Plain vector loads (the walk's length is not known in advance, so nothing is
 // prefetched past it): thread (seg, cg) reads 4 adjacent channels of TS consecutive steps, the 8
-// threads of a quarter warp one 128-byte row.  fp32, 32-channel blocks, C % 4 == 0.
-template <int SEG, int TS, bool BWD, bool SIGMOID = false>
-__global__ void __launch_bounds__(8 * SEG)
-cl_tail_map_kernel(const float *__restrict__ gate, const float *__restrict__ in1,  // value | gout
+// threads of a quarter warp one 128-byte row.  Blocks of 128 bytes of channels (32 fp32, 64 bf16 /
+// fp16: the 16 threads of a half warp read one row, 8 bytes each), C % 4 == 0; fp32 arithmetic.
+template <typename IO>
+__device__ __forceinline__ float4 ldcs_vec4(const IO *p) {  // four adjacent channels of one step, streamed
+    if constexpr (sizeof(IO) == 4) {
+        return __ldcs(reinterpret_cast<const float4 *>(p));
+    } else {
+        const uint2 v = __ldcs(reinterpret_cast<const uint2 *>(p));
+        float4 r;
+        unpack2<IO>(v.x, r.x, r.y);
+        unpack2<IO>(v.y, r.z, r.w);
+        return r;
+    }
+}
+
+template <int SEG, int TS, bool BWD, bool SIGMOID = false, typename IO = float>
+__global__ void __launch_bounds__(32 / (int)sizeof(IO) * SEG)
+cl_tail_map_kernel(const IO *__restrict__ gate, const IO *__restrict__ in1,  // value | gout
                    int64_t T, int64_t C, int64_t n_units, int cblocks, int64_t chunk_steps, int chunks, float cut,
                    float *__restrict__ maps) {
-    constexpr int CC = 32, CG = 8, THREADS = CG * SEG, NW = THREADS / 32, SPW = 4, TT = SEG * TS;
+    constexpr int CC = 128 / (int)sizeof(IO), CG = CC / 4, THREADS = CG * SEG, NW = THREADS / 32, SPW = 32 / CG, TT = SEG * TS;
+    static_assert(THREADS % 32 == 0 && THREADS <= 1024, "whole warps");
     __shared__ float4 s_tot[NW][CG][2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cg = tid % CG, seg = tid / CG, seg_in_warp = lane / CG;
@@ -320,7 +335,7 @@ cl_tail_map_kernel(const float *__restrict__ gate, const float *__restrict__ in1
         const int c = (int)(pair % cblocks) * CC + cg * 4;
         const bool c_ok = c < C;  // C % 4 == 0: a float4 is all in or all out
         const int64_t lo = (int64_t)chunk * chunk_steps, hi = lo + chunk_steps < T ? lo + chunk_steps : T;
-        const float *ga = gate + n * T * C + c, *xa = in1 + n * T * C + c;
+        const IO *ga = gate + n * T * C + c, *xa = in1 + n * T * C + c;
         float4 sA = one4, sB = zero4;
         for (int64_t walked = 0; walked < hi - lo; walked += TT) {
             // this thread's TS steps of the tile; steps outside the chunk are the identity
@@ -330,8 +345,8 @@ cl_tail_map_kernel(const float *__restrict__ gate, const float *__restrict__ in1
             for (int k = 0; k < TS; k++) {
                 const int64_t t = t0 + k;
                 if (c_ok && t >= lo && t < hi && SSB_INDEX_OK(n * T * C + c + t * C, (n_units / chunks / cblocks) * T * C, 70)) {
-                    a[k] = __ldcs(reinterpret_cast<const float4 *>(ga + t * C));
-                    x[k] = __ldcs(reinterpret_cast<const float4 *>(xa + t * C));
+                    a[k] = ldcs_vec4<IO>(ga + t * C);
+                    x[k] = ldcs_vec4<IO>(xa + t * C);
                     if (SIGMOID) a[k] = sigmoid4(a[k]);
                 } else {
                     a[k] = one4;

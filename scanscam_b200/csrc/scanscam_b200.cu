@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstring>
 #include <limits>
+#include <type_traits>
 
 #include "scan_cl.cuh"
 #include "scan_cl_lookback.cuh"
@@ -1464,17 +1465,14 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
         return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
                     cls_chunk_workspace_bytes(N, T, C, CC), workspace_bytes);
     float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * CC;
-    int rc;
-    if constexpr (sizeof(IO) == 4) {
-        // pass 1 walks each chunk only as far as its gate products need (stops at 2^-40 in all 32 channels)
-        auto mk = ssb::cls::cl_tail_map_kernel<32, 8, BWD, SIGMOID>;
-        const int64_t units = pairs * chunks;
-        const int grid = persistent_grid<700000 + (BWD ? 1 : 0) + (SIGMOID ? 2 : 0)>(mk, 256, units);
-        mk<<<grid, 256, 0, st>>>(gate, BWD ? in2 : in1, T, C, units, (int)((C + CC - 1) / CC), steps, (int)chunks, kChunkCut, maps);
-        rc = check_launch("cl_tail_map_kernel");
-    } else {
-        rc = launch_cls<CC, 256, 16, 2, 1, BWD, true, IO, SIGMOID>(gate, in1, in2, nullptr, nullptr, N, T, C, st, steps, nullptr, maps);
-    }
+    // pass 1 walks each chunk only as far as its gate products need (stops at 2^-40 in all of the block's channels)
+    constexpr int kSeg = 256 / (CC / 4);  // 256 threads: 32 x 8 steps per tile for fp32, 16 x 8 for 16-bit storage
+    auto mk = ssb::cls::cl_tail_map_kernel<kSeg, 8, BWD, SIGMOID, IO>;
+    const int64_t units = pairs * chunks;
+    const int grid = persistent_grid<700000 + (BWD ? 1 : 0) + (SIGMOID ? 2 : 0) + 4 * (int)sizeof(IO) +
+                                     (std::is_same<IO, __half>::value ? 32 : 0)>(mk, 256, units);
+    mk<<<grid, 256, 0, st>>>(gate, BWD ? in2 : in1, T, C, units, (int)((C + CC - 1) / CC), steps, (int)chunks, kChunkCut, maps);
+    int rc = check_launch("cl_tail_map_kernel");
     if (rc != SSB_OK) return rc;
     const int64_t threads = pairs * CC;
     ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
@@ -1612,16 +1610,12 @@ int cl_family_of(int variant) { return variant & 0xff; }
 int cl_tuning_of(int variant) { return (variant >> 8) & 0xff; }
 bool cl_scalar_lanes(int variant) { return ((variant >> 16) & 1) != 0; }
 
-// Channel-block width of the streaming kernels for this shape, or 0 when they do not apply: they
-// need a TMA-describable tensor, rows long enough to fill their 128-256 step tiles, and enough
-// (batch element, channel block) pairs to occupy the GPU without splitting T (measured on B200:
-// 128 pairs of 64 channels when rows have at least 1024 steps and C fills 64-channel blocks, else
-// 96 pairs of 32 channels; below that the look-back kernels win).
-int cl_stream_block(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
-    if (!all_aligned16 || !cl3_eligible(N, T, C) || T < 128 || encode_fn() == nullptr) return 0;
-    if (T >= 1024 && (C % 64 == 0 || C >= 512) && N * ((C + 63) / 64) >= 128) return 64;
-    if (N * ((C + 31) / 32) >= 96) return 32;
-    return 0;
+// Whether the streaming kernels apply to this shape: they need a TMA-describable tensor, rows long
+// enough to fill their 128-256 step tiles, and enough (batch element, 32-channel block) pairs to
+// occupy the GPU without splitting T (measured on B200: from 96 pairs; below that the chunked and
+// look-back forms win).
+bool cl_stream_shape(int64_t N, int64_t T, int64_t C, bool all_aligned16) {
+    return all_aligned16 && cl3_eligible(N, T, C) && T >= 128 && encode_fn() != nullptr && N * ((C + 31) / 32) >= 96;
 }
 
 // Which streaming tile shape (tuning id of SSB_CLS_CONFIGS) a direction gets, -1 = none.  A unit is
@@ -1641,7 +1635,7 @@ double cl_rounds(int64_t units, int64_t slots) {
     return 0.5 * ((double)units / (double)slots + (double)((units + slots - 1) / slots));
 }
 int cl_stream_id(bool backward, int64_t N, int64_t T, int64_t C, bool all_aligned16) {
-    if (cl_stream_block(N, T, C, all_aligned16) == 0) return -1;
+    if (!cl_stream_shape(N, T, C, all_aligned16)) return -1;
     const int64_t sms = sm_count(), p32 = N * ((C + 31) / 32), p64 = N * ((C + 63) / 64);
     int id = (backward && p32 > sms) ? 2 : 0;
     double best = cl_rounds(p32, sms);
@@ -1958,7 +1952,7 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
     if (!al16 || !cl3_eligible(N, T, C) || encode_fn() == nullptr)
         return fail(SSB_ERR_UNSUPPORTED, "%s needs C %% 4 == 0 and 16-byte aligned tensors (C=%lld)", who, (long long)C);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cl_stream_block(N, T, C, true) == 0 && cl_chunked_shape(N, T, C, true) && workspace != nullptr &&
+    if (!cl_stream_shape(N, T, C, true) && cl_chunked_shape(N, T, C, true) && workspace != nullptr &&
         aligned_to(workspace, 256) && workspace_bytes >= cls_chunk_workspace_bytes(N, T, C))
         return launch_cls_chunked<BWD, float, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
     switch (cl_stream_id(BWD, N, T, C, true)) {  // the tile shapes of SSB_CLS_CONFIGS ids 1, 2, 0
@@ -1978,7 +1972,7 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
 extern "C" {
 
 size_t ssb_scan_cl_sigmoid_workspace_bytes(int64_t N, int64_t T, int64_t C) {
-    if (N <= 0 || T <= 0 || C <= 0 || cl_stream_block(N, T, C, true) != 0 || !cl_chunked_shape(N, T, C, true)) return 0;
+    if (N <= 0 || T <= 0 || C <= 0 || cl_stream_shape(N, T, C, true) || !cl_chunked_shape(N, T, C, true)) return 0;
     return cls_chunk_workspace_bytes(N, T, C);
 }
 
