@@ -19,10 +19,14 @@
 //     The 8 (or 16) threads of a quarter warp read one contiguous 128-byte row: no bank conflicts.
 //   * Results go to a staging tile and leave through one bulk tensor store per tile.
 //   * With few (batch element, channel block) pairs the time axis is cut into `chunks` pieces that
-//     run as units of their own, in two passes: the REDUCE instantiation only composes each chunk's
-//     map (reads gate and value / gate and gout, 8 bytes per element, writes 2*CC floats per
-//     chunk), cl_chunk_carry_kernel folds those maps into the state entering every chunk, and the
-//     ordinary instantiation starts each chunk from that state (`carry_in`).
+//     run as units of their own, in two passes: cl_tail_map_kernel composes each chunk's map as
+//     far as the gate products need (or the REDUCE instantiation over the whole chunk: reads gate
+//     and value / gate and gout, 8 bytes per element; both write 2*CC floats per chunk), and the
+//     ordinary instantiation starts each chunk from the fold of the maps of the chunks before it
+//     (after it, for the backward), which every CTA computes for itself at the start of a unit.
+//     That launch may be a programmatic dependent launch: the CTAs set up and issue their first
+//     tile loads while the map kernel drains, and wait for it (griddepcontrol.wait) only before
+//     they read the maps.
 //
 //   * Storage type IO: float, or bf16 / fp16 with fp32 arithmetic.  A thread still owns 4 adjacent
 //     channels; with 16-bit storage they are 8 bytes (one 64-bit shared-memory access), a tile row
@@ -85,7 +89,9 @@ __device__ __forceinline__ float4 shfl4(float4 v, int delta, bool up) {
 // n_units = N * cblocks * chunks; unit u is chunk u % chunks of (batch element, channel block)
 // u / chunks and covers `pieces` tiles.  carry_in (may be NULL): [n_units][CC] states entering the
 // units.  REDUCE: maps [n_units][2][CC] receives each unit's composed map (A, B) and nothing else
-// is written; the value / h tensor is not read by the backward REDUCE.
+// is written; the value / h tensor is not read by the backward REDUCE.  Otherwise, with carry_in
+// NULL and maps given, maps holds the chunk maps a preceding kernel wrote and a unit starts from
+// the fold of the maps of its pair's earlier (backward: later) chunks.
 // Four adjacent channels of one step, shared memory <-> fp32 registers.
 template <typename IO>
 __device__ __forceinline__ float4 lds_vec4(uint32_t addr) {
@@ -116,6 +122,12 @@ __device__ __forceinline__ float4 sigmoid4(float4 z) {
 __device__ __forceinline__ float4 dsigmoid4(float4 a) {  // a (1 - a), the derivative of the sigmoid at its output a
     return make_float4(a.x * (1.f - a.x), a.y * (1.f - a.y), a.z * (1.f - a.z), a.w * (1.f - a.w));
 }
+
+// Programmatic dependent launch: the wait returns once the grids this one depends on have completed
+// and their writes are visible (at once when the launch carried no such dependency); the trigger
+// lets a dependent grid start its prologue while this grid is still running.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float,
           bool SIGMOID = false>
@@ -172,7 +184,7 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     }
     __syncthreads();
 
-    bool timed_out = false;
+    bool timed_out = false, maps_ready = false;
     unsigned phase_bits = 0u;
     int out_slot = 0, buf = 0;
     float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);  // state entering the tile, for this thread's 4 channels
@@ -188,6 +200,22 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             if (!REDUCE && carry_in != nullptr) {
                 const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
                 carry = *reinterpret_cast<const float4 *>(carry_in + unit * CC + cg * 4);
+            } else if (!REDUCE && maps != nullptr) {
+                if (!maps_ready) {  // the maps come from the kernel before this one
+                    grid_dependency_wait();
+                    maps_ready = true;
+                }
+                const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
+                const int chunk = (int)(unit % chunks);
+                const float *m = maps + (unit - chunk) * 2 * CC + cg * 4;  // the pair's first chunk
+                const int n_before = BWD ? chunks - 1 - chunk : chunk;
+#pragma unroll 4
+                for (int q = 0; q < n_before; q++) {
+                    const int k = BWD ? chunks - 1 - q : q;
+                    const float4 mA = __ldcg(reinterpret_cast<const float4 *>(m + (int64_t)k * 2 * CC));
+                    const float4 mB = __ldcg(reinterpret_cast<const float4 *>(m + ((int64_t)k * 2 + 1) * CC));
+                    carry = fma4(mA, carry, mB);
+                }
             }
         }
         if (!tma::mbar_wait_bounded(bar0 + 8 * stage, (phase_bits >> stage) & 1u)) timed_out = true;
@@ -328,6 +356,7 @@ cl_tail_map_kernel(const IO *__restrict__ gate, const IO *__restrict__ in1,  // 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cg = tid % CG, seg = tid / CG, seg_in_warp = lane / CG;
     const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    grid_dependents_may_launch();  // the scan pass may set up beside this grid; it waits before it reads `maps`
     for (int64_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
         const int chunk = (int)(unit % chunks);
         const int64_t pair = unit / chunks;
@@ -392,24 +421,6 @@ cl_tail_map_kernel(const IO *__restrict__ gate, const IO *__restrict__ in1,  // 
             *reinterpret_cast<float4 *>(maps + (unit * 2) * CC + cg * 4) = sA;
             *reinterpret_cast<float4 *>(maps + (unit * 2 + 1) * CC + cg * 4) = sB;
         }
-    }
-}
-
-// Folds the chunk maps of each (batch element, channel block) pair into the state entering every
-// chunk: forward left to right, backward right to left.  One thread per pair and channel.
-template <bool BWD>
-__global__ void cl_chunk_carry_kernel(const float *__restrict__ maps, float *__restrict__ carry, int64_t pairs, int chunks,
-                                      int cc) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= pairs * cc) return;
-    const int64_t pair = idx / cc;
-    const int c = (int)(idx % cc);
-    float x = 0.f;
-    for (int q = 0; q < chunks; q++) {
-        const int k = BWD ? chunks - 1 - q : q;
-        const int64_t unit = pair * chunks + k;
-        carry[unit * cc + c] = x;
-        x = fmaf(maps[(unit * 2) * cc + c], x, maps[(unit * 2 + 1) * cc + c]);
     }
 }
 

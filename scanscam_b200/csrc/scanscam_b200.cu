@@ -1422,6 +1422,24 @@ int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typ
     }
     const int64_t units = N * cblocks * chunks, cap = (int64_t)sm_count() * occ;
     const int grid = (int)(units < cap ? units : cap);
+    if (!REDUCE && maps != nullptr && carry_in == nullptr) {
+        // the scan pass of the chunked form: it may start beside the map kernel it follows and waits
+        // for it inside (griddepcontrol.wait) before the first read of `maps`
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3((unsigned)Cfg::THREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const int cb = (int)cblocks, pc = (int)pieces, ch = (int)chunks;
+        if (cudaLaunchKernelEx(&cfg, kern, mg, m1, m2, mo1, mo2, units, cb, pc, ch, carry_in, maps) != cudaSuccess)
+            return check_launch("cl_stream_kernel (dependent launch)");
+        return check_launch("cl_stream_kernel");
+    }
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces, (int)chunks,
                                                       carry_in, maps);
     return check_launch("cl_stream_kernel");
@@ -1452,7 +1470,7 @@ int64_t cls_chunk_steps(int64_t N, int64_t T, int64_t C, int cc = 32) {
 }
 size_t cls_chunk_workspace_bytes(int64_t N, int64_t T, int64_t C, int cc = 32) {
     const int64_t steps = cls_chunk_steps(N, T, C, cc), chunks = (T + steps - 1) / steps;
-    return (size_t)(N * ((C + cc - 1) / cc) * chunks) * 3 * cc * sizeof(float);
+    return (size_t)(N * ((C + cc - 1) / cc) * chunks) * 2 * cc * sizeof(float);  // (A, B) per unit and channel
 }
 
 template <bool BWD, typename IO = float, bool SIGMOID = false>
@@ -1464,7 +1482,7 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
     if (workspace == nullptr || workspace_bytes < cls_chunk_workspace_bytes(N, T, C, CC))
         return fail(SSB_ERR_WORKSPACE, "channels-last chunked streaming needs %zu bytes of workspace, got %zu",
                     cls_chunk_workspace_bytes(N, T, C, CC), workspace_bytes);
-    float *maps = static_cast<float *>(workspace), *carry = maps + pairs * chunks * 2 * CC;
+    float *maps = static_cast<float *>(workspace);
     // pass 1 walks each chunk only as far as its gate products need (stops at 2^-40 in all of the block's channels)
     constexpr int kSeg = 256 / (CC / 4);  // 256 threads: 32 x 8 steps per tile for fp32, 16 x 8 for 16-bit storage
     auto mk = ssb::cls::cl_tail_map_kernel<kSeg, 8, BWD, SIGMOID, IO>;
@@ -1474,14 +1492,12 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
     mk<<<grid, 256, 0, st>>>(gate, BWD ? in2 : in1, T, C, units, (int)((C + CC - 1) / CC), steps, (int)chunks, kChunkCut, maps);
     int rc = check_launch("cl_tail_map_kernel");
     if (rc != SSB_OK) return rc;
-    const int64_t threads = pairs * CC;
-    ssb::cls::cl_chunk_carry_kernel<BWD><<<(int)((threads + 255) / 256), 256, 0, st>>>(maps, carry, pairs, (int)chunks, CC);
-    if ((rc = check_launch("cl_chunk_carry_kernel")) != SSB_OK) return rc;
-    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, carry);
+    // pass 2: the scan over the chunks; every unit folds the maps of its pair's chunks before it for itself
+    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, nullptr, maps);
     if constexpr (sizeof(IO) == 2)
-        return launch_cls<CC, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+        return launch_cls<CC, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, nullptr, maps);
     else
-        return launch_cls<CC, 128, 16, 2, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, carry);
+        return launch_cls<CC, 128, 16, 2, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, nullptr, maps);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
