@@ -191,6 +191,42 @@ def test_scan_can_be_captured_in_a_cuda_graph():
         assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
 
 
+def test_chunked_channels_last_can_be_captured_in_a_cuda_graph():
+    """The two-pass channels-last form -- map kernel, then the scan kernel as its programmatic
+    dependent -- recorded once with the caller's scratch and replayed on new data."""
+    from scanscam_b200 import _native
+
+    lib = _native.load()
+    N, T, C = 2, 6144, 64
+    a, b, g = make_inputs("sigmoid2", (N, T, C), seed=61)
+    da, db, dg = a.cuda(), b.cuda(), g.cuda()
+    h, ga, gb = torch.empty_like(da), torch.empty_like(da), torch.empty_like(da)
+    v = _native.CL_CHUNKED
+    need = max(lib.ssb_scan_cl_variant_workspace_bytes(N, T, C, v, d) for d in (0, 1))
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+
+    def both(st):
+        _native.check(lib.ssb_scan_cl_fwd_f32_ex(da.data_ptr(), db.data_ptr(), h.data_ptr(), N, T, C, v, ws.data_ptr(), need, st))
+        _native.check(lib.ssb_scan_cl_bwd_f32_ex(da.data_ptr(), h.data_ptr(), dg.data_ptr(), ga.data_ptr(), gb.data_ptr(),
+                                                 N, T, C, v, ws.data_ptr(), need, st))
+
+    both(torch.cuda.current_stream().cuda_stream)  # warm-up outside capture (occupancy queries are cached on first use)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        both(torch.cuda.current_stream().cuda_stream)
+    for seed in (62, 63):
+        a2, b2, g2 = make_inputs("sigmoid2", (N, T, C), seed=seed)
+        da.copy_(a2); db.copy_(b2); dg.copy_(g2)
+        graph.replay()
+        torch.cuda.synchronize()
+        h_ref = oracle.scan_forward_channels_last(a2.numpy(), b2.numpy())
+        ga_ref, gb_ref = oracle.scan_backward_channels_last(a2.numpy(), h_ref, g2.numpy())
+        assert _gpu.allclose_ref(h, h_ref) and _gpu.allclose_ref(ga, ga_ref) and _gpu.allclose_ref(gb, gb_ref)
+    _gpu.device_ok()
+
+
 @pytest.mark.parametrize("shape", [(64, 4096), (3, 5, 1024), (2, 20000), (1000, 8), (7, 1001)])
 def test_fused_sigmoid_gate_matches_unfused_oracle(shape):
     """scan_sigmoid_gate(z, b) against the CPU oracle fed sigmoid(z) computed in fp32 on the host;
