@@ -87,6 +87,16 @@ __device__ __forceinline__ void store_stream(real *p, const Pack<real, VEC> &r) 
     }
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A kernel launched with the attribute cudaLaunchAttributeProgrammaticStreamSerialization may
+// start while the kernel before it in the stream is still running, once every CTA of that kernel
+// has executed the trigger (or exited); the wait returns when the earlier kernel has completed
+// and its writes are visible -- at once when the launch carried no such dependency.  A kernel that
+// waits before its first access to global memory is therefore ordered exactly like an ordinary
+// launch; what overlaps is its launch, its block scheduling and whatever set-up precedes the wait.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- 16-bit storage types (bf16 / fp16 in memory, fp32 arithmetic) -------------------------
 // Two packed 16-bit values <-> two floats.  `lo` is the element at the lower address.
 template <typename io_t>

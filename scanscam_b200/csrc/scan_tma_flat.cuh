@@ -121,8 +121,14 @@ tma_flat_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_const
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) tma::mbar_init(bar0 + 8 * s, 1);
         tma::fence_mbar_init();
-        for (int64_t i = 0; i < STAGES - 1 && i < my_spans; i++) issue(i);
     }
+    // Every CTA of this grid is resident by now (persistent grid): the next kernel in the stream may
+    // be scheduled onto SMs as they free up.  This kernel itself touches global memory only after
+    // the kernel before it has completed.
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+    if (tid == 0)
+        for (int64_t i = 0; i < STAGES - 1 && i < my_spans; i++) issue(i);
     __syncthreads();
 
     uint32_t off[NCH];

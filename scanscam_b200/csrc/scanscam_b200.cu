@@ -239,6 +239,29 @@ int persistent_grid(K kern, int threads, int64_t units) {
     return (int)(units < cap ? (units > 0 ? units : 1) : cap);
 }
 
+// Launches `kern` as a programmatic dependent of the work ahead of it in `st`.  Only for kernels that
+// execute griddepcontrol.wait before their first access to global memory: such a kernel is ordered
+// like an ordinary launch, and its launch and set-up overlap the tail of the kernel ahead.  Used for
+// the span sweep on bulk tensor copies (measured on B200, 2048 x 4096 forward + backward: 47.4 -> 43.3 us
+// per step as stream launches, 42.8 -> 41.9 us inside a CUDA graph; no change on 16384 x 4096) and for
+// the scan pass of the channels-last chunked form; NOT for the flat sweeps, whose thousands of small
+// CTAs queue up behind the wait and cost more than the launch they hide (1024 x 1024: 9.3 -> 10.7 us
+// per step), nor for the channels-last streaming kernels in general (-1 ... -12 %).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), int grid, int threads, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 int64_t flat_units(int64_t rows, int64_t T4, int cap) {
     if (T4 > cap) return rows;
     const int64_t rps = cap / T4;
@@ -623,8 +646,12 @@ int launch_tmaflat(const IO *gate, const IO *in1, const typename as_given<IO>::t
         grid = (int)((spans + per_cta - 1) / per_cta);
     }
     const int pieces = LONG ? (int)(T / span_elems) : 1;
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b, pieces,
-                                                      (LONG && BWD) ? in1 : nullptr);
+    // a programmatic dependent of whatever precedes it in the stream: the kernel waits for that before
+    // its first access to global memory, so only its launch and set-up overlap the predecessor's tail
+    const IO *h_rows = (LONG && BWD) ? in1 : nullptr;
+    if (launch_dependent(kern, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, mg, m1, m2, mo1, mo2, rows, upr, carry_a, carry_b, pieces,
+                         h_rows) != cudaSuccess)
+        return check_launch("tma_flat_kernel (dependent launch)");
     return check_launch("tma_flat_kernel");
 }
 
@@ -1425,18 +1452,8 @@ int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typ
     if (!REDUCE && maps != nullptr && carry_in == nullptr) {
         // the scan pass of the chunked form: it may start beside the map kernel it follows and waits
         // for it inside (griddepcontrol.wait) before the first read of `maps`
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)grid);
-        cfg.blockDim = dim3((unsigned)Cfg::THREADS);
-        cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        const int cb = (int)cblocks, pc = (int)pieces, ch = (int)chunks;
-        if (cudaLaunchKernelEx(&cfg, kern, mg, m1, m2, mo1, mo2, units, cb, pc, ch, carry_in, maps) != cudaSuccess)
+        if (launch_dependent(kern, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces,
+                             (int)chunks, carry_in, maps) != cudaSuccess)
             return check_launch("cl_stream_kernel (dependent launch)");
         return check_launch("cl_stream_kernel");
     }
