@@ -406,6 +406,23 @@ def test_peer_exchange_emulated_on_one_gpu(world, rows, step):
     _gpu.device_ok()
 
 
+def test_channels_last_stream_tile_choice():
+    """ssb_scan_cl_recommend on a 148-SM part: the streaming tile shape follows the rounds estimate, per
+    direction (units of 32 channels just above a multiple of the SM count keep 32-channel blocks; where
+    halving the units halves the rounds, 64-channel blocks; the backward's 256-step tiles from 149
+    units up)."""
+    lib = _native.load()
+    if torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the expected choices are those of a 148-SM GPU")
+    S = _native.CL_STREAM
+    expect = {(8, 4096, 512): (0, 0), (12, 4096, 512): (2, 1), (16, 4096, 512): (1, 1), (20, 4096, 512): (0, 2),
+              (24, 4096, 512): (0, 2), (32, 4096, 512): (1, 1), (64, 4096, 512): (1, 2)}
+    for shape, (fwd_id, bwd_id) in expect.items():
+        assert lib.ssb_scan_cl_recommend(*shape, 0, 1, 1) == S | (fwd_id << 8), shape
+        assert lib.ssb_scan_cl_recommend(*shape, 1, 1, 1) == S | (bwd_id << 8), shape
+        assert lib.ssb_scan_cl_variant_workspace_bytes(*shape, S | (fwd_id << 8), 0) == 0
+
+
 def test_cfg3_full_size_under_auto_sampled():
     """cfg3 as configured -- [1024, 2^20], near-unit gates, the kernels AUTO picks at that size --
     at full size on the GPU; a strided sample of 16 rows against the oracle, the backward fed with
