@@ -20,10 +20,9 @@
 //   * Results go to a staging tile and leave through one bulk tensor store per tile.
 //   * With few (batch element, channel block) pairs the time axis is cut into `chunks` pieces that
 //     run as units of their own, in two passes: cl_tail_map_kernel composes each chunk's map as
-//     far as the gate products need (or the REDUCE instantiation over the whole chunk: reads gate
-//     and value / gate and gout, 8 bytes per element; both write 2*CC floats per chunk), and the
-//     ordinary instantiation starts each chunk from the fold of the maps of the chunks before it
-//     (after it, for the backward), which every CTA computes for itself at the start of a unit.
+//     far as the gate products need (2*CC floats per chunk), and this kernel starts each chunk
+//     from the fold of the maps of the chunks before it (after it, for the backward), which every
+//     CTA computes for itself at the start of a unit.
 //     That launch may be a programmatic dependent launch: the CTAs set up and issue their first
 //     tile loads while the map kernel drains, and wait for it (griddepcontrol.wait) only before
 //     they read the maps.
@@ -47,7 +46,7 @@
 namespace ssb {
 namespace cls {
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float>
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, typename IO = float>
 struct Config {
     static constexpr int ROW = CC * (int)sizeof(IO);  // bytes of one tile row
     static constexpr int CG = CC / 4;            // float4 channel groups per tile row
@@ -55,8 +54,8 @@ struct Config {
     static constexpr int TS = TT / SEG;          // steps per thread
     static constexpr int SPW = 32 / CG;          // segments per warp
     static constexpr int NW = THREADS / 32;
-    static constexpr int N_IN = (BWD && !REDUCE) ? 3 : 2;
-    static constexpr int N_OUT = REDUCE ? 0 : (BWD ? 2 : 1);
+    static constexpr int N_IN = BWD ? 3 : 2;
+    static constexpr int N_OUT = BWD ? 2 : 1;
     static constexpr int TILE = TT * ROW;
     static constexpr int SMEM_BYTES = (STAGES * N_IN + OUTBUF * N_OUT) * TILE + 128;
     static_assert(CC == 32 || CC == 64 || CC == 128, "a tile row is 8, 16 or 32 groups of 4 channels");
@@ -87,11 +86,9 @@ __device__ __forceinline__ float4 shfl4(float4 v, int delta, bool up) {
 }
 
 // n_units = N * cblocks * chunks; unit u is chunk u % chunks of (batch element, channel block)
-// u / chunks and covers `pieces` tiles.  carry_in (may be NULL): [n_units][CC] states entering the
-// units.  REDUCE: maps [n_units][2][CC] receives each unit's composed map (A, B) and nothing else
-// is written; the value / h tensor is not read by the backward REDUCE.  Otherwise, with carry_in
-// NULL and maps given, maps holds the chunk maps a preceding kernel wrote and a unit starts from
-// the fold of the maps of its pair's earlier (backward: later) chunks.
+// u / chunks and covers `pieces` tiles.  maps (NULL when chunks == 1): [n_units][2][CC], the chunk
+// maps (A, B) a preceding kernel wrote; a unit starts from the fold of the maps of its pair's
+// earlier (backward: later) chunks.
 // Four adjacent channels of one step, shared memory <-> fp32 registers.
 template <typename IO>
 __device__ __forceinline__ float4 lds_vec4(uint32_t addr) {
@@ -123,14 +120,13 @@ __device__ __forceinline__ float4 dsigmoid4(float4 a) {  // a (1 - a), the deriv
     return make_float4(a.x * (1.f - a.x), a.y * (1.f - a.y), a.z * (1.f - a.z), a.w * (1.f - a.w));
 }
 
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float,
-          bool SIGMOID = false>
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, typename IO = float, bool SIGMOID = false>
 __global__ void __launch_bounds__(CC / 4 * SEG)
 cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_in1,
                  const __grid_constant__ CUtensorMap map_in2, const __grid_constant__ CUtensorMap map_out1,
                  const __grid_constant__ CUtensorMap map_out2, int64_t n_units, int cblocks, int pieces, int chunks,
-                 const float *__restrict__ carry_in, float *__restrict__ maps) {
-    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
+                 const float *__restrict__ maps) {
+    using Cfg = Config<CC, TT, SEG, STAGES, OUTBUF, BWD, IO>;
     constexpr int CG = Cfg::CG, TS = Cfg::TS, SPW = Cfg::SPW, NW = Cfg::NW, N_IN = Cfg::N_IN, N_OUT = Cfg::N_OUT,
                   TILE = Cfg::TILE, ROW = Cfg::ROW;
     extern __shared__ uint8_t smem_raw[];
@@ -163,12 +159,8 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         const uint32_t bar = bar0 + 8 * stage, dst = smem0 + stage * N_IN * TILE;
         tma::mbar_expect_tx(bar, N_IN * TILE);
         tma::load_box(dst, &map_gate, c0, t0, n, bar);
-        if (BWD && REDUCE) {
-            tma::load_box(dst + TILE, &map_in2, c0, t0, n, bar);
-        } else {
-            tma::load_box(dst + TILE, &map_in1, c0, BWD ? t0 - 1 : t0, n, bar);  // backward: h one step earlier
-            if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, c0, t0, n, bar);
-        }
+        tma::load_box(dst + TILE, &map_in1, c0, BWD ? t0 - 1 : t0, n, bar);  // backward: h one step earlier
+        if (BWD) tma::load_box(dst + 2 * TILE, &map_in2, c0, t0, n, bar);
     };
 
     // The scan pass of the chunked form is launched as a programmatic dependent of the map kernel: it
@@ -187,18 +179,13 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     int out_slot = 0, buf = 0;
     float4 carry = make_float4(0.f, 0.f, 0.f, 0.f);  // state entering the tile, for this thread's 4 channels
     const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 unit_A = one4;  // REDUCE: the gate product of the unit so far (carry holds its B)
 
     for (int64_t i = 0; i < n_items; i++) {
         const int stage = (int)(i % STAGES);
         const uint32_t in0 = smem0 + stage * N_IN * TILE + my_off;
         if (i % pieces == 0) {  // a new unit starts
             carry = zero4;
-            unit_A = one4;
-            if (!REDUCE && carry_in != nullptr) {
-                const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
-                carry = *reinterpret_cast<const float4 *>(carry_in + unit * CC + cg * 4);
-            } else if (!REDUCE && maps != nullptr) {
+            if (maps != nullptr) {
                 if (!maps_ready) {  // the maps come from the kernel before this one
                     grid_dependency_wait();
                     maps_ready = true;
@@ -224,12 +211,8 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         for (int k = 0; k < TS; k++) {
             a[k] = lds_vec4<IO>(in0 + k * ROW);
             if (SIGMOID) a[k] = sigmoid4(a[k]);
-            if (BWD && REDUCE) {
-                y[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
-            } else {
-                x[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
-                if (BWD) y[k] = lds_vec4<IO>(in0 + 2 * TILE + k * ROW);
-            }
+            x[k] = lds_vec4<IO>(in0 + TILE + k * ROW);
+            if (BWD) y[k] = lds_vec4<IO>(in0 + 2 * TILE + k * ROW);
         }
         // This thread's run as one map, then the runs of the warp composed (forward: left to
         // right, lower segments first; backward: right to left).
@@ -253,7 +236,7 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             s_tot[buf][warp][cg][0] = m.A;
             s_tot[buf][warp][cg][1] = m.B;
         }
-        if (!REDUCE && tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
+        if (tid == 0) tma::store_wait_read<OUTBUF - 1>();  // the staging slot about to be reused is free
         __syncthreads();
         // Every thread holds its tile data in registers: this very stage can be refilled now.
         if (tid == 0 && i + STAGES < n_items) issue(i + STAGES);
@@ -266,18 +249,8 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             const float4 tA = s_tot[buf][w][cg][0], tB = s_tot[buf][w][cg][1];
             if (w == warp) s = run;
             run = fma4(tA, run, tB);
-            if (REDUCE) unit_A = mul4(unit_A, tA);
         }
         carry = run;
-        if (REDUCE) {  // nothing to replay or store; the unit's map leaves after its last tile
-            if (i % pieces == pieces - 1 && seg == 0) {
-                const int64_t unit = blockIdx.x + (i / pieces) * (int64_t)gridDim.x;
-                *reinterpret_cast<float4 *>(maps + (unit * 2) * CC + cg * 4) = unit_A;
-                *reinterpret_cast<float4 *>(maps + (unit * 2 + 1) * CC + cg * 4) = carry;
-            }
-            buf ^= 1;
-            continue;
-        }
         // ... and this thread's own run: the exclusive prefix inside the warp
         {
             float4 eA = shfl4(m.A, CG, !BWD), eB = shfl4(m.B, CG, !BWD);
@@ -319,8 +292,8 @@ cl_stream_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     if (timed_out && lane == 0) report_device_wait(7);
 }
 
-// The chunk maps of the two-pass form without reading whole chunks: the same maps as the REDUCE
-// instantiation above (layout and meaning of `maps`), folded from the end of the chunk that the NEXT
+// The chunk maps of the two-pass form without reading whole chunks (`maps` as the kernel above reads
+// it: [unit][2][CC], A then B), folded from the end of the chunk that the NEXT
 // chunk depends on -- the forward map from the chunk's last step towards its first, the reverse map
 // from its first step towards the last -- in tiles of SEG*TS steps, and abandoned as soon as the
 // product of the gates walked so far has dropped to |A| <= cut in every one of the unit's 32

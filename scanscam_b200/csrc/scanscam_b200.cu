@@ -1413,28 +1413,28 @@ int make_cl_map(CUtensorMap *map, const IO *ptr, int64_t N, int64_t T, int64_t C
     X(6, 128, 32, 8, 3, 2, 128, 32, 8, 2, 1) X(7, 32, 128, 32, 2, 1, 32, 128, 32, 2, 1)
 
 // `chunk_steps` = 0: a unit is all of T.  Otherwise (a multiple of TT) T is cut into chunks of that
-// many steps, each a unit of its own that starts from carry_in[unit][CC] (or, REDUCE, only writes
-// its map to maps[unit][2][CC]).  Tensors a REDUCE launch does not touch may be NULL.
-template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, bool REDUCE = false, typename IO = float, bool SIGMOID = false>
+// many steps, each a unit of its own that starts from the fold of maps[unit'][2][CC] over the chunks
+// before it (written by cl_tail_map_kernel just ahead in the stream).
+template <int CC, int TT, int SEG, int STAGES, int OUTBUF, bool BWD, typename IO = float, bool SIGMOID = false>
 int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typename as_given<IO>::type *in2,
                typename as_given<IO>::type *out1, typename as_given<IO>::type *out2, int64_t N, int64_t T,
-               int64_t C, cudaStream_t st, int64_t chunk_steps = 0, const float *carry_in = nullptr, float *maps = nullptr) {
-    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO>;
-    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, REDUCE, IO, SIGMOID>;
+               int64_t C, cudaStream_t st, int64_t chunk_steps = 0, const float *maps = nullptr) {
+    using Cfg = ssb::cls::Config<CC, TT, SEG, STAGES, OUTBUF, BWD, IO>;
+    auto kern = ssb::cls::cl_stream_kernel<CC, TT, SEG, STAGES, OUTBUF, BWD, IO, SIGMOID>;
     const int64_t cblocks = (C + CC - 1) / CC, tiles = (T + TT - 1) / TT;
     if (tiles > 0x7fffffffLL) return fail(SSB_ERR_UNSUPPORTED, "channels-last streaming kernels: T too large");
     if (chunk_steps % TT != 0) return fail(SSB_ERR_BAD_ARG, "channels-last streaming kernels: chunk of %lld steps, tiles of %d", (long long)chunk_steps, TT);
     const int64_t pieces = chunk_steps > 0 ? chunk_steps / TT : tiles;
     const int64_t chunks = (tiles + pieces - 1) / pieces;
-    // tensors this launch does not touch still need a valid descriptor: describe the gate instead
-    const IO *p_in1 = (BWD && REDUCE) ? gate : in1, *p_in2 = BWD ? in2 : p_in1;
-    IO *p_out1 = REDUCE ? const_cast<IO *>(gate) : out1, *p_out2 = (BWD && !REDUCE) ? out2 : p_out1;
+    // tensors this launch does not touch still need a valid descriptor: describe a tensor it does
+    const IO *p_in2 = BWD ? in2 : in1;
+    IO *p_out2 = BWD ? out2 : out1;
     CUtensorMap mg, m1, m2, mo1, mo2;
     int rc;
     if ((rc = make_cl_map(&mg, gate, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&m1, p_in1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&m1, in1, N, T, C, CC, TT)) != SSB_OK) return rc;
     if ((rc = make_cl_map(&m2, p_in2, N, T, C, CC, TT)) != SSB_OK) return rc;
-    if ((rc = make_cl_map(&mo1, p_out1, N, T, C, CC, TT)) != SSB_OK) return rc;
+    if ((rc = make_cl_map(&mo1, out1, N, T, C, CC, TT)) != SSB_OK) return rc;
     if ((rc = make_cl_map(&mo2, p_out2, N, T, C, CC, TT)) != SSB_OK) return rc;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
         return check_launch("cudaFuncSetAttribute(cl_stream_kernel)");
@@ -1449,16 +1449,15 @@ int launch_cls(const IO *gate, const typename as_given<IO>::type *in1, const typ
     }
     const int64_t units = N * cblocks * chunks, cap = (int64_t)sm_count() * occ;
     const int grid = (int)(units < cap ? units : cap);
-    if (!REDUCE && maps != nullptr && carry_in == nullptr) {
+    if (maps != nullptr) {
         // the scan pass of the chunked form: it may start beside the map kernel it follows and waits
         // for it inside (griddepcontrol.wait) before the first read of `maps`
         if (launch_dependent(kern, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces,
-                             (int)chunks, carry_in, maps) != cudaSuccess)
+                             (int)chunks, maps) != cudaSuccess)
             return check_launch("cl_stream_kernel (dependent launch)");
         return check_launch("cl_stream_kernel");
     }
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces, (int)chunks,
-                                                      carry_in, maps);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(mg, m1, m2, mo1, mo2, units, (int)cblocks, (int)pieces, (int)chunks, maps);
     return check_launch("cl_stream_kernel");
 }
 
@@ -1510,11 +1509,11 @@ int launch_cls_chunked(const IO *gate, const typename as_given<IO>::type *in1, c
     int rc = check_launch("cl_tail_map_kernel");
     if (rc != SSB_OK) return rc;
     // pass 2: the scan over the chunks; every unit folds the maps of its pair's chunks before it for itself
-    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, nullptr, maps);
+    if (!BWD) return launch_cls<CC, 256, 16, 2, 2, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st, steps, maps);
     if constexpr (sizeof(IO) == 2)
-        return launch_cls<CC, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, nullptr, maps);
+        return launch_cls<CC, 256, 16, 1, 1, true, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, maps);
     else
-        return launch_cls<CC, 128, 16, 2, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, nullptr, maps);
+        return launch_cls<CC, 128, 16, 2, 1, true, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st, steps, maps);
 }
 
 template <int CC, int TT, int STAGES, int OUTBUF, bool BWD>
@@ -1913,11 +1912,11 @@ int cl_h16(const void *gate_, const void *in1_, const void *in2_, void *out1_, v
         workspace_bytes >= cls_chunk_workspace_bytes(N, T, C, 64))
         return launch_cls_chunked<BWD, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
     if (cl_h16_small_tiles(pairs, BWD, SIGMOID)) {
-        if (!BWD) return launch_cls<64, 128, 8, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-        return launch_cls<64, 128, 8, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);
+        if (!BWD) return launch_cls<64, 128, 8, 2, 2, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+        return launch_cls<64, 128, 8, 1, 1, true, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);
     }
-    if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-    return launch_cls<64, 256, 16, 1, 1, true, false, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
+    if (!BWD) return launch_cls<64, 256, 16, 2, 2, false, IO, SIGMOID>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+    return launch_cls<64, 256, 16, 1, 1, true, IO, SIGMOID>(gate, in1, in2, out1, out2, N, T, C, st);  // from a sweep of 42 shapes
 }
 }  // namespace
 
@@ -1990,14 +1989,14 @@ int cl_sigmoid_f32(const float *gate, const float *in1, const float *in2, float 
         return launch_cls_chunked<BWD, float, true>(gate, in1, in2, out1, out2, N, T, C, workspace, workspace_bytes, st);
     switch (cl_stream_id(BWD, N, T, C, true)) {  // the tile shapes of SSB_CLS_CONFIGS ids 1, 2, 0
         case 1:
-            if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-            return launch_cls<64, 128, 8, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+            if (!BWD) return launch_cls<64, 256, 16, 1, 1, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<64, 128, 8, 1, 1, true, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
         case 2:
-            if (!BWD) return launch_cls<32, 128, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-            return launch_cls<32, 256, 16, 1, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+            if (!BWD) return launch_cls<32, 128, 16, 2, 2, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<32, 256, 16, 1, 1, true, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
         default:
-            if (!BWD) return launch_cls<32, 256, 16, 2, 2, false, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
-            return launch_cls<32, 128, 16, 2, 1, true, false, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
+            if (!BWD) return launch_cls<32, 256, 16, 2, 2, false, float, true>(gate, in1, nullptr, out1, nullptr, N, T, C, st);
+            return launch_cls<32, 128, 16, 2, 1, true, float, true>(gate, in1, in2, out1, out2, N, T, C, st);
     }
 }
 }  // namespace
