@@ -776,11 +776,17 @@ int pick_variant(bool backward, int64_t rows, int64_t T, bool all_aligned16, boo
     if (workspace_ok && all_aligned16 && lookback_eligible(rows, T, 0) && T > 4096 && (rows < 1024 || T >= 16384))
         return SSB_VARIANT_LOOKBACK;
     // Small problems (a few spans per SM at most, e.g. [4,256,1024]): the kernels are a few microseconds
-    // long and what counts is how fast the grid gets going, not the steady state: 512-element spans of
-    // 128 threads x 1 float4 give every SM several CTAs at once (6.6 against 7.5 us per forward +
-    // backward on [1024,1024] inside a CUDA graph).
-    if (all_aligned16 && flat_eligible(rows, T) && T <= 4096 && rows * T <= (int64_t)sm_count() * 4 * 4096)
-        return SSB_VARIANT_FLAT | (12 << 8);
+    // long and what counts is how fast the grid gets going, not the steady state.  Power-of-two rows up
+    // to 2048 steps: the TMA-staged sweep with 64-line spans, whose launch overlaps the tail of the
+    // kernel ahead (programmatic dependent launch) -- on [1024,1024], forward + backward: 9.0 us inside
+    // a CUDA graph, 9.6 us as stream launches, against 9.4 / 12.3 us for the choice below.  Other row
+    // lengths: 512-element spans of 128 threads x 1 float4, which give every SM several CTAs at once.
+    // (4096-step rows go to the general rule for power-of-two rows further down.)
+    if (all_aligned16 && T <= 4096 && rows * T <= (int64_t)sm_count() * 4 * 4096) {
+        const bool tma_ok = encode_fn() != nullptr;
+        if (tma_ok && tmaflat_eligible(rows, T, 64)) return SSB_VARIANT_TMA | (34 << 8);
+        if (flat_eligible(rows, T) && !(tma_ok && tmaflat_eligible(rows, T, 128))) return SSB_VARIANT_FLAT | (12 << 8);
+    }
     if (all_aligned16 && tmaflat_eligible(rows, T, 128) && encode_fn() != nullptr) {
         // power-of-two rows that fit a span: the TMA-staged sweep (forward 128 lines x 2 stages;
         // backward 128 lines x 3 stages for 4096-step rows, 64 lines x 2 stages below)

@@ -555,7 +555,10 @@ def test_lookback_workspace_contract():
     assert lib.ssb_scan_recommend(64, 65540, 0, 1, 1) == LOOKBACK               # T not a multiple of 4096
     assert lib.ssb_scan_recommend(64, 65536, 0, 1, 0) & 0xff == FLAT
     assert lib.ssb_scan_recommend(4096, 4096, 0, 1, 1) & 0xff == TMA      # power-of-two rows that fit a span
-    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) == FLAT | (12 << 8)  # ... unless the whole problem is a few spans per SM
+    assert lib.ssb_scan_recommend(64, 4096, 0, 1, 1) == TMA | (32 << 8)   # ... also when the whole problem is a few spans per SM
+    assert lib.ssb_scan_recommend(1024, 1024, 0, 1, 1) == TMA | (34 << 8)  # small problems, power-of-two rows up to 2048 steps: 64-line spans
+    assert lib.ssb_scan_recommend(1024, 1024, 1, 1, 0) == TMA | (34 << 8)
+    assert lib.ssb_scan_recommend(64, 4092, 0, 1, 1) == FLAT | (12 << 8)   # small problems, other row lengths: 512-element spans
     assert lib.ssb_scan_recommend(64, 4092, 0, 1, 1) & 0xff == FLAT
     assert lib.ssb_scan_recommend(64, 4097, 1, 1, 1) & 0xff in (WARP, FLAT_ANY)
     assert lib.ssb_scan_recommend(64, 65536, 1, 0, 1) & 0xff == WARP
