@@ -216,7 +216,7 @@ def test_edge_shapes_and_errors():
 
 @pytest.mark.parametrize("gates,shape", [("sigmoid2", (64, 4096)), ("resets", (40, 2048)), ("nearunit", (4, 65536))])
 @pytest.mark.parametrize("variant", [WARP, TMA, FLAT, _gpu.flat_variant(2), _gpu.flat_variant(3), _gpu.tma_variant(32),
-                                     _gpu.tma_variant(34)])
+                                     _gpu.tma_variant(34), _gpu.tma_variant(10), _gpu.tma_variant(1)])
 def test_shard_carries(gates, shape, variant):
     """A call with carry-in must continue a scan exactly where another call stopped."""
     a, b, g = make_inputs(gates, shape, seed=9)
