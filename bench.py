@@ -55,7 +55,7 @@ TRAFFIC_RECORD = os.path.join(REPO, "profiles", "bwd_kernel_dram_traffic.json")
 # world sizes at which the peer-memory exchange of the T-sharded path has run on real B200s (tests and
 # this bench); at other sizes the default run leaves it out rather than try it first inside the
 # measurement every other number of the line depends on
-PEER_EXCHANGE_WORLDS = frozenset({2, 4})
+PEER_EXCHANGE_WORLDS = frozenset({2, 4, 8})
 
 
 def parse_args():
@@ -85,7 +85,7 @@ def parse_args():
     p.add_argument("--ts-steps", type=int, default=20, help="timed steps of the T-sharded measurement")
     p.add_argument("--peer-exchange", default="auto", choices=["auto", "on", "off"],
                    help="T-sharded measurement: also time the shard maps exchanged through peer memory (auto: at the "
-                        "world sizes this exchange has been run at on B200s: 2 and 4)")
+                        "world sizes this exchange has been run at on B200s: 2, 4 and 8)")
     p.add_argument("--cut", type=float, default=None, help="early-termination threshold of the shard maps (default: the library's)")
     p.add_argument("--sets", type=int, default=0,
                    help="independent buffer sets the timed steps rotate over (0 = as many as keep the L2 from serving re-reads; "
