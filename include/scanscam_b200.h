@@ -332,7 +332,7 @@ typedef enum ssb_cl_variant {
  * the caller can supply whatever ssb_scan_cl_variant_workspace_bytes asks for). */
 int ssb_scan_cl_recommend(int64_t N, int64_t T, int64_t C, int backward, int aligned16, int can_provide_workspace);
 /* Scratch that `variant` needs for this problem and direction: 0 for the plain and streaming
- * kernels, the chunk maps and carries for the chunked form, one record per tile for look-back.
+ * kernels, the chunk maps for the chunked form, one record per tile for look-back.
  * 256-byte aligned; contents need not be initialised. */
 size_t ssb_scan_cl_variant_workspace_bytes(int64_t N, int64_t T, int64_t C, int variant, int backward);
 /* An upper bound of the above over every variant and both directions, for callers that would
